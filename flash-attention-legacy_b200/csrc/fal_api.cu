@@ -1,0 +1,487 @@
+// C-ABI entry points (see include/fal_b200.h): argument validation, TMA
+// descriptor construction and kernel launches.  This file is the counterpart
+// of the reference's csrc/flash_attn_legacy.cpp, minus everything torch.
+#include "../../include/fal_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "fal_common.h"
+#include "fal_launch.h"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return FAL_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------
+// Driver entry point for tensor-map encoding, fetched through the runtime so
+// that the library has no link-time dependency on libcuda.
+// ---------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// fp16 tensor addressed as [batch, head, row, head_dim]; box = 64 x box_rows x 1 x 1,
+// 128-byte swizzle, out-of-range elements read as zero.
+int make_tensor_map(CUtensorMap* map, const void* base, int head_dim, int64_t rows, int64_t heads,
+                    int64_t batch, const fal::RowStrides& st, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return FAL_ERR_TENSOR_MAP;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return FAL_ERR_INVALID_ARGUMENT;
+  // Degenerate dimensions: the driver wants non-zero extents and 16-byte-multiple strides.
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim),
+                              static_cast<cuuint64_t>(rows > 0 ? rows : 1),
+                              static_cast<cuuint64_t>(heads > 0 ? heads : 1),
+                              static_cast<cuuint64_t>(batch > 0 ? batch : 1)};
+  auto fix = [&](int64_t s) -> cuuint64_t {
+    if (s <= 0) s = head_dim;  // unused dimension (extent 1): any valid stride will do
+    return static_cast<cuuint64_t>(s) * 2u;
+  };
+  const cuuint64_t strides[3] = {fix(st.row), fix(st.head), fix(st.batch)};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] % 16u != 0) return FAL_ERR_INVALID_ARGUMENT;
+  const cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(box_rows), 1u, 1u};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FAL_OK : FAL_ERR_TENSOR_MAP;
+}
+
+fal::RowStrides to_rs(const fal_strides* s) { return fal::RowStrides{s->batch, s->head, s->row}; }
+
+int check_device() {
+  static std::mutex mu;
+  static int cached[64] = {};  // 0 unknown, 1 ok, -1 unsupported
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return FAL_ERR_UNSUPPORTED_DEVICE;
+  std::lock_guard<std::mutex> g(mu);
+  if (cached[dev] == 0) {
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    cached[dev] = (major == 10) ? 1 : -1;
+  }
+  return cached[dev] == 1 ? FAL_OK : FAL_ERR_UNSUPPORTED_DEVICE;
+}
+
+bool head_dim_ok(int d) { return d == 64 || d == 128; }
+
+int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+// Backward scratch layout: [dq_accum fp32 batch*heads*padded_rows*d][delta fp32 batch*heads*padded_rows]
+struct BwdWorkspace {
+  int64_t padded_rows;
+  size_t dq_bytes;
+  size_t delta_bytes;
+  size_t total() const { return dq_bytes + delta_bytes; }
+};
+
+BwdWorkspace bwd_workspace_layout(int batch, int heads_q, int rows, int head_dim) {
+  BwdWorkspace w;
+  // One extra 64-row tile of slack: packed sequences start at arbitrary rows.
+  w.padded_rows = round_up(rows, 64) + 64;
+  w.dq_bytes = static_cast<size_t>(batch) * heads_q * w.padded_rows * head_dim * sizeof(float);
+  w.delta_bytes = round_up(static_cast<int64_t>(batch) * heads_q * w.padded_rows * sizeof(float), 256);
+  return w;
+}
+
+constexpr int kDecodeSplitLen = 1024;
+
+}  // namespace
+
+extern "C" {
+
+const char* fal_strerror(int code) {
+  switch (code) {
+    case FAL_OK: return "ok";
+    case FAL_ERR_INVALID_ARGUMENT: return "invalid argument (shape, stride, alignment or null pointer)";
+    case FAL_ERR_UNSUPPORTED_HEAD_DIM: return "unsupported head_dim (64 and 128 are supported)";
+    case FAL_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case FAL_ERR_CUDA: return "CUDA runtime error";
+    case FAL_ERR_TENSOR_MAP: return "TMA descriptor could not be built";
+    case FAL_ERR_UNSUPPORTED_DEVICE: return "device is not compute capability 10.x (B200)";
+    default: return "unknown error";
+  }
+}
+
+int fal_last_cuda_error(void) { return g_last_cuda_error; }
+
+const char* fal_version(void) { return "0.1.0"; }
+
+int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
+            int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
+            const fal_strides* q_strides, const fal_strides* k_strides,
+            const fal_strides* v_strides, const fal_strides* o_strides, float softmax_scale,
+            int is_causal, int* status, void* stream) {
+  if (!q || !k || !v || !o || !lse || !q_strides || !k_strides || !v_strides || !o_strides)
+    return FAL_ERR_INVALID_ARGUMENT;
+  if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || seqlen_q <= 0 || seqlen_k < 0)
+    return FAL_ERR_INVALID_ARGUMENT;
+  if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
+  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
+      o_strides->head % 8 != 0 || o_strides->batch % 8 != 0)
+    return FAL_ERR_INVALID_ARGUMENT;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+
+  CUtensorMap tq, tk, tv;
+  if ((rc = make_tensor_map(&tq, q, head_dim, seqlen_q, heads_q, batch, to_rs(q_strides), 128)))
+    return rc;
+  if ((rc = make_tensor_map(&tk, k, head_dim, seqlen_k, heads_kv, batch, to_rs(k_strides), 128)))
+    return rc;
+  if ((rc = make_tensor_map(&tv, v, head_dim, seqlen_k, heads_kv, batch, to_rs(v_strides), 128)))
+    return rc;
+
+  fal::FwdParams p{};
+  p.o = o;
+  p.lse = lse;
+  p.o_strides = to_rs(o_strides);
+  p.lse_strides = fal::RowStrides{static_cast<int64_t>(heads_q) * seqlen_q, seqlen_q, 1};
+  p.cu_q = nullptr;
+  p.cu_k = nullptr;
+  p.num_seqs = 0;
+  p.batch = batch;
+  p.heads_q = heads_q;
+  p.heads_kv = heads_kv;
+  p.seqlen_q = seqlen_q;
+  p.seqlen_k = seqlen_k;
+  p.num_qblk = (seqlen_q + 255) / 256;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q;
+  if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
+  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid),
+                                  static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* lse,
+                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int num_seqs,
+                   int total_q, int total_k, int max_seqlen_q, int max_seqlen_k, int heads_q,
+                   int heads_kv, int head_dim, const fal_strides* q_strides,
+                   const fal_strides* k_strides, const fal_strides* v_strides,
+                   const fal_strides* o_strides, float softmax_scale, int is_causal, int* status,
+                   void* stream) {
+  (void)max_seqlen_q;
+  (void)max_seqlen_k;
+  if (!q || !k || !v || !o || !lse || !cu_seqlens_q || !cu_seqlens_k || !q_strides || !k_strides ||
+      !v_strides || !o_strides)
+    return FAL_ERR_INVALID_ARGUMENT;
+  if (num_seqs <= 0 || total_q <= 0 || total_k < 0 || heads_q <= 0 || heads_kv <= 0)
+    return FAL_ERR_INVALID_ARGUMENT;
+  if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
+  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
+      o_strides->head % 8 != 0)
+    return FAL_ERR_INVALID_ARGUMENT;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+
+  CUtensorMap tq, tk, tv;
+  fal::RowStrides qs = to_rs(q_strides), ks = to_rs(k_strides), vs = to_rs(v_strides);
+  qs.batch = ks.batch = vs.batch = 0;
+  if ((rc = make_tensor_map(&tq, q, head_dim, total_q, heads_q, 1, qs, 128))) return rc;
+  if ((rc = make_tensor_map(&tk, k, head_dim, total_k, heads_kv, 1, ks, 128))) return rc;
+  if ((rc = make_tensor_map(&tv, v, head_dim, total_k, heads_kv, 1, vs, 128))) return rc;
+
+  fal::FwdParams p{};
+  p.o = o;
+  p.lse = lse;
+  p.o_strides = to_rs(o_strides);
+  p.o_strides.batch = 0;
+  p.lse_strides = fal::RowStrides{0, 1, heads_q};  // lse[token, head]
+  p.cu_q = cu_seqlens_q;
+  p.cu_k = cu_seqlens_k;
+  p.num_seqs = num_seqs;
+  p.batch = 1;
+  p.heads_q = heads_q;
+  p.heads_kv = heads_kv;
+  p.seqlen_q = 0;
+  p.seqlen_k = 0;
+  // Every sequence rounds up to whole 256-row blocks: at most one extra block each.
+  p.num_qblk = total_q / 256 + num_seqs;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q;
+  if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
+  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid),
+                                  static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+size_t fal_bwd_workspace_bytes(int batch, int heads_q, int rows, int head_dim) {
+  if (batch <= 0 || heads_q <= 0 || rows <= 0 || head_dim <= 0) return 0;
+  return bwd_workspace_layout(batch, heads_q, rows, head_dim).total();
+}
+
+namespace {
+
+// Shared tail of the batched and packed backward: pre-pass, main kernel, post-pass.
+struct BwdCall {
+  const void *d_out, *q, *k, *v, *o;
+  const float* lse;
+  void *dq, *dk, *dv;
+  const int32_t *cu_q, *cu_k;
+  int num_seqs;
+  int batch, heads_q, heads_kv, rows_q, rows_k, head_dim;
+  fal::RowStrides s_do, s_q, s_k, s_v, s_o, s_dq, s_dk, s_dv;
+  fal::RowStrides s_lse;
+  float scale;
+  int causal;
+  void* workspace;
+  size_t workspace_bytes;
+  int* status;
+  cudaStream_t stream;
+};
+
+int run_bwd(const BwdCall& c) {
+  if (!c.d_out || !c.q || !c.k || !c.v || !c.o || !c.lse || !c.dq || !c.dk || !c.dv || !c.workspace)
+    return FAL_ERR_INVALID_ARGUMENT;
+  if (c.batch <= 0 || c.heads_q <= 0 || c.heads_kv <= 0 || c.rows_q <= 0 || c.rows_k <= 0)
+    return FAL_ERR_INVALID_ARGUMENT;
+  if (c.heads_q % c.heads_kv != 0 || !(c.scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
+  if (!head_dim_ok(c.head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  auto out_ok = [](const void* ptr, const fal::RowStrides& s) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && s.row % 8 == 0 && s.head % 8 == 0 &&
+           s.batch % 8 == 0;
+  };
+  if (!out_ok(c.dq, c.s_dq) || !out_ok(c.dk, c.s_dk) || !out_ok(c.dv, c.s_dv) ||
+      !out_ok(c.o, c.s_o) || !out_ok(c.d_out, c.s_do))
+    return FAL_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(c.workspace) & 255u) != 0) return FAL_ERR_INVALID_ARGUMENT;
+  const BwdWorkspace w = bwd_workspace_layout(c.batch, c.heads_q, c.rows_q, c.head_dim);
+  if (c.workspace_bytes < w.total()) return FAL_ERR_WORKSPACE_TOO_SMALL;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+
+  float* dq_accum = static_cast<float*>(c.workspace);
+  float* delta = reinterpret_cast<float*>(static_cast<char*>(c.workspace) + w.dq_bytes);
+  const int64_t acc_head = w.padded_rows * c.head_dim;
+  const int64_t acc_batch = acc_head * c.heads_q;
+
+  CUtensorMap tq, tk, tv, tdo;
+  if ((rc = make_tensor_map(&tq, c.q, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_q, 64))) return rc;
+  if ((rc = make_tensor_map(&tdo, c.d_out, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_do, 64)))
+    return rc;
+  if ((rc = make_tensor_map(&tk, c.k, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_k, 128))) return rc;
+  if ((rc = make_tensor_map(&tv, c.v, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_v, 128))) return rc;
+
+  fal::BwdPrepParams pp{};
+  pp.o = c.o;
+  pp.d_o = c.d_out;
+  pp.o_strides = c.s_o;
+  pp.do_strides = c.s_do;
+  pp.delta = delta;
+  pp.delta_head_stride = w.padded_rows;
+  pp.delta_batch_stride = w.padded_rows * c.heads_q;
+  pp.dq_accum = dq_accum;
+  pp.dq_accum_head_stride = acc_head;
+  pp.dq_accum_batch_stride = acc_batch;
+  pp.batch = c.batch;
+  pp.heads_q = c.heads_q;
+  pp.rows = c.rows_q;
+  pp.padded_rows = static_cast<int>(w.padded_rows);
+  pp.head_dim = c.head_dim;
+  cudaError_t e = fal::launch_bwd_prep(pp, c.stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+
+  fal::BwdParams p{};
+  p.dk = c.dk;
+  p.dv = c.dv;
+  p.dk_strides = c.s_dk;
+  p.dv_strides = c.s_dv;
+  p.dq_accum = dq_accum;
+  p.dq_accum_head_stride = acc_head;
+  p.dq_accum_batch_stride = acc_batch;
+  p.lse = c.lse;
+  p.lse_strides = c.s_lse;
+  p.delta = delta;
+  p.delta_head_stride = pp.delta_head_stride;
+  p.delta_batch_stride = pp.delta_batch_stride;
+  p.cu_q = c.cu_q;
+  p.cu_k = c.cu_k;
+  p.num_seqs = c.num_seqs;
+  p.batch = c.batch;
+  p.heads_q = c.heads_q;
+  p.heads_kv = c.heads_kv;
+  p.seqlen_q = c.cu_q ? 0 : c.rows_q;
+  p.seqlen_k = c.cu_k ? 0 : c.rows_k;
+  p.num_kvblk = c.cu_k ? (c.rows_k / 128 + c.num_seqs) : (c.rows_k + 127) / 128;
+  p.scale = c.scale;
+  p.scale_log2 = c.scale * 1.4426950408889634f;
+  p.status = c.status;
+  const int64_t grid = static_cast<int64_t>(p.num_kvblk) * c.batch * c.heads_kv;
+  if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
+  e = fal::launch_bwd(c.head_dim, c.causal != 0, tq, tk, tv, tdo, p, static_cast<int>(grid), c.stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+
+  fal::BwdPostParams po{};
+  po.dq_accum = dq_accum;
+  po.dq_accum_head_stride = acc_head;
+  po.dq_accum_batch_stride = acc_batch;
+  po.dq = c.dq;
+  po.dq_strides = c.s_dq;
+  po.batch = c.batch;
+  po.heads_q = c.heads_q;
+  po.rows = c.rows_q;
+  po.head_dim = c.head_dim;
+  po.scale = c.scale;
+  e = fal::launch_bwd_post(po, c.stream);
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+}  // namespace
+
+int fal_bwd(const void* d_out, const void* q, const void* k, const void* v, const void* o,
+            const float* lse, void* dq, void* dk, void* dv, int batch, int heads_q, int heads_kv,
+            int seqlen_q, int seqlen_k, int head_dim, const fal_strides* do_strides,
+            const fal_strides* q_strides, const fal_strides* k_strides,
+            const fal_strides* v_strides, const fal_strides* o_strides,
+            const fal_strides* dq_strides, const fal_strides* dk_strides,
+            const fal_strides* dv_strides, float softmax_scale, int is_causal, void* workspace,
+            size_t workspace_bytes, int* status, void* stream) {
+  if (!do_strides || !q_strides || !k_strides || !v_strides || !o_strides || !dq_strides ||
+      !dk_strides || !dv_strides)
+    return FAL_ERR_INVALID_ARGUMENT;
+  BwdCall c{};
+  c.d_out = d_out; c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse;
+  c.dq = dq; c.dk = dk; c.dv = dv;
+  c.cu_q = nullptr; c.cu_k = nullptr; c.num_seqs = 0;
+  c.batch = batch; c.heads_q = heads_q; c.heads_kv = heads_kv;
+  c.rows_q = seqlen_q; c.rows_k = seqlen_k; c.head_dim = head_dim;
+  c.s_do = to_rs(do_strides); c.s_q = to_rs(q_strides); c.s_k = to_rs(k_strides);
+  c.s_v = to_rs(v_strides); c.s_o = to_rs(o_strides); c.s_dq = to_rs(dq_strides);
+  c.s_dk = to_rs(dk_strides); c.s_dv = to_rs(dv_strides);
+  c.s_lse = fal::RowStrides{static_cast<int64_t>(heads_q) * seqlen_q, seqlen_q, 1};
+  c.scale = softmax_scale; c.causal = is_causal;
+  c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+  c.status = status; c.stream = static_cast<cudaStream_t>(stream);
+  return run_bwd(c);
+}
+
+int fal_bwd_varlen(const void* d_out, const void* q, const void* k, const void* v, const void* o,
+                   const float* lse, void* dq, void* dk, void* dv, const int32_t* cu_seqlens_q,
+                   const int32_t* cu_seqlens_k, int num_seqs, int total_q, int total_k,
+                   int max_seqlen_q, int max_seqlen_k, int heads_q, int heads_kv, int head_dim,
+                   const fal_strides* do_strides, const fal_strides* q_strides,
+                   const fal_strides* k_strides, const fal_strides* v_strides,
+                   const fal_strides* o_strides, const fal_strides* dq_strides,
+                   const fal_strides* dk_strides, const fal_strides* dv_strides,
+                   float softmax_scale, int is_causal, void* workspace, size_t workspace_bytes,
+                   int* status, void* stream) {
+  (void)max_seqlen_q;
+  (void)max_seqlen_k;
+  if (!do_strides || !q_strides || !k_strides || !v_strides || !o_strides || !dq_strides ||
+      !dk_strides || !dv_strides || !cu_seqlens_q || !cu_seqlens_k || num_seqs <= 0)
+    return FAL_ERR_INVALID_ARGUMENT;
+  BwdCall c{};
+  c.d_out = d_out; c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse;
+  c.dq = dq; c.dk = dk; c.dv = dv;
+  c.cu_q = cu_seqlens_q; c.cu_k = cu_seqlens_k; c.num_seqs = num_seqs;
+  c.batch = 1; c.heads_q = heads_q; c.heads_kv = heads_kv;
+  c.rows_q = total_q; c.rows_k = total_k; c.head_dim = head_dim;
+  auto packed = [](const fal_strides* s) { return fal::RowStrides{0, s->head, s->row}; };
+  c.s_do = packed(do_strides); c.s_q = packed(q_strides); c.s_k = packed(k_strides);
+  c.s_v = packed(v_strides); c.s_o = packed(o_strides); c.s_dq = packed(dq_strides);
+  c.s_dk = packed(dk_strides); c.s_dv = packed(dv_strides);
+  c.s_lse = fal::RowStrides{0, 1, heads_q};
+  c.scale = softmax_scale; c.causal = is_causal;
+  c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+  c.status = status; c.stream = static_cast<cudaStream_t>(stream);
+  return run_bwd(c);
+}
+
+size_t fal_decode_workspace_bytes(int batch, int heads_q, int capacity, int head_dim) {
+  if (batch <= 0 || heads_q <= 0 || capacity <= 0 || head_dim <= 0) return 0;
+  const int64_t splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
+  const int64_t rows = static_cast<int64_t>(batch) * heads_q * splits;
+  return static_cast<size_t>(rows) * (head_dim + 2) * sizeof(float);
+}
+
+int fal_decode(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,
+               const fal_strides* v_strides, const int32_t* cache_seqlens, const void* k_new,
+               const void* v_new, void* o, float* lse, int batch, int heads_q, int heads_kv,
+               int capacity, int head_dim, float softmax_scale, void* workspace,
+               size_t workspace_bytes, int* status, void* stream) {
+  if (!q || !k_cache || !v_cache || !k_strides || !v_strides || !cache_seqlens || !o || !workspace)
+    return FAL_ERR_INVALID_ARGUMENT;
+  if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
+  if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || capacity <= 0) return FAL_ERR_INVALID_ARGUMENT;
+  if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
+  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o) ||
+      !aligned16(k_new) || !aligned16(v_new))
+    return FAL_ERR_INVALID_ARGUMENT;
+  const fal_strides* both[2] = {k_strides, v_strides};
+  for (const fal_strides* s : both)
+    if (s->row % 8 != 0 || s->head % 8 != 0 || s->batch % 8 != 0) return FAL_ERR_INVALID_ARGUMENT;
+  if (workspace_bytes < fal_decode_workspace_bytes(batch, heads_q, capacity, head_dim))
+    return FAL_ERR_WORKSPACE_TOO_SMALL;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+
+  fal::DecodeParams p{};
+  p.q = q;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.k_strides = to_rs(k_strides);
+  p.v_strides = to_rs(v_strides);
+  p.k_new = k_new;
+  p.v_new = v_new;
+  p.cache_seqlens = cache_seqlens;
+  p.o = o;
+  p.lse = lse;
+  p.batch = batch;
+  p.heads_q = heads_q;
+  p.heads_kv = heads_kv;
+  p.capacity = capacity;
+  p.head_dim = head_dim;
+  p.split_len = kDecodeSplitLen;
+  p.splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
+  p.scale = softmax_scale;
+  p.status = status;
+  p.part_o = static_cast<float*>(workspace);
+  p.part_ml = p.part_o + static_cast<int64_t>(batch) * heads_q * p.splits * head_dim;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (k_new != nullptr) {
+    e = fal::launch_decode_append(p, st);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  e = fal::launch_decode_splitk(p, st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = fal::launch_decode_combine(p, st);
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+}  // extern "C"

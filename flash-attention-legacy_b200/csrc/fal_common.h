@@ -1,0 +1,70 @@
+// Host/device-shared parameter blocks for the attention kernels.
+//
+// These play the role of the reference's POD argument structs
+// (csrc/include/flash_attn_common.h:25-147 in sirCamp/flash-attention-legacy):
+// raw pointers, sizes, element strides, softmax scale and the causal flag.
+// Strides are 64-bit here (the reference's are int32, which overflows on
+// long-context inputs).
+#pragma once
+
+#include <stdint.h>
+
+namespace fal {
+
+// Where a [batch, head, row] coordinate lives inside a tensor whose last
+// dimension (head_dim) is contiguous.  Strides are in elements.
+struct RowStrides {
+  int64_t batch;
+  int64_t head;
+  int64_t row;
+};
+
+struct FwdParams {
+  void* o;     // fp16 output
+  float* lse;  // natural-log LSE of the scaled scores
+  RowStrides o_strides;
+  RowStrides lse_strides;  // in floats; batched [B,Hq,N] or packed [total,Hq]
+  const int32_t* cu_q;     // packed mode: cumulative lengths, else nullptr
+  const int32_t* cu_k;
+  int num_seqs;   // packed mode only
+  int batch;      // batched mode only
+  int heads_q;
+  int heads_kv;
+  int seqlen_q;   // batched mode only
+  int seqlen_k;   // batched mode only
+  int num_qblk;   // batched: ceil(seqlen_q / 256); packed: bound on all sequences' blocks
+  float scale;       // softmax scale
+  float scale_log2;  // softmax scale * log2(e)
+  int* status;       // device status word, may be nullptr
+};
+
+struct BwdParams {
+  // outputs
+  void* dk;  // fp16
+  void* dv;  // fp16
+  RowStrides dk_strides;
+  RowStrides dv_strides;
+  float* dq_accum;  // fp32 [batch, heads_q, padded_q_rows, head_dim] (packed: [heads_q, padded_total, head_dim])
+  int64_t dq_accum_head_stride;   // floats
+  int64_t dq_accum_batch_stride;  // floats
+  // per-row statistics, [batch, heads_q, rows] (packed: strides say where)
+  const float* lse;
+  RowStrides lse_strides;
+  const float* delta;  // rowsum(dO * O), same indexing as dq_accum rows: [batch, heads_q, padded rows]
+  int64_t delta_head_stride;
+  int64_t delta_batch_stride;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int num_seqs;
+  int batch;
+  int heads_q;
+  int heads_kv;
+  int seqlen_q;
+  int seqlen_k;
+  int num_kvblk;  // batched: ceil(seqlen_k / 128); packed: bound over all sequences
+  float scale;
+  float scale_log2;
+  int* status;
+};
+
+}  // namespace fal

@@ -1,0 +1,467 @@
+// FlashAttention-2 forward for sm_100a: online-softmax QK^T / PV on tcgen05
+// tensor cores with TMEM accumulators, TMA-staged 128B-swizzled shared memory
+// and a warp-specialised producer / MMA-issuer / softmax pipeline.
+//
+// Replaces flash_attn_fwd_volta_kernel and its packed twin
+// (csrc/kernels/flash_attn_fwd_volta.cu:170-345, :350-523 of the reference):
+// same math -- s = (q.k) * scale, top-left-aligned causal mask (kv > q masked,
+// local indices), fp32 online softmax with P rounded to fp16 before PV,
+// O = acc / l, L = m + ln(l) -- on a different machine model.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row tiles, each
+// with its own softmax warpgroup, S/P tile and O accumulator in TMEM.  The
+// single MMA-issuing thread interleaves the two tiles so that one tile's
+// softmax overlaps the other's tensor-core work:
+//
+//   warps 0-3   softmax + output for rows   0..127  (TMEM lanes by warp % 4)
+//   warps 4-7   softmax + output for rows 128..255
+//   warp  8     TMA producer (one elected lane)
+//   warp  9     tcgen05.mma issuer (one elected lane), TMEM owner
+//
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+// P (fp16) overwrites the first 64 columns of its S tile and feeds the PV MMA
+// straight from TMEM.
+#include "fal_common.h"
+#include "fal_launch.h"
+#include "sm100_ptx.cuh"
+
+namespace fal {
+
+namespace {
+
+constexpr int kFwdThreads = 320;
+constexpr int kTileM = 128;   // query rows per softmax warpgroup
+constexpr int kTileN = 128;   // keys per step
+constexpr int kCtaRows = 2 * kTileM;
+constexpr float kNegInf = -INFINITY;
+// Skip the O rescale while the running maximum grows by less than 2^8.
+constexpr float kRescaleThreshold = 8.0f;
+
+// Barrier ids (only used to label a wait that gave up).
+enum FwdBarrier : int {
+  kBarQFull = 0,
+  kBarKFull = 10,
+  kBarKEmpty = 20,
+  kBarVFull = 30,
+  kBarVEmpty = 40,
+  kBarSReady = 50,
+  kBarPReady = 60,
+  kBarODone = 70,
+};
+
+template <int D>
+struct FwdSmem {
+  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kBoxes = D / 64;                 // 64-element (128-byte) column boxes
+  static constexpr int kBoxBytes = kTileM * 128;        // one box of a 128-row tile
+  static constexpr int kTileBytes = kBoxes * kBoxBytes;  // Q, K and V tiles are all 128 x D
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = 2 * kTileBytes;
+  static constexpr int kVOff = kKOff + kStages * kTileBytes;
+  static constexpr int kBarOff = kVOff + kStages * kTileBytes;
+  // barriers: q_full[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_ready[2] p_ready[2] o_done[2]
+  static constexpr int kNumBars = 2 + 4 * kStages + 6;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
+  static constexpr int kBytes = kMiscOff + 16;
+  static constexpr int kAllocBytes = kBytes + 1024;  // room to align the base to 1024
+};
+
+struct FwdWork {
+  int batch;     // TMA batch coordinate (0 when packed)
+  int head;
+  int kv_head;
+  int qblk;      // 256-row block inside the sequence
+  int q_row0;    // TMA row coordinate of the sequence's first query
+  int k_row0;    // TMA row coordinate of the sequence's first key
+  int seqlen_q;
+  int seqlen_k;
+  int64_t o_base;    // element offset of (batch, head, sequence row 0)
+  int64_t lse_base;  // float offset of the same
+};
+
+// Maps blockIdx.x to a unit of work.  Returns false when the block has none
+// (packed mode launches an upper bound of blocks).
+__device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, FwdWork& w) {
+  const int idx = blockIdx.x;
+  if (p.cu_q == nullptr) {
+    const int bh_count = p.batch * p.heads_q;
+    // Heaviest (last) query blocks first: under a causal mask they have the most keys.
+    w.qblk = p.num_qblk - 1 - idx / bh_count;
+    const int bh = idx % bh_count;
+    w.batch = bh / p.heads_q;
+    w.head = bh % p.heads_q;
+    w.q_row0 = 0;
+    w.k_row0 = 0;
+    w.seqlen_q = p.seqlen_q;
+    w.seqlen_k = p.seqlen_k;
+    w.o_base = w.batch * p.o_strides.batch + w.head * p.o_strides.head;
+    w.lse_base = w.batch * p.lse_strides.batch + w.head * p.lse_strides.head;
+  } else {
+    const int slot = idx / p.heads_q;
+    w.head = idx % p.heads_q;
+    w.batch = 0;
+    int first = 0;
+    int seq = -1;
+    int q_start = 0;
+    for (int s = 0; s < p.num_seqs; ++s) {
+      const int a = __ldg(p.cu_q + s);
+      const int e = __ldg(p.cu_q + s + 1);
+      const int nblk = (e - a + kCtaRows - 1) / kCtaRows;
+      if (slot < first + nblk) {
+        seq = s;
+        q_start = a;
+        w.seqlen_q = e - a;
+        break;
+      }
+      first += nblk;
+    }
+    if (seq < 0) return false;
+    w.qblk = slot - first;
+    w.q_row0 = q_start;
+    w.k_row0 = __ldg(p.cu_k + seq);
+    w.seqlen_k = __ldg(p.cu_k + seq + 1) - w.k_row0;
+    w.o_base = w.head * p.o_strides.head + static_cast<int64_t>(q_start) * p.o_strides.row;
+    w.lse_base = w.head * p.lse_strides.head + static_cast<int64_t>(q_start) * p.lse_strides.row;
+  }
+  w.kv_head = w.head / (p.heads_q / p.heads_kv);
+  return true;
+}
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using L = FwdSmem<D>;
+  constexpr int NS = L::kStages;
+
+  FwdWork wk;
+  if (!fwd_decode_work(p, wk)) return;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+
+  const uint32_t bar0 = sbase + L::kBarOff;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  const int iQFull = 0, iKFull = 2, iKEmpty = 2 + NS, iVFull = 2 + 2 * NS, iVEmpty = 2 + 3 * NS,
+            iSReady = 2 + 4 * NS, iPReady = iSReady + 2, iODone = iSReady + 4;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kMiscOff + 4);
+  const WaitCtx wctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Number of key tiles each 128-row query tile visits.
+  const int nk_tiles = (wk.seqlen_k + kTileN - 1) / kTileN;
+  int ntile[2];
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    const int row0 = wk.qblk * kCtaRows + w * kTileM;
+    int n = 0;
+    if (row0 < wk.seqlen_q) {
+      n = nk_tiles;
+      if (CAUSAL) n = min(n, row0 / kTileN + 1);
+    }
+    ntile[w] = n;
+  }
+  const int n_max = max(ntile[0], ntile[1]);
+
+  // ---- one-time setup -------------------------------------------------------
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(iQFull + 0), 1);
+    mbar_init(bar(iQFull + 1), 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bar(iKFull + s), 1);
+      mbar_init(bar(iKEmpty + s), 1);
+      mbar_init(bar(iVFull + s), 1);
+      mbar_init(bar(iVEmpty + s), 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(bar(iSReady + w), 1);
+      mbar_init(bar(iPReady + w), kTileM);
+      mbar_init(bar(iODone + w), 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // ===================== TMA producer =====================================
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      for (int w = 0; w < 2; ++w) {
+        if (ntile[w] == 0) continue;
+        mbar_arrive_expect_tx(bar(iQFull + w), L::kTileBytes);
+        const int row = wk.q_row0 + wk.qblk * kCtaRows + w * kTileM;
+        for (int bx = 0; bx < L::kBoxes; ++bx)
+          tma_load_4d(sbase + L::kQOff + w * L::kTileBytes + bx * L::kBoxBytes, &tm_q,
+                      bar(iQFull + w), bx * 64, row, wk.head, wk.batch);
+      }
+      for (int j = 0; j < n_max; ++j) {
+        const int s = j % NS;
+        const int use = j / NS;
+        const int row = wk.k_row0 + j * kTileN;
+        if (use > 0) mbar_wait(bar(iKEmpty + s), (use - 1) & 1, wctx, kBarKEmpty + s);
+        mbar_arrive_expect_tx(bar(iKFull + s), L::kTileBytes);
+        for (int bx = 0; bx < L::kBoxes; ++bx)
+          tma_load_4d(sbase + L::kKOff + s * L::kTileBytes + bx * L::kBoxBytes, &tm_k,
+                      bar(iKFull + s), bx * 64, row, wk.kv_head, wk.batch);
+        if (use > 0) mbar_wait(bar(iVEmpty + s), (use - 1) & 1, wctx, kBarVEmpty + s);
+        mbar_arrive_expect_tx(bar(iVFull + s), L::kTileBytes);
+        for (int bx = 0; bx < L::kBoxes; ++bx)
+          tma_load_4d(sbase + L::kVOff + s * L::kTileBytes + bx * L::kBoxBytes, &tm_v,
+                      bar(iVFull + s), bx * 64, row, wk.kv_head, wk.batch);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    // ===================== MMA issuer =======================================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(kTileM, kTileN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_f16(kTileM, D, 0, 1);
+      // S[w] = Q[w] K_j^T : both operands K-major (head_dim contiguous), 16 head-dim
+      // elements (32 bytes inside the 128-byte swizzle row) per instruction.
+      auto issue_qk = [&](int w, int j) {
+        const uint32_t qa = sbase + L::kQOff + w * L::kTileBytes;
+        const uint32_t ka = sbase + L::kKOff + (j % NS) * L::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * L::kBoxBytes + (ks & 3) * 32;
+          umma_ss(tmem_base + w * kTileN, make_smem_desc_sw128(qa + off, 16, 1024),
+                  make_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+        }
+      };
+      // O[w] += P[w] V_j : A = P from TMEM (8 columns of packed fp16 per 16 keys), B = V
+      // MN-major (head_dim contiguous): 16 keys = 2048 bytes per step, 64-column halves
+      // kBoxBytes apart (LBO), 8-key groups 1024 bytes apart (SBO).
+      auto issue_pv = [&](int w, int j) {
+        const uint32_t va = sbase + L::kVOff + (j % NS) * L::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kTileN / 16; ++ks) {
+          umma_ts(tmem_base + 256 + w * D, tmem_base + w * kTileN + ks * 8,
+                  make_smem_desc_sw128(va + ks * 2048, L::kBoxBytes, 1024), idesc_pv,
+                  (j > 0 || ks > 0) ? 1u : 0u);
+        }
+      };
+
+      if (n_max > 0) {
+        mbar_wait(bar(iKFull + 0), 0, wctx, kBarKFull);
+        for (int w = 0; w < 2; ++w) {
+          if (ntile[w] == 0) continue;
+          mbar_wait(bar(iQFull + w), 0, wctx, kBarQFull + w);
+          tc_fence_after_sync();
+          issue_qk(w, 0);
+          tc_commit(bar(iSReady + w));
+        }
+        tc_commit(bar(iKEmpty + 0));
+      }
+      for (int j = 0; j < n_max; ++j) {
+        const int s = j % NS;
+        const int use = j / NS;
+        for (int w = 0; w < 2; ++w) {
+          if (j >= ntile[w]) continue;
+          mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w);
+          mbar_wait(bar(iVFull + s), use & 1, wctx, kBarVFull + s);
+          tc_fence_after_sync();
+          issue_pv(w, j);
+          tc_commit(bar(iODone + w));
+          if (w == 1 || j >= ntile[1]) tc_commit(bar(iVEmpty + s));
+          if (j + 1 < ntile[w]) {
+            const int s1 = (j + 1) % NS;
+            mbar_wait(bar(iKFull + s1), ((j + 1) / NS) & 1, wctx, kBarKFull + s1);
+            tc_fence_after_sync();
+            issue_qk(w, j + 1);
+            tc_commit(bar(iSReady + w));
+            if (w == 1 || j + 1 >= ntile[1]) tc_commit(bar(iKEmpty + s1));
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===================== softmax + output =================================
+    const int wg = warp >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int q_tile0 = wk.qblk * kCtaRows + wg * kTileM;  // first row of this tile (local)
+    const int q_local = q_tile0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_addr + wg * kTileN;
+    const uint32_t tO = tmem_base + lane_addr + 256 + wg * D;
+    const int nt = ntile[wg];
+    const float c2 = p.scale_log2;
+
+    float m_ref = kNegInf;
+    float l = 0.f;
+
+    for (int j = 0; j < nt; ++j) {
+      mbar_wait(bar(iSReady + wg), j & 1, wctx, kBarSReady + wg);
+      tc_fence_after_sync();
+      const int kv0 = j * kTileN;
+      int limit = wk.seqlen_k - kv0;  // columns c < limit are visible
+      if (CAUSAL) limit = min(limit, q_local - kv0 + 1);
+      const bool tile_mask =
+          (kv0 + kTileN > wk.seqlen_k) || (CAUSAL && (kv0 + kTileN - 1 > q_tile0));
+
+      // pass 1: row maximum of the raw scores
+      float mx = kNegInf;
+#pragma unroll
+      for (int c = 0; c < kTileN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tS + c * 32, r);
+        tmem_wait_ld();
+        if (tile_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = (c * 32 + i < limit) ? __uint_as_float(r[i]) : kNegInf;
+            mx = fmaxf(mx, v);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m_ref, mx);
+
+      if (j == 0) {
+        m_ref = m_new;
+      } else {
+        const bool need = (m_new - m_ref) * c2 > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          // PV of the previous step must have landed before O is touched.
+          mbar_wait(bar(iODone + wg), (j - 1) & 1, wctx, kBarODone + wg);
+          tc_fence_after_sync();
+          const float alpha = (m_new == kNegInf) ? 1.f : fast_exp2((m_ref - m_new) * c2);
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tO + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(tO + c * 32, r);
+          }
+          l *= alpha;
+          m_ref = m_new;
+        }
+      }
+      const float moff = (m_ref == kNegInf) ? 0.f : m_ref * c2;
+
+      // pass 2: P = exp2(s * c2 - m * c2), row sum, fp16 P back into TMEM
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < kTileN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tS + c * 32, r);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float x0 = fmaf(__uint_as_float(r[i]), c2, -moff);
+          float x1 = fmaf(__uint_as_float(r[i + 1]), c2, -moff);
+          if (tile_mask) {
+            if (c * 32 + i >= limit) x0 = kNegInf;
+            if (c * 32 + i + 1 >= limit) x1 = kNegInf;
+          }
+          const float p0 = fast_exp2(x0);
+          const float p1 = fast_exp2(x1);
+          sum0 += p0;
+          sum1 += p1;
+          pk[i >> 1] = pack_half2(p0, p1);
+        }
+        tmem_st_32x32b_x16(tS + c * 16, pk);
+      }
+      l += sum0 + sum1;
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar(iPReady + wg));
+    }
+
+    // ---- epilogue: O / l -> fp16, LSE -----------------------------------------
+    if (nt > 0) {
+      mbar_wait(bar(iODone + wg), (nt - 1) & 1, wctx, kBarODone + wg);
+      tc_fence_after_sync();
+    }
+    const float inv = (l > 0.f) ? 1.f / l : 0.f;
+    const bool row_ok = q_local < wk.seqlen_q;
+    __half* o_row = static_cast<__half*>(p.o) + wk.o_base +
+                    static_cast<int64_t>(q_local) * p.o_strides.row;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      if (nt > 0) {
+        tmem_ld_32x32b_x32(tO + c * 32, r);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 out;
+          out.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
+          out.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
+          out.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
+          out.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(o_row + c * 32 + v * 8) = out;
+        }
+      }
+    }
+    if (row_ok) {
+      const float lse = (nt > 0 && m_ref != kNegInf) ? m_ref * p.scale + logf(fmaxf(l, 1e-20f))
+                                                      : kNegInf;
+      p.lse[wk.lse_base + static_cast<int64_t>(q_local) * p.lse_strides.row] = lse;
+    }
+  }
+
+  // ---- teardown -------------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D, bool CAUSAL>
+cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         const FwdParams& p, int grid, cudaStream_t stream) {
+  auto kern = fal_fwd_kernel<D, CAUSAL>;
+  static DeviceOnce configured;  // one per template instance
+  cudaError_t e = configured.run([&] {
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                FwdSmem<D>::kAllocBytes);
+  });
+  if (e != cudaSuccess) return e;
+  kern<<<grid, kFwdThreads, FwdSmem<D>::kAllocBytes, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
+                       const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream) {
+  if (head_dim == 128) {
+    return causal ? launch_fwd_t<128, true>(tq, tk, tv, p, grid, stream)
+                  : launch_fwd_t<128, false>(tq, tk, tv, p, grid, stream);
+  }
+  if (head_dim == 64) {
+    return causal ? launch_fwd_t<64, true>(tq, tk, tv, p, grid, stream)
+                  : launch_fwd_t<64, false>(tq, tk, tv, p, grid, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fal

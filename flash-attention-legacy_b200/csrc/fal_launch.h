@@ -1,0 +1,110 @@
+// Internal launcher declarations shared by the kernel files and the C-ABI layer.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "fal_common.h"
+
+namespace fal {
+
+// Runs a per-device set-up action (e.g. cudaFuncSetAttribute) once for each
+// device that launches a kernel, under a mutex so that concurrent callers on
+// different host threads are safe.
+class DeviceOnce {
+ public:
+  template <class F>
+  cudaError_t run(F&& f) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> g(mu_);
+    if (done_[dev]) return cudaSuccess;
+    e = f();
+    if (e == cudaSuccess) done_[dev] = true;
+    return e;
+  }
+
+ private:
+  static constexpr int kMaxDevices = 64;
+  std::mutex mu_;
+  bool done_[kMaxDevices] = {};
+};
+
+// Forward: grid = number of (256-row block, batch*head) units.
+cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
+                       const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream);
+
+// Backward pre-pass: delta = rowsum(dO * O) and zero of the fp32 dQ accumulator.
+struct BwdPrepParams {
+  const void* o;
+  const void* d_o;
+  RowStrides o_strides;
+  RowStrides do_strides;
+  float* delta;
+  int64_t delta_head_stride;
+  int64_t delta_batch_stride;
+  float* dq_accum;
+  int64_t dq_accum_head_stride;
+  int64_t dq_accum_batch_stride;
+  int batch;       // 1 when packed
+  int heads_q;
+  int rows;        // batched: seqlen_q; packed: total_q
+  int padded_rows; // rows of delta / dq_accum per (batch, head)
+  int head_dim;
+};
+cudaError_t launch_bwd_prep(const BwdPrepParams& p, cudaStream_t stream);
+
+// Backward main kernel: grid = number of (128-key block, batch*kv_head) units.
+cudaError_t launch_bwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
+                       const CUtensorMap& tv, const CUtensorMap& tdo, const BwdParams& p, int grid,
+                       cudaStream_t stream);
+
+// Backward post-pass: dQ = fp16(scale * dq_accum).
+struct BwdPostParams {
+  const float* dq_accum;
+  int64_t dq_accum_head_stride;
+  int64_t dq_accum_batch_stride;
+  void* dq;
+  RowStrides dq_strides;
+  int batch;
+  int heads_q;
+  int rows;
+  int head_dim;
+  float scale;
+};
+cudaError_t launch_bwd_post(const BwdPostParams& p, cudaStream_t stream);
+
+// Split-K decode over a KV cache, then the log-sum-exp combine.
+struct DecodeParams {
+  const void* q;        // [batch, heads_q, head_dim] fp16, contiguous
+  void* k_cache;        // fp16
+  void* v_cache;        // fp16
+  RowStrides k_strides; // batch / head / row(position) strides in elements
+  RowStrides v_strides;
+  const void* k_new;    // optional [batch, heads_kv, head_dim] fp16 to append, else nullptr
+  const void* v_new;
+  const int32_t* cache_seqlens;  // [batch] valid positions before the append
+  void* o;              // [batch, heads_q, head_dim] fp16
+  float* lse;           // optional [batch, heads_q]
+  float* part_o;        // workspace [batch, heads_q, splits, head_dim] fp32
+  float* part_ml;       // workspace [batch, heads_q, splits, 2] (max, sum)
+  int batch;
+  int heads_q;
+  int heads_kv;
+  int capacity;         // cache positions per batch entry
+  int head_dim;
+  int split_len;        // positions per split (multiple of the key tile)
+  int splits;           // ceil(capacity / split_len)
+  float scale;
+  int* status;
+};
+cudaError_t launch_decode_append(const DecodeParams& p, cudaStream_t stream);
+cudaError_t launch_decode_splitk(const DecodeParams& p, cudaStream_t stream);
+cudaError_t launch_decode_combine(const DecodeParams& p, cudaStream_t stream);
+
+}  // namespace fal

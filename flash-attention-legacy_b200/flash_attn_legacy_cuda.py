@@ -1,0 +1,326 @@
+"""ctypes binding of `lib/libfal_b200.so`, under the module name of the reference's extension.
+
+The reference imports a pybind11 module `flash_attn_legacy_cuda`
+(csrc/flash_attn_legacy.cpp:294-310 of sirCamp/flash-attention-legacy) exposing
+`forward`, `forward_varlen` and `backward`.  This module keeps those three
+functions with the same arguments and return conventions, and adds
+`backward_varlen` and `decode`.  All compute happens in the shared library's
+sm_100a kernels; there is no PyTorch or CPU fallback -- if the library is
+missing the import fails, and if the device is not a B200 the calls raise.
+
+PyTorch is used only to allocate outputs / workspaces and to hand over raw
+device pointers and the current stream.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libfal_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} not found. Build it with: python {os.path.join(_HERE, 'build.py')}"
+    )
+
+_lib = ctypes.CDLL(LIB_PATH)
+
+
+class _Strides(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_int64), ("head", ctypes.c_int64), ("row", ctypes.c_int64)]
+
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_f = ctypes.c_float
+_sp = ctypes.POINTER(_Strides)
+
+_lib.fal_strerror.restype = ctypes.c_char_p
+_lib.fal_strerror.argtypes = [_i]
+_lib.fal_last_cuda_error.restype = _i
+_lib.fal_last_cuda_error.argtypes = []
+_lib.fal_version.restype = ctypes.c_char_p
+_lib.fal_version.argtypes = []
+
+_lib.fal_fwd.restype = _i
+_lib.fal_fwd.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _sp, _sp, _sp, _sp, _f, _i,
+                         _vp, _vp]
+_lib.fal_fwd_varlen.restype = _i
+_lib.fal_fwd_varlen.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
+                                _sp, _sp, _sp, _sp, _f, _i, _vp, _vp]
+_lib.fal_bwd_workspace_bytes.restype = ctypes.c_size_t
+_lib.fal_bwd_workspace_bytes.argtypes = [_i, _i, _i, _i]
+_lib.fal_bwd.restype = _i
+_lib.fal_bwd.argtypes = [_vp] * 9 + [_i] * 6 + [_sp] * 8 + [_f, _i, _vp, ctypes.c_size_t, _vp, _vp]
+_lib.fal_bwd_varlen.restype = _i
+_lib.fal_bwd_varlen.argtypes = ([_vp] * 9 + [_vp, _vp] + [_i] * 8 + [_sp] * 8 +
+                                [_f, _i, _vp, ctypes.c_size_t, _vp, _vp])
+_lib.fal_decode_workspace_bytes.restype = ctypes.c_size_t
+_lib.fal_decode_workspace_bytes.argtypes = [_i, _i, _i, _i]
+_lib.fal_decode.restype = _i
+_lib.fal_decode.argtypes = [_vp, _vp, _vp, _sp, _sp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
+                            _vp, ctypes.c_size_t, _vp, _vp]
+
+__version__ = _lib.fal_version().decode()
+
+# One device status word per GPU; kernels set it non-zero if an internal wait ran out.
+_status = {}
+
+
+def _status_word(device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[idx] = t
+    return t
+
+
+def device_status(device=None):
+    """Synchronises and returns the device status word (0 = no kernel reported a problem)."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    device = torch.device(device)
+    t = _status_word(device)
+    torch.cuda.synchronize(device)
+    return int(t.item())
+
+
+def reset_device_status(device=None):
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    _status_word(torch.device(device)).zero_()
+
+
+def _check(rc):
+    if rc != 0:
+        msg = _lib.fal_strerror(rc).decode()
+        if rc == -4:
+            msg += f" (cudaError {_lib.fal_last_cuda_error()})"
+        raise RuntimeError(f"flash_attn_legacy_cuda: {msg}")
+
+
+def _bhn_strides(t):
+    """Strides of a [B, H, N, d] view."""
+    return _Strides(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _packed_strides(t):
+    """Strides of a [total, H, d] view."""
+    return _Strides(0, t.stride(1), t.stride(0))
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require_cuda_half(name, t, ndim):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be on CUDA")
+    if t.dtype != torch.float16:
+        raise RuntimeError(f"{name} must be float16")
+    if t.dim() != ndim:
+        raise RuntimeError(f"{name} must be {ndim}D")
+    if t.stride(-1) != 1:
+        raise RuntimeError(f"{name} must have a contiguous last dimension")
+
+
+def _same_device(*ts):
+    dev = ts[0].device
+    for t in ts:
+        if t is not None and t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+    if dev.index != torch.cuda.current_device():
+        raise RuntimeError("tensors must live on the current CUDA device")
+
+
+def forward(Q, K, V, softmax_scale, is_causal=False, out=None, lse=None):
+    """Batched forward.  Q [B,Hq,N,d], K/V [B,Hkv,N,d] fp16 -> [O [B,Hq,N,d] fp16, L [B,Hq,N] fp32].
+
+    Same contract as the reference's `forward` (csrc/flash_attn_legacy.cpp:42-98),
+    including its requirement that K and V have Q's sequence length.  `out` / `lse`
+    let a caller supply preallocated outputs.
+    """
+    _require_cuda_half("Q", Q, 4)
+    _require_cuda_half("K", K, 4)
+    _require_cuda_half("V", V, 4)
+    _same_device(Q, K, V)
+    B, Hq, N, d = Q.shape
+    Hkv = K.shape[1]
+    if K.shape != (B, Hkv, N, d) or V.shape != K.shape:
+        raise RuntimeError("K/V must be [B, H_kv, N, d] with Q's batch, sequence length and head_dim")
+    if Hq % Hkv != 0:
+        raise RuntimeError("H_q must be divisible by H_kv")
+    O = torch.empty((B, Hq, N, d), dtype=torch.float16, device=Q.device) if out is None else out
+    L = torch.empty((B, Hq, N), dtype=torch.float32, device=Q.device) if lse is None else lse
+    _check(_lib.fal_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), L.data_ptr(),
+                        B, Hq, Hkv, N, N, d,
+                        _bhn_strides(Q), _bhn_strides(K), _bhn_strides(V), _bhn_strides(O),
+                        float(softmax_scale), int(bool(is_causal)),
+                        _status_word(Q.device).data_ptr(), _stream(Q)))
+    return [O, L]
+
+
+def forward_rect(Q, K, V, softmax_scale, is_causal=False):
+    """Forward with seqlen_k != seqlen_q allowed (top-left-aligned causal mask)."""
+    _require_cuda_half("Q", Q, 4)
+    _require_cuda_half("K", K, 4)
+    _require_cuda_half("V", V, 4)
+    _same_device(Q, K, V)
+    B, Hq, Nq, d = Q.shape
+    Hkv, Nk = K.shape[1], K.shape[2]
+    O = torch.empty((B, Hq, Nq, d), dtype=torch.float16, device=Q.device)
+    L = torch.empty((B, Hq, Nq), dtype=torch.float32, device=Q.device)
+    _check(_lib.fal_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), L.data_ptr(),
+                        B, Hq, Hkv, Nq, Nk, d,
+                        _bhn_strides(Q), _bhn_strides(K), _bhn_strides(V), _bhn_strides(O),
+                        float(softmax_scale), int(bool(is_causal)),
+                        _status_word(Q.device).data_ptr(), _stream(Q)))
+    return [O, L]
+
+
+def forward_varlen(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale,
+                   is_causal=False):
+    """Packed forward.  Q [total_q,Hq,d], K/V [total_k,Hkv,d] -> [O [total_q,Hq,d], L [total_q,Hq]].
+
+    Same contract as the reference's `forward_varlen` (csrc/flash_attn_legacy.cpp:193-290), but
+    cu_seqlens stay on the device: there is no device-to-host copy or synchronisation.
+    """
+    _require_cuda_half("Q", Q, 3)
+    _require_cuda_half("K", K, 3)
+    _require_cuda_half("V", V, 3)
+    _same_device(Q, K, V, cu_seqlens_q, cu_seqlens_k)
+    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32:
+        raise RuntimeError("cu_seqlens must be int32")
+    total_q, Hq, d = Q.shape
+    total_k, Hkv = K.shape[0], K.shape[1]
+    num_seqs = cu_seqlens_q.numel() - 1
+    if cu_seqlens_k.numel() != num_seqs + 1:
+        raise RuntimeError("cu_seqlens_q and cu_seqlens_k must have the same length")
+    if Hq % Hkv != 0:
+        raise RuntimeError("H_q must be divisible by H_kv")
+    O = torch.empty((total_q, Hq, d), dtype=torch.float16, device=Q.device)
+    L = torch.empty((total_q, Hq), dtype=torch.float32, device=Q.device)
+    _check(_lib.fal_fwd_varlen(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), L.data_ptr(),
+                               cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), num_seqs,
+                               total_q, total_k, int(max_seqlen_q), int(max_seqlen_k), Hq, Hkv, d,
+                               _packed_strides(Q), _packed_strides(K), _packed_strides(V),
+                               _packed_strides(O), float(softmax_scale), int(bool(is_causal)),
+                               _status_word(Q.device).data_ptr(), _stream(Q)))
+    return [O, L]
+
+
+def backward(dO, Q, K, V, O, L, softmax_scale, is_causal=False):
+    """Batched backward -> [dQ [B,Hq,N,d], dK [B,Hkv,N,d], dV [B,Hkv,N,d]] fp16.
+
+    Same contract as the reference's `backward` (csrc/flash_attn_legacy.cpp:105-186).
+    """
+    for name, t in (("dO", dO), ("Q", Q), ("K", K), ("V", V), ("O", O)):
+        _require_cuda_half(name, t, 4)
+    _same_device(dO, Q, K, V, O, L)
+    B, Hq, Nq, d = Q.shape
+    Hkv, Nk = K.shape[1], K.shape[2]
+    if dO.shape != Q.shape or O.shape != Q.shape:
+        raise RuntimeError("dO and O must have Q's shape")
+    if L.dtype != torch.float32 or tuple(L.shape) != (B, Hq, Nq) or not L.is_contiguous():
+        raise RuntimeError("L must be contiguous float32 [B, H_q, N]")
+    dQ = torch.empty((B, Hq, Nq, d), dtype=torch.float16, device=Q.device)
+    dK = torch.empty((B, Hkv, Nk, d), dtype=torch.float16, device=Q.device)
+    dV = torch.empty((B, Hkv, Nk, d), dtype=torch.float16, device=Q.device)
+    nbytes = _lib.fal_bwd_workspace_bytes(B, Hq, Nq, d)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device)
+    _check(_lib.fal_bwd(dO.data_ptr(), Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(),
+                        L.data_ptr(), dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(),
+                        B, Hq, Hkv, Nq, Nk, d,
+                        _bhn_strides(dO), _bhn_strides(Q), _bhn_strides(K), _bhn_strides(V),
+                        _bhn_strides(O), _bhn_strides(dQ), _bhn_strides(dK), _bhn_strides(dV),
+                        float(softmax_scale), int(bool(is_causal)),
+                        ws.data_ptr(), nbytes, _status_word(Q.device).data_ptr(), _stream(Q)))
+    return [dQ, dK, dV]
+
+
+def backward_varlen(dO, Q, K, V, O, L, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                    softmax_scale, is_causal=False):
+    """Packed backward in one native call -> [dQ [total_q,Hq,d], dK, dV [total_k,Hkv,d]] fp16.
+
+    Replaces the per-sequence Python loop of the reference
+    (flash_attn_legacy/flash_attn.py:133-157).
+    """
+    for name, t in (("dO", dO), ("Q", Q), ("K", K), ("V", V), ("O", O)):
+        _require_cuda_half(name, t, 3)
+    _same_device(dO, Q, K, V, O, L, cu_seqlens_q, cu_seqlens_k)
+    total_q, Hq, d = Q.shape
+    total_k, Hkv = K.shape[0], K.shape[1]
+    num_seqs = cu_seqlens_q.numel() - 1
+    if L.dtype != torch.float32 or tuple(L.shape) != (total_q, Hq) or not L.is_contiguous():
+        raise RuntimeError("L must be contiguous float32 [total_q, H_q]")
+    dQ = torch.empty((total_q, Hq, d), dtype=torch.float16, device=Q.device)
+    dK = torch.empty((total_k, Hkv, d), dtype=torch.float16, device=Q.device)
+    dV = torch.empty((total_k, Hkv, d), dtype=torch.float16, device=Q.device)
+    nbytes = _lib.fal_bwd_workspace_bytes(1, Hq, total_q, d)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device)
+    _check(_lib.fal_bwd_varlen(dO.data_ptr(), Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(),
+                               L.data_ptr(), dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(),
+                               cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), num_seqs,
+                               total_q, total_k, int(max_seqlen_q), int(max_seqlen_k), Hq, Hkv, d,
+                               _packed_strides(dO), _packed_strides(Q), _packed_strides(K),
+                               _packed_strides(V), _packed_strides(O), _packed_strides(dQ),
+                               _packed_strides(dK), _packed_strides(dV),
+                               float(softmax_scale), int(bool(is_causal)),
+                               ws.data_ptr(), nbytes, _status_word(Q.device).data_ptr(), _stream(Q)))
+    return [dQ, dK, dV]
+
+
+_decode_ws = {}
+
+
+def decode(q, k_cache, v_cache, cache_seqlens, softmax_scale, k_new=None, v_new=None,
+           cache_layout="bshd", return_lse=False, out=None):
+    """Single-token decode.  q [B,Hq,d]; caches [B,S,Hkv,d] ("bshd") or [B,Hkv,S,d] ("bhsd").
+
+    If k_new / v_new ([B,Hkv,d]) are given they are written into the caches at position
+    cache_seqlens[b] first.  Returns O [B,Hq,d] fp16 (and LSE [B,Hq] fp32 if asked).
+    """
+    _require_cuda_half("q", q, 3)
+    _require_cuda_half("k_cache", k_cache, 4)
+    _require_cuda_half("v_cache", v_cache, 4)
+    _same_device(q, k_cache, v_cache, cache_seqlens, k_new, v_new)
+    if not q.is_contiguous():
+        raise RuntimeError("q must be contiguous [B, H_q, d]")
+    if cache_seqlens.dtype != torch.int32:
+        raise RuntimeError("cache_seqlens must be int32")
+    B, Hq, d = q.shape
+    if cache_layout == "bshd":
+        S, Hkv = k_cache.shape[1], k_cache.shape[2]
+        ks = _Strides(k_cache.stride(0), k_cache.stride(2), k_cache.stride(1))
+        vs = _Strides(v_cache.stride(0), v_cache.stride(2), v_cache.stride(1))
+    elif cache_layout == "bhsd":
+        Hkv, S = k_cache.shape[1], k_cache.shape[2]
+        ks = _Strides(k_cache.stride(0), k_cache.stride(1), k_cache.stride(2))
+        vs = _Strides(v_cache.stride(0), v_cache.stride(1), v_cache.stride(2))
+    else:
+        raise ValueError("cache_layout must be 'bshd' or 'bhsd'")
+    if k_new is not None:
+        _require_cuda_half("k_new", k_new, 3)
+        _require_cuda_half("v_new", v_new, 3)
+        if not (k_new.is_contiguous() and v_new.is_contiguous()):
+            raise RuntimeError("k_new / v_new must be contiguous [B, H_kv, d]")
+    o = torch.empty((B, Hq, d), dtype=torch.float16, device=q.device) if out is None else out
+    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if return_lse else None
+    nbytes = _lib.fal_decode_workspace_bytes(B, Hq, S, d)
+    key = (q.device.index, nbytes)
+    ws = _decode_ws.get(key)
+    if ws is None:
+        # Kept across calls: decode loops call this once per generated token.
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        _decode_ws.clear()
+        _decode_ws[key] = ws
+    _check(_lib.fal_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ks, vs,
+                           cache_seqlens.data_ptr(),
+                           k_new.data_ptr() if k_new is not None else None,
+                           v_new.data_ptr() if v_new is not None else None,
+                           o.data_ptr(), lse.data_ptr() if lse is not None else None,
+                           B, Hq, Hkv, S, d, float(softmax_scale), ws.data_ptr(), nbytes,
+                           _status_word(q.device).data_ptr(), _stream(q)))
+    return (o, lse) if return_lse else o

@@ -1,0 +1,160 @@
+/*
+ * C ABI of the B200 (sm_100a) attention library: the native boundary behind
+ * the Python module `flash_attn_legacy_cuda`.
+ *
+ * It replaces the pybind11/torch extension of sirCamp/flash-attention-legacy
+ * (csrc/flash_attn_legacy.cpp): each entry point below names the reference
+ * function it stands in for.  Differences by design:
+ *   - plain pointers and sizes, no torch types; the caller owns every buffer,
+ *     outputs and workspaces included -- the library never allocates or frees
+ *     device memory;
+ *   - element strides are passed per tensor, so [B,H,N,d] and [B,N,H,d] views
+ *     work without copies (head_dim must be contiguous, rows 16-byte aligned);
+ *   - functions return 0 or a negative fal_error code and never throw, print
+ *     or exit; fal_strerror() names a code;
+ *   - launches are asynchronous on the caller's stream, with the caller's
+ *     device current; no call synchronises the device;
+ *   - `status` is an optional device int the kernels set non-zero if an
+ *     internal wait ran out (a bug indicator); read it after synchronising.
+ *
+ * All tensor data is fp16, statistics are fp32, index data int32.
+ * Supported head_dim: 64 and 128.
+ */
+#ifndef FAL_B200_H_
+#define FAL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define FAL_API __attribute__((visibility("default")))
+#else
+#define FAL_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum fal_error {
+  FAL_OK = 0,
+  FAL_ERR_INVALID_ARGUMENT = -1,  /* shape, stride, alignment or null-pointer problem */
+  FAL_ERR_UNSUPPORTED_HEAD_DIM = -2,
+  FAL_ERR_WORKSPACE_TOO_SMALL = -3,
+  FAL_ERR_CUDA = -4,        /* a CUDA runtime call failed; see fal_last_cuda_error() */
+  FAL_ERR_TENSOR_MAP = -5,  /* the driver rejected a TMA descriptor */
+  FAL_ERR_UNSUPPORTED_DEVICE = -6 /* not compute capability 10.x */
+};
+
+/* Human-readable name of a fal_error code. */
+FAL_API const char* fal_strerror(int code);
+
+/* cudaError_t value of the last failed CUDA call on this host thread (0 if none). */
+FAL_API int fal_last_cuda_error(void);
+
+/* Library version, "major.minor.patch". */
+FAL_API const char* fal_version(void);
+
+/* Element strides of a tensor addressed as [batch, head, row, head_dim]. */
+typedef struct fal_strides {
+  int64_t batch;
+  int64_t head;
+  int64_t row;
+} fal_strides;
+
+/*
+ * Batched forward.  Stands in for flash_attn_forward
+ * (csrc/flash_attn_legacy.cpp:42-98; bound as `forward` at :295-298).
+ *   q [B,Hq,Nq,d], k/v [B,Hkv,Nk,d], o [B,Hq,Nq,d] fp16; lse [B,Hq,Nq] fp32 contiguous.
+ *   Causal masking is top-left aligned: key j is visible to query i iff j <= i.
+ *   lse = natural-log sum-exp of the scaled, masked scores.
+ */
+FAL_API int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+            int batch, int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
+            const fal_strides* q_strides, const fal_strides* k_strides,
+            const fal_strides* v_strides, const fal_strides* o_strides,
+            float softmax_scale, int is_causal, int* status, void* stream);
+
+/*
+ * Packed (variable-length) forward.  Stands in for flash_attn_forward_varlen
+ * (csrc/flash_attn_legacy.cpp:193-290; bound as `forward_varlen` at :299-304).
+ *   q [total_q,Hq,d], k/v [total_k,Hkv,d], o [total_q,Hq,d]; lse [total_q,Hq] contiguous.
+ *   cu_seqlens_* are device int32 [num_seqs+1]; no host copy of them is made.
+ *   Strides: `row` is the token stride, `head` the head stride, `batch` is ignored.
+ */
+FAL_API int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* lse,
+                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int num_seqs,
+                   int total_q, int total_k, int max_seqlen_q, int max_seqlen_k,
+                   int heads_q, int heads_kv, int head_dim,
+                   const fal_strides* q_strides, const fal_strides* k_strides,
+                   const fal_strides* v_strides, const fal_strides* o_strides,
+                   float softmax_scale, int is_causal, int* status, void* stream);
+
+/*
+ * Bytes of scratch the backward needs (fp32 dQ accumulator and the
+ * rowsum(dO*O) vector).  `rows` is seqlen_q (batched) or total_q (packed, with
+ * batch = 1).
+ */
+FAL_API size_t fal_bwd_workspace_bytes(int batch, int heads_q, int rows, int head_dim);
+
+/*
+ * Batched backward.  Stands in for flash_attn_backward
+ * (csrc/flash_attn_legacy.cpp:105-186; bound as `backward` at :305-309), which
+ * runs precompute_D, the dK/dV/dQ kernel and the fp32->fp16 dQ cast.
+ *   d_out, q, o, dq [B,Hq,Nq,d]; k, v, dk, dv [B,Hkv,Nk,d]; lse [B,Hq,Nq] contiguous.
+ *   dQ is accumulated with fp32 reductions whose order is not fixed, so dq can
+ *   differ in the last bit between runs (the reference's atomics do the same).
+ */
+FAL_API int fal_bwd(const void* d_out, const void* q, const void* k, const void* v, const void* o,
+            const float* lse, void* dq, void* dk, void* dv,
+            int batch, int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
+            const fal_strides* do_strides, const fal_strides* q_strides,
+            const fal_strides* k_strides, const fal_strides* v_strides,
+            const fal_strides* o_strides, const fal_strides* dq_strides,
+            const fal_strides* dk_strides, const fal_strides* dv_strides,
+            float softmax_scale, int is_causal,
+            void* workspace, size_t workspace_bytes, int* status, void* stream);
+
+/*
+ * Packed backward in one launch sequence.  Replaces the per-sequence Python
+ * loop of FlashAttnVarlenFunc.backward (flash_attn_legacy/flash_attn.py:119-159).
+ *   lse [total_q,Hq] contiguous, as written by fal_fwd_varlen.
+ */
+FAL_API int fal_bwd_varlen(const void* d_out, const void* q, const void* k, const void* v, const void* o,
+                   const float* lse, void* dq, void* dk, void* dv,
+                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int num_seqs,
+                   int total_q, int total_k, int max_seqlen_q, int max_seqlen_k,
+                   int heads_q, int heads_kv, int head_dim,
+                   const fal_strides* do_strides, const fal_strides* q_strides,
+                   const fal_strides* k_strides, const fal_strides* v_strides,
+                   const fal_strides* o_strides, const fal_strides* dq_strides,
+                   const fal_strides* dk_strides, const fal_strides* dv_strides,
+                   float softmax_scale, int is_causal,
+                   void* workspace, size_t workspace_bytes, int* status, void* stream);
+
+/* Bytes of scratch fal_decode needs for its split-K partial results. */
+FAL_API size_t fal_decode_workspace_bytes(int batch, int heads_q, int capacity, int head_dim);
+
+/*
+ * Single-token decode against a KV cache (q_len = 1): split-K streaming pass
+ * plus a log-sum-exp combine.  Stands in for the eager fallback branch of the
+ * reference's attention hook (flash_attn_legacy/integrations.py:77-98): no
+ * causal mask, GQA by head mapping, softmax over the cached positions.
+ *   q, o [B,Hq,d] contiguous; caches addressed by strides as [B,Hkv,position,d];
+ *   cache_seqlens device int32 [B] (positions already valid); if k_new/v_new
+ *   ([B,Hkv,d] contiguous) are given they are first written at position
+ *   cache_seqlens[b] and attended to as well.  lse [B,Hq] is optional.
+ */
+FAL_API int fal_decode(const void* q, void* k_cache, void* v_cache,
+               const fal_strides* k_strides, const fal_strides* v_strides,
+               const int32_t* cache_seqlens, const void* k_new, const void* v_new,
+               void* o, float* lse,
+               int batch, int heads_q, int heads_kv, int capacity, int head_dim,
+               float softmax_scale, void* workspace, size_t workspace_bytes,
+               int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FAL_B200_H_ */
