@@ -1,0 +1,383 @@
+"""Headline benchmark: causal GQA attention forward + backward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (one "step" = one forward + one backward over one batch of synthetic input):
+    B=4, Hq=32, Hkv=8, N=4096, d=128, causal, fp16, scale 1/sqrt(128); q, k, v, dO iid N(0,1).
+Algorithmic work per step = 3.5 * (4*B*Hq*N*N*d / 2) = 1.924e12 FLOP (forward 2 GEMMs,
+backward 5; the causal half is counted once; recompute and softmax are not counted).
+
+Prints ONE JSON line.  `value` is whole-job TFLOP/s with inputs resident in HBM (kernel
+path through the C-ABI with preallocated outputs); `e2e` is the same metric through the
+public autograd API from pinned HOST buffers, host<->device copies inside the timed
+region.  With --gpus N each rank (one process per GPU) runs the same workload on its own
+shard of independent (batch, head-group) units -- no collective on the data path -- and
+the time is the maximum over ranks.
+
+--impl reference times the reference's CPU math path (the fp32 naive attention its
+tests use, restated in oracle/attention_oracle.py) on the host cores, on a bounded
+sample of the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "flash-attention-legacy_b200"))
+
+WORKLOAD = dict(B=4, Hq=32, Hkv=8, N=4096, d=128, causal=True)
+WORKLOAD_NAME = "gqa_fwd_bwd_B4_Hq32_Hkv8_N4096_d128_causal_fp16"
+METRIC = "attn_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def step_flops(w=WORKLOAD):
+    fwd = 4.0 * w["B"] * w["Hq"] * w["N"] * w["N"] * w["d"] * (0.5 if w["causal"] else 1.0)
+    return fwd, 2.5 * fwd
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            m = json.load(f)
+        return {"bf16_tflops": m.get("bf16_tflops"), "bf16_tflops_sustained": m.get("bf16_tflops_sustained"),
+                "hbm_gbs": m.get("hbm_gbs"), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # Samples taken while the GPU was actually busy: the upper half of the observed clocks.
+        sm.sort()
+        busy = sm[len(sm) // 2:] if sm else []
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return rank, world, local, dist
+    torch.cuda.set_device(0)
+    return 0, 1, 0, None
+
+
+def cpu_baseline_sample(num_slices, threads=None):
+    """Times the oracle's forward + backward on `num_slices` (batch, kv-head-group) slices.
+
+    One slice = 1 batch entry x 4 query heads x 1 KV head x N=4096 x d=128 (1/32 of a step).
+    Returns (tflops, seconds, threads).
+    """
+    sys.path.insert(0, ROOT)
+    from oracle import attention_oracle as orc
+    w = WORKLOAD
+    group = w["Hq"] // w["Hkv"]
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(1, group, w["N"], w["d"], generator=g).half()
+    k = torch.randn(1, 1, w["N"], w["d"], generator=g).half()
+    v = torch.randn(1, 1, w["N"], w["d"], generator=g).half()
+    do = torch.randn(1, group, w["N"], w["d"], generator=g).half()
+    scale = 1.0 / math.sqrt(w["d"])
+    fwd, bwd = step_flops()
+    slice_flops = (fwd + bwd) / (w["B"] * w["Hkv"])
+    t0 = time.perf_counter()
+    for _ in range(num_slices):
+        orc.attention_fwd(q, k, v, scale, w["causal"])
+        orc.attention_bwd(q, k, v, do, scale, w["causal"])
+    dt = time.perf_counter() - t0
+    return slice_flops * num_slices / dt / 1e12, dt, torch.get_num_threads()
+
+
+def run_reference(args):
+    """Reference arm: the reference's fp32 CPU math path, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    slices_per_step = 1
+    for _ in range(min(args.warmup, 1)):
+        cpu_baseline_sample(1)
+    t_total, tf_list = 0.0, []
+    for _ in range(args.steps):
+        tf, dt, threads = cpu_baseline_sample(slices_per_step)
+        tf_list.append(tf)
+        t_total += dt
+    value = sum(tf_list) / len(tf_list)
+    sample = (f"{slices_per_step} of 32 (batch, kv-head-group) slices per step: 4 query heads x 1 KV head, "
+              "N=4096, d=128, fp32 forward + closed-form backward")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD_NAME, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def run_decode_extra(ext, peaks, steps=256):
+    """Secondary metric: KV-cache split-K decode with appends, B=64 Hq=32 Hkv=8 d=128, cache 32768."""
+    B, Hq, Hkv, S, d = 64, 32, 8, 32768, 128
+    g = torch.Generator(device="cuda").manual_seed(3)
+    kc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
+    vc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
+    lens0 = torch.randint(1024, S - steps + 1, (B,), device="cuda", generator=g).to(torch.int32)
+    q = torch.randn(steps, B, Hq, d, device="cuda", dtype=torch.float16, generator=g)
+    kn = torch.randn(steps, B, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
+    vn = torch.randn(steps, B, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
+    out = torch.empty(B, Hq, d, device="cuda", dtype=torch.float16)
+    scale = 1.0 / math.sqrt(d)
+    lens = lens0.clone()
+    for i in range(3):
+        ext.decode(q[i], kc, vc, lens, scale, kn[i], vn[i], out=out)
+    torch.cuda.synchronize()
+    lens = lens0.clone()
+    ext.profile_read(ext.KERNEL_DECODE_SPLITK)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        ext.decode(q[i], kc, vc, lens, scale, kn[i], vn[i], out=out)
+        lens += 1
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    k_ms, k_n = ext.profile_read(ext.KERNEL_DECODE_SPLITK)
+    mean_len = lens0.float().mean().item() + (steps + 1) / 2.0
+    kv_bytes = mean_len * B * Hkv * d * 2 * 2  # K and V, fp16, read once per KV head
+    res = {"workload": "decode_B64_Hq32_Hkv8_d128_cache32768_256steps_with_append",
+           "ms_per_step": ms, "kv_gbs": kv_bytes / ms / 1e6,
+           "frac_of_hbm_peak": kv_bytes / ms / 1e6 / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
+           "launches_per_step": 3}
+    if k_n:
+        res["splitk_kernel_ms"] = k_ms / k_n
+        res["splitk_kernel_gbs"] = kv_bytes / (k_ms / k_n) / 1e6
+    del kc, vc
+    torch.cuda.empty_cache()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and decode extras")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
+    rank, world, local, dist = dist_setup(args.gpus)
+    import flash_attn_legacy_cuda as ext
+    import flash_attn_legacy as fal
+
+    w = WORKLOAD
+    B, Hq, Hkv, N, d, causal = w["B"], w["Hq"], w["Hkv"], w["N"], w["d"], w["causal"]
+    scale = 1.0 / math.sqrt(d)
+    dev = torch.device("cuda", local)
+    gen = torch.Generator(device="cuda").manual_seed(1 + rank)
+    q = torch.randn(B, Hq, N, d, device=dev, generator=gen).half()
+    k = torch.randn(B, Hkv, N, d, device=dev, generator=gen).half()
+    v = torch.randn(B, Hkv, N, d, device=dev, generator=gen).half()
+    do = torch.randn(B, Hq, N, d, device=dev, generator=gen).half()
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, N, device=dev, dtype=torch.float32)
+    grads = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    ws = torch.empty(ext.backward_workspace_bytes(B, Hq, N, d), dtype=torch.uint8, device=dev)
+    fwd_flops, bwd_flops = step_flops()
+
+    def step():
+        ext.forward(q, k, v, scale, causal, out=o, lse=lse)
+        ext.backward(do, q, k, v, o, lse, scale, causal, out=grads, workspace=ws)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- device-resident timing ----------------------------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ext.profile_enable(True)
+    ext.profile_read(ext.KERNEL_FWD)
+    ext.profile_read(ext.KERNEL_BWD)
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    time.sleep(0.2)
+    clocks = sampler.stop()
+    fwd_ms, fwd_n = ext.profile_read(ext.KERNEL_FWD)
+    bwd_ms, bwd_n = ext.profile_read(ext.KERNEL_BWD)
+    ext.profile_enable(False)
+    if dist is not None:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = t.item()
+    ms_step = ms_total / args.steps
+    value = world * (fwd_flops + bwd_flops) / (ms_step * 1e-3) / 1e12
+
+    # ---------------- end to end from pinned host memory ------------------------
+    hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
+    h_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v)]
+    dq_, dk_, dv_ = q, k, v  # device staging buffers reused as H2D destinations
+
+    def e2e_step():
+        dq_.copy_(hq, non_blocking=True)
+        dk_.copy_(hk, non_blocking=True)
+        dv_.copy_(hv, non_blocking=True)
+        gdo = do.copy_(hdo, non_blocking=True)
+        qa, ka, va = dq_.detach().requires_grad_(True), dk_.detach().requires_grad_(True), dv_.detach().requires_grad_(True)
+        out = fal.flash_attention(qa, ka, va, softmax_scale=scale, is_causal=causal)
+        out.backward(gdo)
+        h_out[0].copy_(qa.grad, non_blocking=True)
+        h_out[1].copy_(ka.grad, non_blocking=True)
+        h_out[2].copy_(va.grad, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e_ms /= e2e_steps
+    e2e_value = world * (fwd_flops + bwd_flops) / (e2e_ms * 1e-3) / 1e12
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
+    d2h = sum(t.numel() * t.element_size() for t in h_out)
+    status = ext.device_status()
+
+    # ---------------- roofline of the dominant kernel (backward main kernel) -----------
+    peaks = measured_peaks()
+    peak_tf = peaks["bf16_tflops"]
+    roofline = None
+    extra = {}
+    if bwd_n:
+        bwd_kernel_ms = bwd_ms / bwd_n
+        achieved = bwd_flops / (bwd_kernel_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "fal_bwd_kernel<128,causal>", "achieved": achieved,
+                    "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "traffic": None,
+                    "kernel_ms": bwd_kernel_ms, "frac_of_nominal_2250": achieved / 2250.0}
+    if fwd_n:
+        fwd_kernel_ms = fwd_ms / fwd_n
+        fa = fwd_flops / (fwd_kernel_ms * 1e-3) / 1e12
+        extra["fwd_kernel"] = {"kernel": "fal_fwd_kernel<128,causal>", "kernel_ms": fwd_kernel_ms,
+                               "achieved_tflops": fa, "frac_of_measured_peak": fa / peak_tf,
+                               "frac_of_nominal_2250": fa / 2250.0}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        tf, dt, threads = cpu_baseline_sample(6)
+        cpu_baseline = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
+                        "sample": f"6 of 32 (batch, kv-head-group) slices of the same workload, {dt:.1f} s, "
+                                  f"fp32 oracle forward + backward, os.cpu_count()={os.cpu_count()}"}
+        try:
+            extra["decode"] = run_decode_extra(ext, peaks)
+        except RuntimeError as e:  # e.g. not enough free memory next to another job
+            extra["decode"] = {"error": str(e)[:200]}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD_NAME, "global_batch": B * world, "per_gpu": w,
+                       "l2_policy": "inputs+outputs per step (about 1 GB) exceed the 126 MB L2",
+                       "parallelism": f"{world} x independent (batch, head-group) shards, no collective"},
+            "per_gpu_tflops": value / world,
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": 4 * args.steps,
+            "launches_per_step": {"fal_fwd_kernel": 1, "fal_bwd_prep_kernel": 1, "fal_bwd_kernel": 1,
+                                  "fal_bwd_post_kernel": 1, "cudaMemsetAsync": 1},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": clocks,
+            "device_status": status, "extra": extra,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <mutex>
+#include <vector>
 
 #include "fal_common.h"
 #include "fal_launch.h"
@@ -113,6 +114,37 @@ BwdWorkspace bwd_workspace_layout(int batch, int heads_q, int rows, int head_dim
 
 constexpr int kDecodeSplitLen = 1024;
 
+// ---------------------------------------------------------------------------
+// Optional event timing around the main kernels (off by default).
+// ---------------------------------------------------------------------------
+struct KernelTimer {
+  static constexpr int kKinds = 3;
+  static constexpr int kMaxRecords = 8192;
+  std::mutex mu;
+  bool enabled = false;
+  struct Rec { cudaEvent_t a, b; };
+  std::vector<Rec> recs[kKinds];
+
+  // Returns the index of a new record with its start event recorded, or -1.
+  int begin(int kind, cudaStream_t st) {
+    std::lock_guard<std::mutex> g(mu);
+    if (!enabled || static_cast<int>(recs[kind].size()) >= kMaxRecords) return -1;
+    Rec r;
+    if (cudaEventCreate(&r.a) != cudaSuccess) return -1;
+    if (cudaEventCreate(&r.b) != cudaSuccess) { cudaEventDestroy(r.a); return -1; }
+    cudaEventRecord(r.a, st);
+    recs[kind].push_back(r);
+    return static_cast<int>(recs[kind].size()) - 1;
+  }
+  void end(int kind, int idx, cudaStream_t st) {
+    if (idx < 0) return;
+    std::lock_guard<std::mutex> g(mu);
+    if (idx < static_cast<int>(recs[kind].size())) cudaEventRecord(recs[kind][idx].b, st);
+  }
+};
+KernelTimer g_timer;
+
+
 }  // namespace
 
 extern "C" {
@@ -178,8 +210,10 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   p.status = status;
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
-  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid),
-                                  static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
+  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
 
@@ -233,8 +267,10 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   p.status = status;
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
-  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid),
-                                  static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
+  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
 
@@ -341,7 +377,9 @@ int run_bwd(const BwdCall& c) {
   p.status = c.status;
   const int64_t grid = static_cast<int64_t>(p.num_kvblk) * c.batch * c.heads_kv;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
+  const int rec = g_timer.begin(FAL_KERNEL_BWD, c.stream);
   e = fal::launch_bwd(c.head_dim, c.causal != 0, tq, tk, tv, tdo, p, static_cast<int>(grid), c.stream);
+  g_timer.end(FAL_KERNEL_BWD, rec, c.stream);
   if (e != cudaSuccess) return cuda_fail(e);
 
   fal::BwdPostParams po{};
@@ -478,10 +516,46 @@ int fal_decode(const void* q, void* k_cache, void* v_cache, const fal_strides* k
     e = fal::launch_decode_append(p, st);
     if (e != cudaSuccess) return cuda_fail(e);
   }
+  const int rec = g_timer.begin(FAL_KERNEL_DECODE_SPLITK, st);
   e = fal::launch_decode_splitk(p, st);
+  g_timer.end(FAL_KERNEL_DECODE_SPLITK, rec, st);
   if (e != cudaSuccess) return cuda_fail(e);
   e = fal::launch_decode_combine(p, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+int fal_profile_enable(int on) {
+  std::lock_guard<std::mutex> g(g_timer.mu);
+  g_timer.enabled = on != 0;
+  return FAL_OK;
+}
+
+int fal_profile_read(int kind, double* total_ms, int* launches) {
+  if (kind < 0 || kind >= KernelTimer::kKinds || !total_ms || !launches) return FAL_ERR_INVALID_ARGUMENT;
+  std::vector<KernelTimer::Rec> recs;
+  {
+    std::lock_guard<std::mutex> g(g_timer.mu);
+    recs.swap(g_timer.recs[kind]);
+  }
+  double sum = 0.0;
+  int n = 0;
+  int rc = FAL_OK;
+  for (auto& r : recs) {
+    float ms = 0.f;
+    cudaError_t e = cudaEventSynchronize(r.b);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, r.a, r.b);
+    if (e == cudaSuccess) {
+      sum += ms;
+      ++n;
+    } else {
+      rc = cuda_fail(e);
+    }
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  *total_ms = sum;
+  *launches = n;
+  return rc;
 }
 
 }  // extern "C"

@@ -1,0 +1,281 @@
+"""Autograd operators and modules: the Python operator surface of flash_attn_legacy on B200.
+
+Drop-in for flash_attn_legacy/flash_attn.py of sirCamp/flash-attention-legacy:
+`flash_attention`, `flash_attn_varlen_func`, `FlashAttentionFunc`,
+`FlashAttnVarlenFunc`, `FlashAttention`, `FlashMultiHeadAttention` keep their
+names, argument meaning, assertions and return conventions.  Added:
+`flash_attn_with_kvcache` (single-token decode against a KV cache) -- the
+reference has no such entry; its HF hook falls back to eager attention there.
+
+All compute is in the sm_100a kernels reached through `flash_attn_legacy_cuda`.
+"""
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.autograd import Function
+
+try:
+    import flash_attn_legacy_cuda
+except ImportError as e:  # same failure mode as the reference: no extension, no package
+    raise ImportError(
+        "flash_attn_legacy_cuda (the B200 attention library binding) could not be imported. "
+        "Build it with: python flash-attention-legacy_b200/build.py\n"
+        f"Original error: {e}"
+    )
+
+SUPPORTED_HEAD_DIMS = (32, 64, 96, 128, 256)
+_NATIVE_HEAD_DIMS = (64, 128)
+
+
+def _native_head_dim(d: int) -> int:
+    """Head dim the kernels run at: 32 -> 64 and 96 -> 128 by zero padding (exact: padded
+    columns add 0 to every score and produce output columns that are sliced away)."""
+    if d in _NATIVE_HEAD_DIMS:
+        return d
+    if d == 32:
+        return 64
+    if d == 96:
+        return 128
+    raise NotImplementedError(
+        f"head_dim={d} is accepted by the reference but not built for B200 yet (64 and 128 are "
+        "native; 32 and 96 run zero-padded)"
+    )
+
+
+class FlashAttentionFunc(Function):
+    """q [B,Hq,N,d], k/v [B,Hkv,N,d] fp16 -> o [B,Hq,N,d]; Hq % Hkv == 0 (GQA / MQA).
+
+    Mirrors FlashAttentionFunc of the reference (flash_attn.py:22-56).
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, is_causal):
+        assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
+        assert k.dtype == torch.float16 and v.dtype == torch.float16
+        assert q.is_cuda and q.dim() == 4
+        d = q.shape[-1]
+        assert d in _NATIVE_HEAD_DIMS, f"native head_dim must be 64 or 128, got {d}"
+        h_q, h_kv = q.shape[1], k.shape[1]
+        assert h_q % h_kv == 0, f"H_q ({h_q}) must be divisible by H_kv ({h_kv})"
+
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = flash_attn_legacy_cuda.forward(q, k, v, softmax_scale, is_causal)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.softmax_scale = softmax_scale
+        ctx.is_causal = is_causal
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = flash_attn_legacy_cuda.backward(
+            grad_output.contiguous(), q, k, v, o, lse, ctx.softmax_scale, ctx.is_causal
+        )
+        return dq, dk, dv, None, None
+
+
+def _pad_last(x, d_to):
+    return x if x.shape[-1] == d_to else F.pad(x, (0, d_to - x.shape[-1]))
+
+
+def flash_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: Optional[float] = None,
+    is_causal: bool = False,
+) -> torch.Tensor:
+    """softmax(q k^T * scale [+ causal mask]) v, O(N) memory, fp16 in / fp16 out.
+
+    q [B,Hq,N,d]; k, v [B,Hkv,N,d] with Hq divisible by Hkv (MHA, GQA, MQA).
+    `softmax_scale` defaults to 1/sqrt(d).  The causal mask hides key j from query i
+    when j > i.  Same contract as the reference's flash_attention (flash_attn.py:59-87).
+    """
+    assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
+    d = q.shape[-1]
+    assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(d)
+    dn = _native_head_dim(d)
+    if dn != d:
+        out = FlashAttentionFunc.apply(_pad_last(q, dn), _pad_last(k, dn), _pad_last(v, dn),
+                                       softmax_scale, is_causal)
+        return out[..., :d]
+    return FlashAttentionFunc.apply(q, k, v, softmax_scale, is_causal)
+
+
+class FlashAttnVarlenFunc(Function):
+    """Packed-sequence attention; forward AND backward are single native calls.
+
+    Mirrors FlashAttnVarlenFunc of the reference (flash_attn.py:90-159); the reference's
+    backward loops over sequences in Python with four host syncs each, this one does not.
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                softmax_scale, is_causal):
+        assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
+        assert q.is_cuda and q.dim() == 3
+        d = q.shape[-1]
+        assert d in _NATIVE_HEAD_DIMS, f"native head_dim must be 64 or 128, got {d}"
+
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        cu_seqlens_q = cu_seqlens_q.contiguous().to(torch.int32)
+        cu_seqlens_k = cu_seqlens_k.contiguous().to(torch.int32)
+        o, lse = flash_attn_legacy_cuda.forward_varlen(
+            q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, is_causal
+        )
+        ctx.save_for_backward(q, k, v, o, lse, cu_seqlens_q, cu_seqlens_k)
+        ctx.softmax_scale = softmax_scale
+        ctx.is_causal = is_causal
+        ctx.max_seqlen_q = max_seqlen_q
+        ctx.max_seqlen_k = max_seqlen_k
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        q, k, v, o, lse, cu_q, cu_k = ctx.saved_tensors
+        dq, dk, dv = flash_attn_legacy_cuda.backward_varlen(
+            grad_output.contiguous(), q, k, v, o, lse, cu_q, cu_k,
+            ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.softmax_scale, ctx.is_causal,
+        )
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def flash_attn_varlen_func(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    softmax_scale: Optional[float] = None,
+    causal: bool = False,
+) -> torch.Tensor:
+    """Attention over sequences packed along the token axis (no padding).
+
+    q [total_q,H,d]; k, v [total_k,H_k,d]; cu_seqlens_* int32 [num_seqs+1] with the
+    cumulative lengths.  Returns [total_q,H,d].  Same contract as the reference's
+    flash_attn_varlen_func (flash_attn.py:162-220).  The causal mask is aligned to the
+    top-left corner of each sequence's score matrix (key j hidden when j > i), as in
+    the reference kernels (flash_attn_fwd_volta.cu:448-451).
+    """
+    assert q.dim() == 3, f"q must be [total, heads, d], got shape {q.shape}"
+    assert k.dim() == 3, f"k must be [total, heads_k, d], got shape {k.shape}"
+    assert v.dim() == 3, f"v must be [total, heads_k, d], got shape {v.shape}"
+    assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
+    d = q.shape[-1]
+    assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(d)
+    dn = _native_head_dim(d)
+    if dn != d:
+        out = FlashAttnVarlenFunc.apply(_pad_last(q, dn), _pad_last(k, dn), _pad_last(v, dn),
+                                        cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                                        softmax_scale, causal)
+        return out[..., :d]
+    return FlashAttnVarlenFunc.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                                     softmax_scale, causal)
+
+
+def flash_attn_with_kvcache(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    k: Optional[torch.Tensor] = None,
+    v: Optional[torch.Tensor] = None,
+    cache_seqlens: Optional[torch.Tensor] = None,
+    softmax_scale: Optional[float] = None,
+    cache_layout: str = "bshd",
+) -> torch.Tensor:
+    """One decode step: q [B,1,Hq,d] attends to the first cache_seqlens[b] cache positions.
+
+    Caches are [B,S,Hkv,d] (`cache_layout="bshd"`) or [B,Hkv,S,d] ("bhsd", HuggingFace).
+    If k, v ([B,1,Hkv,d]) are given they are written into the caches at position
+    cache_seqlens[b] first and attended to as well; `cache_seqlens` itself is not
+    modified.  No causal mask (q_len == 1), as in the reference hook's decode branch
+    (integrations.py:77-98), which this replaces with a split-K kernel.  Inference only.
+    """
+    assert q.dim() == 4 and q.shape[1] == 1, "q must be [B, 1, H_q, d]"
+    assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
+    b, _, hq, d = q.shape
+    assert d in _NATIVE_HEAD_DIMS, f"decode supports head_dim 64 and 128, got {d}"
+    seq_axis = 1 if cache_layout == "bshd" else 2
+    if cache_seqlens is None:
+        cache_seqlens = torch.full((b,), k_cache.shape[seq_axis], dtype=torch.int32, device=q.device)
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(d)
+    k_new = k.reshape(b, -1, d).contiguous() if k is not None else None
+    v_new = v.reshape(b, -1, d).contiguous() if v is not None else None
+    out = flash_attn_legacy_cuda.decode(
+        q.reshape(b, hq, d).contiguous(), k_cache, v_cache, cache_seqlens.to(torch.int32),
+        softmax_scale, k_new, v_new, cache_layout=cache_layout,
+    )
+    return out.view(b, 1, hq, d)
+
+
+class FlashAttention(nn.Module):
+    """Module form of flash_attention with a fixed head_dim, causal flag and scale."""
+
+    def __init__(self, head_dim: int = 64, causal: bool = False,
+                 softmax_scale: Optional[float] = None):
+        super().__init__()
+        assert head_dim in SUPPORTED_HEAD_DIMS
+        self.head_dim = head_dim
+        self.causal = causal
+        self.softmax_scale = softmax_scale or (1.0 / math.sqrt(head_dim))
+
+    def forward(self, q, k, v):
+        return flash_attention(q, k, v, self.softmax_scale, self.causal)
+
+
+class FlashMultiHeadAttention(nn.Module):
+    """Multi-head attention block (q/k/v/out projections) on the flash kernels.
+
+    `num_kv_heads` < `num_heads` gives GQA, 1 gives MQA.  Inputs in any float dtype are
+    computed in fp16 and cast back; dropout is applied after the output projection.
+    Same constructor and forward signature as the reference's module (flash_attn.py:238-312).
+    """
+
+    def __init__(self, embed_dim: int, num_heads: int, num_kv_heads: Optional[int] = None,
+                 causal: bool = False, bias: bool = True, dropout: float = 0.0):
+        super().__init__()
+        num_kv_heads = num_heads if num_kv_heads is None else num_kv_heads
+        assert embed_dim % num_heads == 0
+        assert num_heads % num_kv_heads == 0, (
+            f"num_heads ({num_heads}) must be divisible by num_kv_heads ({num_kv_heads})"
+        )
+        self.embed_dim = embed_dim
+        self.num_heads = num_heads
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = embed_dim // num_heads
+        assert self.head_dim in SUPPORTED_HEAD_DIMS, (
+            f"head_dim={self.head_dim}, must be 32, 64, 96, 128, or 256"
+        )
+        self.causal = causal
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+        self.q_proj = nn.Linear(embed_dim, num_heads * self.head_dim, bias=bias)
+        self.k_proj = nn.Linear(embed_dim, num_kv_heads * self.head_dim, bias=bias)
+        self.v_proj = nn.Linear(embed_dim, num_kv_heads * self.head_dim, bias=bias)
+        self.out_proj = nn.Linear(embed_dim, embed_dim, bias=bias)
+        self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
+
+    def forward(self, x: torch.Tensor, key_value: Optional[torch.Tensor] = None):
+        """x [B,N,embed_dim] (and optional key_value [B,N_kv,embed_dim]) -> [B,N,embed_dim]."""
+        bsz, n, _ = x.shape
+        src = x if key_value is None else key_value
+        q = self.q_proj(x).view(bsz, n, self.num_heads, self.head_dim).transpose(1, 2)
+        k = self.k_proj(src).view(bsz, -1, self.num_kv_heads, self.head_dim).transpose(1, 2)
+        v = self.v_proj(src).view(bsz, -1, self.num_kv_heads, self.head_dim).transpose(1, 2)
+        in_dtype = q.dtype
+        if in_dtype != torch.float16:
+            q, k, v = q.half(), k.half(), v.half()
+        out = flash_attention(q, k, v, self.scale, self.causal)
+        if in_dtype != torch.float16:
+            out = out.to(in_dtype)
+        out = out.transpose(1, 2).contiguous().view(bsz, n, self.embed_dim)
+        return self.dropout(self.out_proj(out))

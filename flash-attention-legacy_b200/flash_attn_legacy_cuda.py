@@ -62,7 +62,27 @@ _lib.fal_decode.restype = _i
 _lib.fal_decode.argtypes = [_vp, _vp, _vp, _sp, _sp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
                             _vp, ctypes.c_size_t, _vp, _vp]
 
+_lib.fal_profile_enable.restype = _i
+_lib.fal_profile_enable.argtypes = [_i]
+_lib.fal_profile_read.restype = _i
+_lib.fal_profile_read.argtypes = [_i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_i)]
+
 __version__ = _lib.fal_version().decode()
+
+KERNEL_FWD, KERNEL_BWD, KERNEL_DECODE_SPLITK = 0, 1, 2
+
+
+def profile_enable(on=True):
+    """Turns the library's per-kernel event timing on or off (off by default)."""
+    _check(_lib.fal_profile_enable(int(bool(on))))
+
+
+def profile_read(kind):
+    """Returns (total_ms, launches) recorded for one kernel kind since the last read."""
+    total = ctypes.c_double(0.0)
+    n = _i(0)
+    _check(_lib.fal_profile_read(int(kind), ctypes.byref(total), ctypes.byref(n)))
+    return total.value, n.value
 
 # One device status word per GPU; kernels set it non-zero if an internal wait ran out.
 _status = {}
@@ -211,10 +231,17 @@ def forward_varlen(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen
     return [O, L]
 
 
-def backward(dO, Q, K, V, O, L, softmax_scale, is_causal=False):
+def backward_workspace_bytes(B, Hq, rows, d):
+    """Bytes of scratch `backward` needs for [B,Hq,rows,d] queries (packed: B=1, rows=total_q)."""
+    return int(_lib.fal_bwd_workspace_bytes(B, Hq, rows, d))
+
+
+def backward(dO, Q, K, V, O, L, softmax_scale, is_causal=False, out=None, workspace=None):
     """Batched backward -> [dQ [B,Hq,N,d], dK [B,Hkv,N,d], dV [B,Hkv,N,d]] fp16.
 
     Same contract as the reference's `backward` (csrc/flash_attn_legacy.cpp:105-186).
+    `out` (a [dQ, dK, dV] list) and `workspace` (uint8, backward_workspace_bytes long,
+    256-byte aligned) let a caller reuse buffers across calls.
     """
     for name, t in (("dO", dO), ("Q", Q), ("K", K), ("V", V), ("O", O)):
         _require_cuda_half(name, t, 4)
@@ -225,11 +252,16 @@ def backward(dO, Q, K, V, O, L, softmax_scale, is_causal=False):
         raise RuntimeError("dO and O must have Q's shape")
     if L.dtype != torch.float32 or tuple(L.shape) != (B, Hq, Nq) or not L.is_contiguous():
         raise RuntimeError("L must be contiguous float32 [B, H_q, N]")
-    dQ = torch.empty((B, Hq, Nq, d), dtype=torch.float16, device=Q.device)
-    dK = torch.empty((B, Hkv, Nk, d), dtype=torch.float16, device=Q.device)
-    dV = torch.empty((B, Hkv, Nk, d), dtype=torch.float16, device=Q.device)
+    if out is None:
+        dQ = torch.empty((B, Hq, Nq, d), dtype=torch.float16, device=Q.device)
+        dK = torch.empty((B, Hkv, Nk, d), dtype=torch.float16, device=Q.device)
+        dV = torch.empty((B, Hkv, Nk, d), dtype=torch.float16, device=Q.device)
+    else:
+        dQ, dK, dV = out
     nbytes = _lib.fal_bwd_workspace_bytes(B, Hq, Nq, d)
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device) if workspace is None else workspace
+    if ws.numel() < nbytes:
+        raise RuntimeError("workspace too small")
     _check(_lib.fal_bwd(dO.data_ptr(), Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(),
                         L.data_ptr(), dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(),
                         B, Hq, Hkv, Nq, Nk, d,

@@ -153,6 +153,22 @@ FAL_API int fal_decode(const void* q, void* k_cache, void* v_cache,
                float softmax_scale, void* workspace, size_t workspace_bytes,
                int* status, void* stream);
 
+/*
+ * Optional kernel timing, off by default.  While enabled, the library records a
+ * CUDA event pair on the caller's stream around each launch of the kernel kinds
+ * below (events only -- no synchronisation, no device memory).  fal_profile_read
+ * waits for the recorded events, returns the summed device time and launch count
+ * for one kind and clears that kind's records.  The reference has no counterpart;
+ * its benchmarks time whole operator calls (benchmarks/benchmark.py:36-49).
+ */
+enum fal_kernel_kind {
+  FAL_KERNEL_FWD = 0,          /* forward main kernel */
+  FAL_KERNEL_BWD = 1,          /* backward dK/dV/dQ kernel (without pre/post passes) */
+  FAL_KERNEL_DECODE_SPLITK = 2 /* decode streaming pass (without append / combine) */
+};
+FAL_API int fal_profile_enable(int on);
+FAL_API int fal_profile_read(int kind, double* total_ms, int* launches);
+
 #ifdef __cplusplus
 }
 #endif

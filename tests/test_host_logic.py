@@ -1,0 +1,123 @@
+"""CPU: host-side logic of the Python surface (no kernel launches)."""
+import math
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+
+
+@pytest.fixture(scope="module")
+def fal():
+    import flash_attn_legacy as m
+    return m
+
+
+def test_package_exports_match_the_reference_surface(fal):
+    # flash_attn_legacy/__init__.py:46-54 of the reference, plus the decode entry
+    for name in ("flash_attention", "flash_attn_varlen_func", "FlashAttention", "FlashMultiHeadAttention",
+                 "check_gpu_compatibility", "get_device_info", "register", "flash_attn_with_kvcache"):
+        assert name in fal.__all__ and hasattr(fal, name)
+    assert fal.__version__ == "0.5.0"
+
+
+def test_binding_exposes_the_reference_extension_functions():
+    import flash_attn_legacy_cuda as ext
+    for name in ("forward", "forward_varlen", "backward", "backward_varlen", "decode"):
+        assert callable(getattr(ext, name))
+
+
+def test_native_head_dim_mapping():
+    from flash_attn_legacy.flash_attn import _native_head_dim
+    assert [_native_head_dim(d) for d in (32, 64, 96, 128)] == [64, 64, 128, 128]
+    with pytest.raises(NotImplementedError):
+        _native_head_dim(256)
+
+
+def test_operator_asserts_fire_before_any_launch(fal):
+    q = torch.zeros(1, 2, 8, 64)
+    with pytest.raises(AssertionError):
+        fal.flash_attention(q, q, q)                       # not fp16
+    with pytest.raises(AssertionError):
+        fal.flash_attn_varlen_func(q.half(), q.half(), q.half(), None, None, 8, 8)  # 4-D, not packed
+    with pytest.raises(AssertionError):
+        fal.FlashMultiHeadAttention(100, num_heads=4)      # head_dim 25
+    with pytest.raises(AssertionError):
+        fal.FlashMultiHeadAttention(256, num_heads=4, num_kv_heads=3)
+
+
+def test_binding_refuses_cpu_tensors():
+    import flash_attn_legacy_cuda as ext
+    q = torch.zeros(1, 2, 8, 64, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="must be on CUDA"):
+        ext.forward(q, q, q, 0.125, False)
+
+
+def test_causal_flag_resolution_order():
+    from flash_attn_legacy.integrations import _resolve_causal
+
+    class M:
+        is_causal = False
+
+    assert _resolve_causal(M(), None, 5, {"is_causal": True}) is True      # kwarg wins
+    assert _resolve_causal(M(), None, 5, {}) is False                        # then the module's flag
+    assert _resolve_causal(object(), None, 5, {}) is True                    # then the heuristic
+    assert _resolve_causal(object(), None, 1, {}) is False
+    assert _resolve_causal(object(), torch.zeros(1), 5, {}) is False
+
+
+def test_hook_fallback_branch_matches_the_oracle_on_cpu():
+    """On CPU tensors the hook must take the eager branch (the reference's own arithmetic)."""
+    from flash_attn_legacy.integrations import flash_attn_legacy_forward
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(2, 8, 1, 32, generator=g)
+    k = torch.randn(2, 2, 37, 32, generator=g)
+    v = torch.randn(2, 2, 37, 32, generator=g)
+    out, weights = flash_attn_legacy_forward(torch.nn.Module(), q, k, v, None, scaling=0.2)
+    assert weights is None and out.shape == (2, 1, 8, 32)
+    ref, _ = orc.decode_fwd(q[:, :, 0], k.transpose(1, 2), v.transpose(1, 2), torch.tensor([37, 37]), 0.2)
+    assert torch.allclose(out[:, 0], ref, atol=1e-5)
+    # additive mask and causal chunk: same arithmetic as the reference's fallback
+    mask = torch.zeros(2, 1, 4, 37)
+    mask[..., 1] = float("-inf")
+    q4 = torch.randn(2, 8, 4, 32, generator=g)
+    out2, _ = flash_attn_legacy_forward(torch.nn.Module(), q4, k, v, mask, scaling=0.2, is_causal=True)
+    kk, vv = k.repeat_interleave(4, 1), v.repeat_interleave(4, 1)
+    s = q4 @ kk.transpose(-1, -2) * 0.2 + mask + torch.triu(torch.full((4, 37), float("-inf")), 1)
+    assert torch.allclose(out2, (torch.softmax(s, -1) @ vv).transpose(1, 2), atol=1e-5)
+
+
+def test_register_is_idempotent_and_patches_validation(fal):
+    transformers = pytest.importorskip("transformers")
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS, PreTrainedModel
+    assert fal.register() and fal.register()
+    assert "flash_attn_legacy" in ALL_ATTENTION_FUNCTIONS.valid_keys()
+    check = PreTrainedModel._check_and_adjust_attn_implementation
+    assert getattr(check, "_flash_attn_legacy_patched", False)
+
+    class Cfg:
+        head_dim = 64
+
+    class Fake:
+        config = Cfg()
+
+    assert check(Fake(), "flash_attn_legacy") == "flash_attn_legacy"
+    cfg = transformers.LlamaConfig(vocab_size=100, hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                                   num_attention_heads=2, num_key_value_heads=1)
+    cfg._attn_implementation = "flash_attn_legacy"
+    model = transformers.LlamaForCausalLM(cfg)
+    assert model.config._attn_implementation == "flash_attn_legacy"
+    # a head_dim the kernels do not cover falls back to sdpa, as in the reference
+    cfg2 = transformers.LlamaConfig(vocab_size=100, hidden_size=80, intermediate_size=128, num_hidden_layers=1,
+                                    num_attention_heads=2, num_key_value_heads=1)
+    cfg2._attn_implementation = "flash_attn_legacy"
+    model2 = transformers.LlamaForCausalLM(cfg2)
+    assert model2.config._attn_implementation == "sdpa"
+
+
+def test_device_info_needs_cuda(fal):
+    if torch.cuda.is_available():
+        pytest.skip("covered by the GPU suite")
+    with pytest.raises(RuntimeError):
+        fal.get_device_info()
+    assert fal.check_gpu_compatibility(verbose=False) is False

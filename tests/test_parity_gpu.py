@@ -1,0 +1,531 @@
+"""GPU parity: the sm_100a kernels, called through the C-ABI binding, against the CPU oracle.
+
+Tolerances (written once in oracle/attention_oracle.py):
+    max|O - O_ref| / max|O_ref|  <= 2e-3,   same ratio <= 1e-2 for dQ, dK, dV,   max|LSE - LSE_ref| <= 1e-3.
+The oracle consumes the same fp16 input bits as the kernels and computes in fp32.
+"""
+import math
+
+import pytest
+import torch
+
+from conftest import golden_names, load_golden
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ext():
+    import flash_attn_legacy_cuda as m
+    m.reset_device_status()
+    return m
+
+
+@pytest.fixture(scope="module")
+def fal():
+    import flash_attn_legacy as m
+    return m
+
+
+def rand_half(gen, *shape):
+    return torch.randn(*shape, generator=gen).half()
+
+
+def check_fwd(o, lse, o_ref, lse_ref):
+    assert orc.rel_max_err(o, o_ref) <= orc.TOL_O
+    assert orc.abs_max_err(lse, lse_ref) <= orc.TOL_LSE
+
+
+def check_grads(got, ref):
+    for name, g, r in zip(("dQ", "dK", "dV"), got, ref):
+        err = orc.rel_max_err(g, r)
+        assert err <= orc.TOL_GRAD, f"{name}: {err}"
+
+
+def run_fwd_bwd(ext, q, k, v, do, scale, causal):
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    o, lse = ext.forward(qc, kc, vc, scale, causal)
+    grads = ext.backward(doc, qc, kc, vc, o, lse, scale, causal)
+    return o, lse, grads
+
+
+# ---------------------------------------------------------------------------------------------
+# Golden vectors produced by the reference's own code
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", golden_names("batched_"))
+def test_golden_batched(ext, name):
+    g = load_golden(name)
+    scale, causal = float(g["scale"]), bool(g["causal"])
+    o, lse, grads = run_fwd_bwd(ext, g["q"], g["k"], g["v"], g["d_out"], scale, causal)
+    assert orc.rel_max_err(o, g["o"]) <= orc.TOL_O
+    check_grads(grads, (g["dq"], g["dk"], g["dv"]))
+    _, lse_ref = orc.attention_fwd(g["q"], g["k"], g["v"], scale, causal)
+    assert orc.abs_max_err(lse, lse_ref) <= orc.TOL_LSE
+
+
+@pytest.mark.parametrize("name", golden_names("varlen_"))
+def test_golden_varlen(ext, name):
+    g = load_golden(name)
+    cu = g["cu_seqlens"].cuda()
+    lens = (g["cu_seqlens"][1:] - g["cu_seqlens"][:-1]).tolist()
+    o, _ = ext.forward_varlen(g["q"].cuda(), g["k"].cuda(), g["v"].cuda(), cu, cu, max(lens), max(lens),
+                              float(g["scale"]), bool(g["causal"]))
+    assert orc.rel_max_err(o, g["o"]) <= orc.TOL_O
+
+
+def test_golden_decode(ext):
+    g = load_golden("decode_hook_d64")
+    o = ext.decode(g["q"].cuda(), g["k_cache"].cuda(), g["v_cache"].cuda(), g["cache_seqlens"].cuda(),
+                   float(g["scale"]))
+    assert orc.rel_max_err(o, g["o"]) <= orc.TOL_O
+
+
+# ---------------------------------------------------------------------------------------------
+# Batched forward / backward against the oracle
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("n", [1, 33, 65, 100, 128, 200, 256, 257, 512, 777])
+def test_forward_backward_shapes(ext, d, causal, n):
+    g = torch.Generator().manual_seed(n * 7 + d)
+    q, k, v, do = rand_half(g, 2, 4, n, d), rand_half(g, 2, 2, n, d), rand_half(g, 2, 2, n, d), rand_half(g, 2, 4, n, d)
+    scale = 1 / math.sqrt(d)
+    o, lse, grads = run_fwd_bwd(ext, q, k, v, do, scale, causal)
+    o_ref, lse_ref = orc.attention_fwd(q, k, v, scale, causal)
+    check_fwd(o, lse, o_ref, lse_ref)
+    ref = orc.attention_bwd(q, k, v, do, scale, causal)
+    if n == 1:
+        # dQ and dK are exactly zero for a single token; compare absolutely
+        assert grads[0].abs().max().item() < 1e-3 and grads[1].abs().max().item() < 1e-3
+        assert orc.rel_max_err(grads[2], ref[2]) <= orc.TOL_GRAD
+    else:
+        check_grads(grads, ref)
+    assert ext.device_status() == 0
+
+
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (8, 4), (8, 1), (4, 1), (4, 2), (8, 8), (32, 1)])
+def test_gqa_ratios(ext, hq, hkv):
+    g = torch.Generator().manual_seed(hq * 10 + hkv)
+    n, d = 160, 64
+    q, k, v, do = rand_half(g, 1, hq, n, d), rand_half(g, 1, hkv, n, d), rand_half(g, 1, hkv, n, d), rand_half(g, 1, hq, n, d)
+    o, lse, grads = run_fwd_bwd(ext, q, k, v, do, 0.125, True)
+    check_fwd(o, lse, *orc.attention_fwd(q, k, v, 0.125, True))
+    check_grads(grads, orc.attention_bwd(q, k, v, do, 0.125, True))
+    assert grads[1].shape == k.shape and grads[2].shape == v.shape
+
+
+def test_config1_mha_forward_n1024_d64(ext):
+    """B=2, H=8, N=1024, d=64, causal, seed 0 -- checked in full."""
+    g = torch.Generator().manual_seed(0)
+    q, k, v = rand_half(g, 2, 8, 1024, 64), rand_half(g, 2, 8, 1024, 64), rand_half(g, 2, 8, 1024, 64)
+    o, lse = ext.forward(q.cuda(), k.cuda(), v.cuda(), 0.125, True)
+    check_fwd(o, lse, *orc.attention_fwd(q, k, v, 0.125, True))
+
+
+def test_config2_gqa_n4096_d128_full_size(ext):
+    """B=4, Hq=32, Hkv=8, N=4096, d=128 causal forward + backward at full size on the GPU; the oracle
+    checks two whole (batch, kv-head) groups; the rest is covered by size-independent properties."""
+    B, Hq, Hkv, N, d = 4, 32, 8, 4096, 128
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.randn(B, Hq, N, d, device="cuda", generator=gen).half()
+    k = torch.randn(B, Hkv, N, d, device="cuda", generator=gen).half()
+    v = torch.randn(B, Hkv, N, d, device="cuda", generator=gen).half()
+    do = torch.randn(B, Hq, N, d, device="cuda", generator=gen).half()
+    scale = 1 / math.sqrt(d)
+    o, lse = ext.forward(q, k, v, scale, True)
+    dq, dk, dv = ext.backward(do, q, k, v, o, lse, scale, True)
+    for b, h in ((0, 0), (3, 5)):
+        sl = slice(4 * h, 4 * h + 4)
+        qs, ks, vs, gs = q[b:b + 1, sl].cpu(), k[b:b + 1, h:h + 1].cpu(), v[b:b + 1, h:h + 1].cpu(), do[b:b + 1, sl].cpu()
+        o_ref, lse_ref = orc.attention_fwd_blocked(qs, ks, vs, scale, True)
+        check_fwd(o[b:b + 1, sl], lse[b:b + 1, sl], o_ref, lse_ref)
+        ref = orc.attention_bwd_blocked(qs, ks, vs, gs, scale, True)
+        check_grads((dq[b:b + 1, sl], dk[b:b + 1, h:h + 1], dv[b:b + 1, h:h + 1]), ref)
+    # properties over the whole output: finite, causal first row equals V[0], a second run of the
+    # forward is bitwise identical, and each batch entry computed alone gives the same forward bits.
+    for t in (o, lse, dq, dk, dv):
+        assert torch.isfinite(t).all()
+    v_rep = v[:, :, 0].repeat_interleave(4, dim=1)
+    assert (o[:, :, 0].float() - v_rep.float()).abs().max().item() < 2e-3
+    o2, lse2 = ext.forward(q, k, v, scale, True)
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    o_b, _ = ext.forward(q[2:3], k[2:3], v[2:3], scale, True)
+    assert torch.equal(o_b, o[2:3])
+    # dV is linear in dO: backward(2*dO).dV == 2*dV up to fp16 rounding of the doubled inputs
+    _, _, dv2 = ext.backward(do * 2, q, k, v, o, lse, scale, True)
+    assert orc.rel_max_err(dv2, dv.float().cpu() * 2) <= 2e-3
+    assert ext.device_status() == 0
+
+
+def test_forward_is_deterministic(ext):
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (rand_half(g, 1, 4, 256, 128).cuda() for _ in range(3))
+    a = ext.forward(q, k, v, 0.1, True)
+    b = ext.forward(q, k, v, 0.1, True)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_batch_independence(ext):
+    g = torch.Generator().manual_seed(6)
+    q, k, v = (rand_half(g, 4, 2, 128, 64).cuda() for _ in range(3))
+    full, _ = ext.forward(q, k, v, 0.125, False)
+    for b in range(4):
+        one, _ = ext.forward(q[b:b + 1], k[b:b + 1], v[b:b + 1], 0.125, False)
+        assert torch.equal(full[b:b + 1], one)
+
+
+def test_zero_scores_give_mean_of_v(ext):
+    g = torch.Generator().manual_seed(7)
+    v = rand_half(g, 1, 1, 64, 64) * 0.1
+    z = torch.zeros(1, 1, 64, 64, dtype=torch.float16)
+    o, lse = ext.forward(z.cuda(), z.cuda(), v.cuda(), 0.125, False)
+    expect = v.float().mean(dim=2, keepdim=True).expand_as(v)
+    assert (o.float().cpu() - expect).abs().max().item() < 1e-3
+    assert (lse.cpu() - math.log(64)).abs().max().item() < 1e-4
+
+
+def test_large_magnitude_scores_stay_finite(ext):
+    g = torch.Generator().manual_seed(8)
+    q, k, v = rand_half(g, 1, 2, 300, 128) * 5, rand_half(g, 1, 2, 300, 128) * 5, rand_half(g, 1, 2, 300, 128)
+    scale = 1 / math.sqrt(128)
+    o, lse = ext.forward(q.cuda(), k.cuda(), v.cuda(), scale, True)
+    assert torch.isfinite(o).all() and torch.isfinite(lse).all()
+    check_fwd(o, lse, *orc.attention_fwd(q, k, v, scale, True))
+
+
+def test_custom_scale(ext):
+    g = torch.Generator().manual_seed(9)
+    q, k, v = (rand_half(g, 1, 2, 96, 64) for _ in range(3))
+    o, lse = ext.forward(q.cuda(), k.cuda(), v.cuda(), 0.05, False)
+    check_fwd(o, lse, *orc.attention_fwd(q, k, v, 0.05, False))
+
+
+def test_strided_bnhd_inputs_without_copies(ext):
+    """[B,N,H,d] storage viewed as [B,H,N,d] goes through the C-ABI strides unchanged."""
+    g = torch.Generator().manual_seed(10)
+    qs, ks, vs = rand_half(g, 2, 150, 4, 64), rand_half(g, 2, 150, 2, 64), rand_half(g, 2, 150, 2, 64)
+    q, k, v = (t.cuda().transpose(1, 2) for t in (qs, ks, vs))
+    assert not q.is_contiguous()
+    o, lse = ext.forward(q, k, v, 0.125, True)
+    check_fwd(o, lse, *orc.attention_fwd(qs.transpose(1, 2), ks.transpose(1, 2), vs.transpose(1, 2), 0.125, True))
+
+
+def test_rectangular_forward_top_left_causal(ext):
+    """seqlen_q != seqlen_k in the forward, causal mask aligned top-left as in the reference kernels."""
+    g = torch.Generator().manual_seed(11)
+    q, k, v = rand_half(g, 1, 2, 300, 64), rand_half(g, 1, 2, 170, 64), rand_half(g, 1, 2, 170, 64)
+    for causal in (False, True):
+        o, lse = ext.forward_rect(q.cuda(), k.cuda(), v.cuda(), 0.125, causal)
+        check_fwd(o, lse, *orc.attention_fwd(q, k, v, 0.125, causal))
+
+
+# ---------------------------------------------------------------------------------------------
+# Packed sequences
+# ---------------------------------------------------------------------------------------------
+def packed_inputs(gen, lens, h, hkv, d):
+    total = sum(lens)
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+    return (rand_half(gen, total, h, d), rand_half(gen, total, hkv, d), rand_half(gen, total, hkv, d),
+            rand_half(gen, total, h, d), cu)
+
+
+@pytest.mark.parametrize("lens", [[32, 64, 48], [1, 1, 1, 1], [300, 17, 1025, 256, 511], [257], [64] * 9])
+@pytest.mark.parametrize("d,h,hkv", [(64, 4, 4), (128, 8, 2)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_varlen_forward_backward(ext, lens, d, h, hkv, causal):
+    g = torch.Generator().manual_seed(sum(lens) + d)
+    q, k, v, do, cu = packed_inputs(g, lens, h, hkv, d)
+    scale = 1 / math.sqrt(d)
+    cuc = cu.cuda()
+    o, lse = ext.forward_varlen(q.cuda(), k.cuda(), v.cuda(), cuc, cuc, max(lens), max(lens), scale, causal)
+    grads = ext.backward_varlen(do.cuda(), q.cuda(), k.cuda(), v.cuda(), o, lse, cuc, cuc, max(lens), max(lens),
+                                scale, causal)
+    check_fwd(o, lse, *orc.varlen_fwd(q, k, v, cu, cu, scale, causal))
+    ref = orc.varlen_bwd(q, k, v, do, cu, cu, scale, causal)
+    if max(lens) == 1:
+        assert grads[0].abs().max().item() < 1e-3 and grads[1].abs().max().item() < 1e-3
+        assert orc.rel_max_err(grads[2], ref[2]) <= orc.TOL_GRAD
+    else:
+        check_grads(grads, ref)
+    assert ext.device_status() == 0
+
+
+def test_varlen_single_sequence_equals_batched(ext):
+    g = torch.Generator().manual_seed(12)
+    n, h, d = 200, 4, 64
+    q, k, v = (rand_half(g, 1, h, n, d).cuda() for _ in range(3))
+    ob, lb = ext.forward(q, k, v, 0.125, True)
+    cu = torch.tensor([0, n], dtype=torch.int32).cuda()
+    pk = lambda t: t[0].permute(1, 0, 2).contiguous()
+    ov, lv = ext.forward_varlen(pk(q), pk(k), pk(v), cu, cu, n, n, 0.125, True)
+    assert torch.equal(ov.permute(1, 0, 2), ob[0]) and torch.equal(lv.permute(1, 0), lb[0])
+
+
+def test_varlen_unequal_q_and_k_lengths_forward(ext):
+    g = torch.Generator().manual_seed(13)
+    lq, lk = [40, 130, 7], [100, 60, 300]
+    h, d = 2, 64
+    cu_q = torch.tensor([0, 40, 170, 177], dtype=torch.int32)
+    cu_k = torch.tensor([0, 100, 160, 460], dtype=torch.int32)
+    q, k, v = rand_half(g, 177, h, d), rand_half(g, 460, h, d), rand_half(g, 460, h, d)
+    for causal in (False, True):
+        o, lse = ext.forward_varlen(q.cuda(), k.cuda(), v.cuda(), cu_q.cuda(), cu_k.cuda(), max(lq), max(lk),
+                                    0.125, causal)
+        check_fwd(o, lse, *orc.varlen_fwd(q, k, v, cu_q, cu_k, 0.125, causal))
+
+
+def test_varlen_with_an_empty_sequence(ext):
+    g = torch.Generator().manual_seed(14)
+    lens = [50, 0, 90]
+    q, k, v, do, cu = packed_inputs(g, lens, 2, 2, 64)
+    o, lse = ext.forward_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), 90, 90, 0.125, True)
+    grads = ext.backward_varlen(do.cuda(), q.cuda(), k.cuda(), v.cuda(), o, lse, cu.cuda(), cu.cuda(), 90, 90,
+                                0.125, True)
+    cu2 = torch.tensor([0, 50, 140], dtype=torch.int32)
+    check_fwd(o, lse, *orc.varlen_fwd(q, k, v, cu2, cu2, 0.125, True))
+    check_grads(grads, orc.varlen_bwd(q, k, v, do, cu2, cu2, 0.125, True))
+
+
+def test_config3_varlen_16_sequences(ext):
+    """16 sequences, lengths uniform in [64, 4096] (seed 2), H=16, d=128, causal, forward + backward at
+    full size; the oracle checks two of the 16 heads on every sequence."""
+    gl = torch.Generator().manual_seed(2)
+    lens = torch.randint(64, 4097, (16,), generator=gl).tolist()
+    total, H, d = sum(lens), 16, 128
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    q, k, v, do = (torch.randn(total, H, d, device="cuda", generator=gen).half() for _ in range(4))
+    scale = 1 / math.sqrt(d)
+    cuc = cu.cuda()
+    o, lse = ext.forward_varlen(q, k, v, cuc, cuc, max(lens), max(lens), scale, True)
+    dq, dk, dv = ext.backward_varlen(do, q, k, v, o, lse, cuc, cuc, max(lens), max(lens), scale, True)
+    for t in (o, lse, dq, dk, dv):
+        assert torch.isfinite(t).all()
+    for h in (0, 9):
+        sl = slice(h, h + 1)
+        qs, ks, vs, gs = (t[:, sl].cpu() for t in (q, k, v, do))
+        check_fwd(o[:, sl], lse[:, sl], *orc.varlen_fwd(qs, ks, vs, cu, cu, scale, True))
+        check_grads((dq[:, sl], dk[:, sl], dv[:, sl]), orc.varlen_bwd(qs, ks, vs, gs, cu, cu, scale, True))
+    # every sequence's first row sees only its own first key
+    first = cu[:-1].long().cuda()
+    assert (o[first].float() - v[first].float()).abs().max().item() < 2e-3
+    assert ext.device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------
+# Decode
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (64, 8, 8), (128, 8, 1), (64, 40, 2)])
+@pytest.mark.parametrize("append", [False, True])
+def test_decode_against_oracle(ext, d, hq, hkv, append):
+    g = torch.Generator().manual_seed(d + hq + append)
+    B, S = 5, 2500
+    kc, vc = rand_half(g, B, S, hkv, d), rand_half(g, B, S, hkv, d)
+    q = rand_half(g, B, hq, d)
+    lens = torch.tensor([0 if append else 1, 15, 1024, 1025, 2499], dtype=torch.int32)
+    kn, vn = (rand_half(g, B, hkv, d), rand_half(g, B, hkv, d)) if append else (None, None)
+    kcc, vcc = kc.cuda(), vc.cuda()
+    scale = 1 / math.sqrt(d)
+    o, lse = ext.decode(q.cuda(), kcc, vcc, lens.cuda(), scale, kn.cuda() if append else None,
+                        vn.cuda() if append else None, return_lse=True)
+    if append:
+        for b in range(B):
+            kc[b, lens[b]] = kn[b]
+            vc[b, lens[b]] = vn[b]
+        assert torch.equal(kcc.cpu(), kc) and torch.equal(vcc.cpu(), vc)  # append wrote exactly one row each
+        lens = lens + 1
+    check_fwd(o, lse, *orc.decode_fwd(q, kc, vc, lens, scale))
+    assert ext.device_status() == 0
+
+
+def test_decode_hf_cache_layout(ext):
+    g = torch.Generator().manual_seed(21)
+    B, S, hkv, hq, d = 2, 700, 2, 8, 64
+    kc, vc, q = rand_half(g, B, hkv, S, d), rand_half(g, B, hkv, S, d), rand_half(g, B, hq, d)
+    lens = torch.tensor([700, 333], dtype=torch.int32)
+    o = ext.decode(q.cuda(), kc.cuda(), vc.cuda(), lens.cuda(), 0.125, cache_layout="bhsd")
+    o_ref, _ = orc.decode_fwd(q, kc.transpose(1, 2), vc.transpose(1, 2), lens, 0.125)
+    assert orc.rel_max_err(o, o_ref) <= orc.TOL_O
+
+
+def test_config4_decode_256_steps_with_appends(ext):
+    """batch 64, Hq=32, Hkv=8, d=128, caches [64,32768,8,128], lengths uniform in [1024, 32768-256]
+    (clamped so that 256 appended tokens fit), 256 decode steps with appends.  The oracle checks
+    three batch entries at steps 0, 128 and 255."""
+    B, Hq, Hkv, S, d, steps = 64, 32, 8, 32768, 128, 256
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    kc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=gen)
+    vc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=gen)
+    lens = torch.randint(1024, S - steps + 1, (B,), device="cuda", generator=gen).to(torch.int32)
+    lens[0], lens[1] = 1024, S - steps
+    scale = 1 / math.sqrt(d)
+    picks = [0, 1, 37]
+    for step in range(steps):
+        q = torch.randn(B, Hq, d, device="cuda", dtype=torch.float16, generator=gen)
+        kn = torch.randn(B, Hkv, d, device="cuda", dtype=torch.float16, generator=gen)
+        vn = torch.randn(B, Hkv, d, device="cuda", dtype=torch.float16, generator=gen)
+        o, lse = ext.decode(q, kc, vc, lens, scale, kn, vn, return_lse=True)
+        lens += 1
+        if step in (0, 128, 255):
+            idx = torch.tensor(picks, device="cuda")
+            o_ref, lse_ref = orc.decode_fwd(q[idx].cpu(), kc[idx].cpu(), vc[idx].cpu(), lens[idx].cpu(), scale)
+            check_fwd(o[idx], lse[idx], o_ref, lse_ref)
+            assert torch.isfinite(o).all()
+    assert ext.device_status() == 0
+    del kc, vc
+    torch.cuda.empty_cache()
+
+
+# ---------------------------------------------------------------------------------------------
+# Long context (single GPU, sampled oracle)
+# ---------------------------------------------------------------------------------------------
+def test_config5_long_context_sampled(ext):
+    """B=1, Hq=32, Hkv=8, N=131072, d=128, causal forward + backward on one GPU.  One score matrix row
+    block of one head is 0.5 GB in fp32, so the oracle checks O, LSE and dQ on sampled 256-row blocks
+    of one KV-head group (dQ rows depend only on their own row block); dK/dV are checked for
+    finiteness here and exactly at smaller sizes by the tests above."""
+    B, Hq, Hkv, N, d = 1, 32, 8, 131072, 128
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    q = torch.randn(B, Hq, N, d, device="cuda", generator=gen).half()
+    k = torch.randn(B, Hkv, N, d, device="cuda", generator=gen).half()
+    v = torch.randn(B, Hkv, N, d, device="cuda", generator=gen).half()
+    do = torch.randn(B, Hq, N, d, device="cuda", generator=gen).half()
+    scale = 1 / math.sqrt(d)
+    o, lse = ext.forward(q, k, v, scale, True)
+    dq, dk, dv = ext.backward(do, q, k, v, o, lse, scale, True)
+    assert ext.device_status() == 0
+    for t in (o, lse, dq, dk, dv):
+        assert torch.isfinite(t).all()
+    h = 6  # KV head; query heads 24..27
+    sl = slice(4 * h, 4 * h + 4)
+    kh, vh = k[:, h:h + 1].cpu(), v[:, h:h + 1].cpu()
+    for r0 in (0, 65536 - 128, N - 256):
+        r1 = r0 + 256
+        qs = q[:, sl, :r1].cpu()  # rows beyond r1 are not needed by a causal row block
+        o_ref, lse_ref = orc.attention_fwd_rows(qs, kh, vh, scale, True, r0, r1)
+        check_fwd(o[:, sl, r0:r1], lse[:, sl, r0:r1], o_ref, lse_ref)
+        # dQ of the block: closed form on the block's rows
+        kf, vf = kh[:, :, :r1].float(), vh[:, :, :r1].float()
+        qf, gf = q[:, sl, r0:r1].cpu().float(), do[:, sl, r0:r1].cpu().float()
+        s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+        rows = torch.arange(r0, r1).view(-1, 1)
+        s.masked_fill_(torch.arange(r1).view(1, -1) > rows, float("-inf"))
+        p = torch.softmax(s, -1)
+        ds = p * (torch.matmul(gf, vf.transpose(-1, -2)) - (gf * torch.matmul(p, vf)).sum(-1, keepdim=True))
+        dq_ref = torch.matmul(ds, kf) * scale
+        assert orc.rel_max_err(dq[:, sl, r0:r1], dq_ref) <= orc.TOL_GRAD
+    del q, k, v, do, o, dq, dk, dv
+    torch.cuda.empty_cache()
+
+
+# ---------------------------------------------------------------------------------------------
+# The public operator surface (autograd, modules, error behaviour)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("d", [32, 64, 96, 128])
+def test_flash_attention_autograd_all_head_dims(fal, d):
+    g = torch.Generator().manual_seed(30 + d)
+    q, k, v, do = rand_half(g, 1, 4, 130, d), rand_half(g, 1, 2, 130, d), rand_half(g, 1, 2, 130, d), rand_half(g, 1, 4, 130, d)
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = fal.flash_attention(qc, kc, vc, is_causal=True)
+    assert out.shape == q.shape and out.dtype == torch.float16
+    out.backward(do.cuda())
+    scale = 1 / math.sqrt(d)
+    o_ref, _ = orc.attention_fwd(q, k, v, scale, True)
+    assert orc.rel_max_err(out.detach(), o_ref) <= orc.TOL_O
+    check_grads((qc.grad, kc.grad, vc.grad), orc.attention_bwd(q, k, v, do, scale, True))
+
+
+def test_head_dim_256_is_reported_as_not_built(fal):
+    q = torch.zeros(1, 1, 16, 256, dtype=torch.float16, device="cuda")
+    with pytest.raises(NotImplementedError):
+        fal.flash_attention(q, q, q)
+
+
+def test_varlen_func_autograd(fal):
+    g = torch.Generator().manual_seed(31)
+    lens = [70, 130, 9]
+    q, k, v, do, cu = packed_inputs(g, lens, 4, 4, 64)
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = fal.flash_attn_varlen_func(qc, kc, vc, cu.cuda(), cu.cuda(), 130, 130, causal=True)
+    out.backward(do.cuda())
+    o_ref, _ = orc.varlen_fwd(q, k, v, cu, cu, 0.125, True)
+    assert orc.rel_max_err(out.detach(), o_ref) <= orc.TOL_O
+    check_grads((qc.grad, kc.grad, vc.grad), orc.varlen_bwd(q, k, v, do, cu, cu, 0.125, True))
+
+
+def test_operator_rejects_what_the_reference_rejects(fal):
+    q = torch.zeros(1, 2, 16, 64, device="cuda")
+    with pytest.raises(AssertionError):
+        fal.flash_attention(q, q, q)  # float32
+    qh = torch.zeros(1, 2, 16, 80, device="cuda", dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        fal.flash_attention(qh, qh, qh)  # head_dim 80
+    qh = torch.zeros(1, 3, 16, 64, device="cuda", dtype=torch.float16)
+    kh = torch.zeros(1, 2, 16, 64, device="cuda", dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        fal.flash_attention(qh, kh, kh)  # 3 % 2 != 0
+    with pytest.raises((AssertionError, RuntimeError)):
+        fal.flash_attention(qh.cpu(), qh.cpu(), qh.cpu())
+
+
+def test_modules(fal):
+    torch.manual_seed(0)
+    mha = fal.FlashMultiHeadAttention(256, num_heads=4, num_kv_heads=2, causal=True).cuda()
+    x = torch.randn(2, 50, 256, device="cuda", requires_grad=True)
+    y = mha(x)
+    assert y.shape == x.shape and y.dtype == x.dtype
+    y.sum().backward()
+    assert x.grad is not None and torch.isfinite(x.grad).all()
+    attn = fal.FlashAttention(head_dim=64, causal=True)
+    q = torch.randn(1, 2, 40, 64, device="cuda", dtype=torch.float16)
+    assert attn(q, q, q).shape == q.shape
+
+
+def test_utils(fal):
+    info = fal.get_device_info()
+    assert info["supported"] and info["sm_version"] // 10 == 10
+    assert fal.check_gpu_compatibility(verbose=False)
+
+
+# ---------------------------------------------------------------------------------------------
+# HuggingFace route: attn_implementation="flash_attn_legacy" on a tiny random LLaMA
+# ---------------------------------------------------------------------------------------------
+def _tiny_llama(attn):
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.LlamaConfig(vocab_size=1000, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                                   num_attention_heads=8, num_key_value_heads=2, max_position_embeddings=512)
+    torch.manual_seed(0)
+    cfg._attn_implementation = attn
+    return transformers.LlamaForCausalLM(cfg).half().cuda().eval()
+
+
+def test_hf_registration_prefill_and_generate(fal):
+    assert fal.register()
+    ref_model = _tiny_llama("eager")
+    model = _tiny_llama("flash_attn_legacy")
+    model.load_state_dict(ref_model.state_dict())
+    assert model.config._attn_implementation == "flash_attn_legacy"
+    ids = torch.randint(0, 1000, (2, 64), device="cuda")
+    with torch.no_grad():
+        a = model(ids).logits.float()
+        b = ref_model(ids).logits.float()
+    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+    assert cos > 0.999
+    # one cached decode step: logits must agree with eager attention on the same cache
+    with torch.no_grad():
+        pre = model(ids[:, :40], use_cache=True)
+        pre_ref = ref_model(ids[:, :40], use_cache=True)
+        step = model(ids[:, 40:41], past_key_values=pre.past_key_values, use_cache=True).logits.float()
+        step_ref = ref_model(ids[:, 40:41], past_key_values=pre_ref.past_key_values, use_cache=True).logits.float()
+    cos = torch.nn.functional.cosine_similarity(step.flatten(), step_ref.flatten(), dim=0).item()
+    assert cos > 0.999
+    import flash_attn_legacy_cuda as ext
+    ext.profile_enable(True)
+    ext.profile_read(ext.KERNEL_DECODE_SPLITK)
+    with torch.no_grad():
+        out = model.generate(ids[:, :8], max_new_tokens=16, do_sample=False)
+    _, launches = ext.profile_read(ext.KERNEL_DECODE_SPLITK)
+    ext.profile_enable(False)
+    assert out.shape == (2, 24)
+    assert launches >= 15 * 2  # every decode step of both layers ran the split-K kernel
