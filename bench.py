@@ -176,9 +176,9 @@ def run_reference(args):
     }))
 
 
-def run_decode_extra(ext, peaks, steps=256):
+def run_decode_extra(ext, peaks, steps=256, batch=64):
     """Secondary metric: KV-cache split-K decode with appends, B=64 Hq=32 Hkv=8 d=128, cache 32768."""
-    B, Hq, Hkv, S, d = 64, 32, 8, 32768, 128
+    B, Hq, Hkv, S, d = batch, 32, 8, 32768, 128
     g = torch.Generator(device="cuda").manual_seed(3)
     kc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
     vc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
@@ -205,7 +205,7 @@ def run_decode_extra(ext, peaks, steps=256):
     k_ms, k_n = ext.profile_read(ext.KERNEL_DECODE_SPLITK)
     mean_len = lens0.float().mean().item() + (steps + 1) / 2.0
     kv_bytes = mean_len * B * Hkv * d * 2 * 2  # K and V, fp16, read once per KV head
-    res = {"workload": "decode_B64_Hq32_Hkv8_d128_cache32768_256steps_with_append",
+    res = {"workload": f"decode_B{B}_Hq32_Hkv8_d128_cache32768_{steps}steps_with_append",
            "ms_per_step": ms, "kv_gbs": kv_bytes / ms / 1e6,
            "frac_of_hbm_peak": kv_bytes / ms / 1e6 / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
            "launches_per_step": 3}
@@ -224,6 +224,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and decode extras")
+    ap.add_argument("--decode-profile", action="store_true",
+                    help="run only a small decode case (batch 16, a few steps): the case profilers capture")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -236,6 +238,11 @@ def main():
     rank, world, local, dist = dist_setup(args.gpus)
     import flash_attn_legacy_cuda as ext
     import flash_attn_legacy as fal
+
+    if args.decode_profile:
+        res = run_decode_extra(ext, measured_peaks(), steps=max(args.steps, 4), batch=16)
+        print(json.dumps({"decode_profile_case": res}))
+        return
 
     w = WORKLOAD
     B, Hq, Hkv, N, d, causal = w["B"], w["Hq"], w["Hkv"], w["N"], w["d"], w["causal"]

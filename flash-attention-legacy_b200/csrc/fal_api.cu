@@ -69,7 +69,11 @@ int make_tensor_map(CUtensorMap* map, const void* base, int head_dim, int64_t ro
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? FAL_OK : FAL_ERR_TENSOR_MAP;
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = 100000 + static_cast<int>(r);  // driver (CUresult) codes are offset by 100000
+    return FAL_ERR_TENSOR_MAP;
+  }
+  return FAL_OK;
 }
 
 fal::RowStrides to_rs(const fal_strides* s) { return fal::RowStrides{s->batch, s->head, s->row}; }
@@ -81,6 +85,15 @@ int check_device() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e);
   if (dev < 0 || dev >= 64) return FAL_ERR_UNSUPPORTED_DEVICE;
+  // A host thread that has made no CUDA call yet (an autograd worker, say) has no context bound,
+  // and the driver's tensor-map encoder refuses to run without one.  Re-selecting the current
+  // device binds the primary context to this thread; it changes nothing else.
+  thread_local int bound_device = -1;
+  if (bound_device != dev) {
+    e = cudaSetDevice(dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    bound_device = dev;
+  }
   std::lock_guard<std::mutex> g(mu);
   if (cached[dev] == 0) {
     int major = 0;

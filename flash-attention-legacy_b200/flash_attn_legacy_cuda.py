@@ -116,8 +116,8 @@ def reset_device_status(device=None):
 def _check(rc):
     if rc != 0:
         msg = _lib.fal_strerror(rc).decode()
-        if rc == -4:
-            msg += f" (cudaError {_lib.fal_last_cuda_error()})"
+        if rc in (-4, -5):
+            msg += f" (CUDA error code {_lib.fal_last_cuda_error()})"
         raise RuntimeError(f"flash_attn_legacy_cuda: {msg}")
 
 

@@ -49,7 +49,8 @@ enum fal_error {
 /* Human-readable name of a fal_error code. */
 FAL_API const char* fal_strerror(int code);
 
-/* cudaError_t value of the last failed CUDA call on this host thread (0 if none). */
+/* cudaError_t value of the last failed CUDA runtime call on this host thread (0 if none);
+ * after FAL_ERR_TENSOR_MAP, 100000 + the driver's CUresult. */
 FAL_API int fal_last_cuda_error(void);
 
 /* Library version, "major.minor.patch". */
