@@ -171,6 +171,9 @@ const char* fal_strerror(int code) {
     case FAL_ERR_CUDA: return "CUDA runtime error";
     case FAL_ERR_TENSOR_MAP: return "TMA descriptor could not be built";
     case FAL_ERR_UNSUPPORTED_DEVICE: return "device is not compute capability 10.x (B200)";
+    case FAL_ERR_STATIC_SCRATCH_EXCEEDED:
+      return "problem too large for fal_decode_static's fixed 8 MiB scratch "
+             "(batch*heads_q*ceil(capacity/1024)*(head_dim+2)*4 bytes must fit); use fal_decode";
     default: return "unknown error";
   }
 }
@@ -532,6 +535,65 @@ int fal_decode(const void* q, void* k_cache, void* v_cache, const fal_strides* k
   const int rec = g_timer.begin(FAL_KERNEL_DECODE_SPLITK, st);
   e = fal::launch_decode_splitk(p, st);
   g_timer.end(FAL_KERNEL_DECODE_SPLITK, rec, st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = fal::launch_decode_combine(p, st);
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+int fal_decode_static(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,
+                      const fal_strides* v_strides, const int32_t* cache_seqlens, const void* k_new,
+                      const void* v_new, void* o, float* lse, int batch, int heads_q, int heads_kv,
+                      int capacity, int head_dim, float softmax_scale, int* status, void* stream) {
+  if (!q || !k_cache || !v_cache || !k_strides || !v_strides || !cache_seqlens || !o)
+    return FAL_ERR_INVALID_ARGUMENT;
+  if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
+  if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || capacity <= 0) return FAL_ERR_INVALID_ARGUMENT;
+  if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
+  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o) ||
+      !aligned16(k_new) || !aligned16(v_new))
+    return FAL_ERR_INVALID_ARGUMENT;
+  const fal_strides* both[2] = {k_strides, v_strides};
+  for (const fal_strides* s : both)
+    if (s->row % 8 != 0 || s->head % 8 != 0 || s->batch % 8 != 0) return FAL_ERR_INVALID_ARGUMENT;
+  // The partials of this problem must fit the fixed array; nothing is launched otherwise.
+  if (fal_decode_workspace_bytes(batch, heads_q, capacity, head_dim) > fal::kDecodeStaticScratchBytes)
+    return FAL_ERR_STATIC_SCRATCH_EXCEEDED;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+  float* scratch = nullptr;
+  cudaError_t e = fal::decode_static_scratch(&scratch);  // first call per device: address look-up
+  if (e != cudaSuccess) return cuda_fail(e);
+
+  fal::DecodeParams p{};
+  p.q = q;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.k_strides = to_rs(k_strides);
+  p.v_strides = to_rs(v_strides);
+  p.k_new = k_new;
+  p.v_new = v_new;
+  p.cache_seqlens = cache_seqlens;
+  p.o = o;
+  p.lse = lse;
+  p.batch = batch;
+  p.heads_q = heads_q;
+  p.heads_kv = heads_kv;
+  p.capacity = capacity;
+  p.head_dim = head_dim;
+  p.split_len = kDecodeSplitLen;
+  p.splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
+  p.scale = softmax_scale;
+  p.status = status;
+  p.part_o = scratch;
+  p.part_ml = scratch + static_cast<int64_t>(batch) * heads_q * p.splits * head_dim;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (k_new != nullptr) {
+    e = fal::launch_decode_append(p, st);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  e = fal::launch_decode_splitk(p, st);
   if (e != cudaSuccess) return cuda_fail(e);
   e = fal::launch_decode_combine(p, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);

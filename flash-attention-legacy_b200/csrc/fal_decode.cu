@@ -371,6 +371,35 @@ cudaError_t launch_splitk_t(const DecodeParams& p, cudaStream_t stream) {
 
 }  // namespace
 
+// ---------------------------------------------------------------------------
+// Fixed scratch for fal_decode_static: split-K partials for callers that cannot
+// allocate device memory.  It lives in the library image, so every GPU that
+// loads the library carries these bytes until the process exits.
+// ---------------------------------------------------------------------------
+namespace {
+static __device__ __align__(256) float g_decode_static_scratch[kDecodeStaticScratchBytes / sizeof(float)];
+}  // namespace
+
+// In host code the array's name is only a handle for the runtime, not a device address, so the
+// address is looked up once per device (with that device current) and cached.
+cudaError_t decode_static_scratch(float** ptr) {
+  static std::mutex mu;
+  static float* cached[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> g(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess) return e;
+    cached[dev] = static_cast<float*>(p);
+  }
+  *ptr = cached[dev];
+  return cudaSuccess;
+}
+
 cudaError_t launch_decode_append(const DecodeParams& p, cudaStream_t stream) {
   fal_decode_append_kernel<<<p.batch * p.heads_kv, 32, 0, stream>>>(p);
   return cudaGetLastError();

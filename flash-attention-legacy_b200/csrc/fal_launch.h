@@ -103,6 +103,10 @@ struct DecodeParams {
   float scale;
   int* status;
 };
+// Size of the library-resident scratch behind fal_decode_static, and its per-device address.
+constexpr size_t kDecodeStaticScratchBytes = 8u << 20;
+cudaError_t decode_static_scratch(float** ptr);
+
 cudaError_t launch_decode_append(const DecodeParams& p, cudaStream_t stream);
 cudaError_t launch_decode_splitk(const DecodeParams& p, cudaStream_t stream);
 cudaError_t launch_decode_combine(const DecodeParams& p, cudaStream_t stream);

@@ -62,6 +62,11 @@ _lib.fal_decode.restype = _i
 _lib.fal_decode.argtypes = [_vp, _vp, _vp, _sp, _sp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
                             _vp, ctypes.c_size_t, _vp, _vp]
 
+_lib.fal_decode_static.restype = _i
+_lib.fal_decode_static.argtypes = [_vp, _vp, _vp, _sp, _sp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
+                                   _vp, _vp]
+DECODE_STATIC_SCRATCH_BYTES = 8 << 20
+
 _lib.fal_profile_enable.restype = _i
 _lib.fal_profile_enable.argtypes = [_i]
 _lib.fal_profile_read.restype = _i
@@ -356,3 +361,46 @@ def decode(q, k_cache, v_cache, cache_seqlens, softmax_scale, k_new=None, v_new=
                            B, Hq, Hkv, S, d, float(softmax_scale), ws.data_ptr(), nbytes,
                            _status_word(q.device).data_ptr(), _stream(q)))
     return (o, lse) if return_lse else o
+
+
+def decode_static(q, k_cache, v_cache, cache_seqlens, softmax_scale, out, k_new=None, v_new=None,
+                  cache_layout="bshd", lse=None):
+    """`decode` for callers that must not allocate on the device: binding of fal_decode_static.
+
+    Some users of this library run where device allocation is off limits -- a serving loop with
+    a memory budget fixed at start-up, an operator callback that only gets the operator's own
+    tensors, code that cannot afford the device-wide synchronisation an allocation may imply.
+    This call therefore allocates nothing, in the library or here: the caller passes every
+    buffer, `out` ([B,Hq,d] fp16) and the optional `lse` ([B,Hq] fp32) included, and the split-K
+    partials go to an 8 MiB scratch array inside the library.  Problems whose partials do not
+    fit (fal_decode_workspace_bytes > 8 MiB) raise RuntimeError.  Make the first call on a
+    device outside stream capture (it looks up the scratch address once), and do not let two
+    calls overlap on the GPU: they share the scratch.  Returns `out`.
+    """
+    _require_cuda_half("q", q, 3)
+    _require_cuda_half("k_cache", k_cache, 4)
+    _require_cuda_half("v_cache", v_cache, 4)
+    _same_device(q, k_cache, v_cache, cache_seqlens, k_new, v_new, out, lse)
+    if not q.is_contiguous() or not out.is_contiguous() or out.dtype != torch.float16:
+        raise RuntimeError("q and out must be contiguous [B, H_q, d] float16")
+    if cache_seqlens.dtype != torch.int32:
+        raise RuntimeError("cache_seqlens must be int32")
+    B, Hq, d = q.shape
+    if cache_layout == "bshd":
+        S, Hkv = k_cache.shape[1], k_cache.shape[2]
+        ks = _Strides(k_cache.stride(0), k_cache.stride(2), k_cache.stride(1))
+        vs = _Strides(v_cache.stride(0), v_cache.stride(2), v_cache.stride(1))
+    elif cache_layout == "bhsd":
+        Hkv, S = k_cache.shape[1], k_cache.shape[2]
+        ks = _Strides(k_cache.stride(0), k_cache.stride(1), k_cache.stride(2))
+        vs = _Strides(v_cache.stride(0), v_cache.stride(1), v_cache.stride(2))
+    else:
+        raise ValueError("cache_layout must be 'bshd' or 'bhsd'")
+    _check(_lib.fal_decode_static(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ks, vs,
+                                  cache_seqlens.data_ptr(),
+                                  k_new.data_ptr() if k_new is not None else None,
+                                  v_new.data_ptr() if v_new is not None else None,
+                                  out.data_ptr(), lse.data_ptr() if lse is not None else None,
+                                  B, Hq, Hkv, S, d, float(softmax_scale),
+                                  _status_word(q.device).data_ptr(), _stream(q)))
+    return out

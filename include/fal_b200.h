@@ -43,7 +43,8 @@ enum fal_error {
   FAL_ERR_WORKSPACE_TOO_SMALL = -3,
   FAL_ERR_CUDA = -4,        /* a CUDA runtime call failed; see fal_last_cuda_error() */
   FAL_ERR_TENSOR_MAP = -5,  /* the driver rejected a TMA descriptor */
-  FAL_ERR_UNSUPPORTED_DEVICE = -6 /* not compute capability 10.x */
+  FAL_ERR_UNSUPPORTED_DEVICE = -6, /* not compute capability 10.x */
+  FAL_ERR_STATIC_SCRATCH_EXCEEDED = -7 /* fal_decode_static: problem needs more than its fixed scratch */
 };
 
 /* Human-readable name of a fal_error code. */
@@ -153,6 +154,41 @@ FAL_API int fal_decode(const void* q, void* k_cache, void* v_cache,
                int batch, int heads_q, int heads_kv, int capacity, int head_dim,
                float softmax_scale, void* workspace, size_t workspace_bytes,
                int* status, void* stream);
+
+/*
+ * Decode for callers that must not allocate device memory (no counterpart in the
+ * reference).  Some hosts of this library cannot call cudaMalloc at the point where
+ * they decode: a serving loop that was handed a fixed memory budget at start-up, a
+ * plugin callback that only receives the tensors of the operator it implements, or
+ * code that must stay free of the implicit device synchronisation an allocation
+ * can cause.  fal_decode needs a caller-provided workspace for its split-K partial
+ * results; this variant keeps those partials in a scratch array that is part of the
+ * library image instead, and otherwise behaves exactly like fal_decode (same
+ * arguments minus the workspace, same kernels, same results).
+ *
+ * Limits and rules:
+ *   - the scratch is FAL_DECODE_STATIC_SCRATCH_BYTES (8 MiB) per GPU, held by every
+ *     GPU that loads the library until the process exits; a problem is accepted only
+ *     if fal_decode_workspace_bytes(batch, heads_q, capacity, head_dim) fits in it,
+ *     otherwise the call returns FAL_ERR_STATIC_SCRATCH_EXCEEDED and launches nothing
+ *     (8 MiB covers e.g. batch 8 x 32 heads x capacity 32768 x d 128);
+ *   - the call performs no cudaMalloc / cudaFree and calls no allocating library
+ *     routine; inputs and outputs are still the caller's buffers;
+ *   - the first call on each device looks up the scratch's device address
+ *     (cudaGetSymbolAddress); make that first call before any stream capture;
+ *   - all calls on a device share the one array, which keeps whatever the last call
+ *     left in it.  Nothing in it has to start at zero (every slot the combine step
+ *     reads is written earlier in the same call), but two calls that overlap on the
+ *     GPU -- different streams, or different host threads without ordering -- race
+ *     on it and corrupt each other's results.  Serialise them on one stream.
+ */
+#define FAL_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+FAL_API int fal_decode_static(const void* q, void* k_cache, void* v_cache,
+                      const fal_strides* k_strides, const fal_strides* v_strides,
+                      const int32_t* cache_seqlens, const void* k_new, const void* v_new,
+                      void* o, float* lse,
+                      int batch, int heads_q, int heads_kv, int capacity, int head_dim,
+                      float softmax_scale, int* status, void* stream);
 
 /*
  * Optional kernel timing, off by default.  While enabled, the library records a
