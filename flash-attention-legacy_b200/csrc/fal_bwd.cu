@@ -28,8 +28,10 @@
 //   warp  9      tcgen05.mma issuer, TMEM owner
 //   warps 10-13  dQ tile write-back
 //
-// TMEM columns: S^T/P^T x2 [0,128), dP^T [128,192), dQ^T [192,256),
-//               dV [256,256+D), dK [256+D,256+2D).
+// TMEM columns: S^T/P^T x2 [0,128), dP^T/dQ^T x2 [128,256) (dQ^T of a step reuses the
+//               columns of that step's consumed dP^T), dV [256,256+D), dK [256+D,256+2D).
+// Q/dO tiles and their row statistics go through a 3-deep shared-memory ring, and the
+// issuer runs S^T and dP^T one step ahead of the compute warps.
 #include "fal_common.h"
 #include "fal_launch.h"
 #include "sm100_ptx.cuh"
@@ -51,6 +53,7 @@ enum BwdBarrier : int {
 
 template <int D>
 struct BwdSmem {
+  static constexpr int kStages = 3;                            // Q / dO / statistics ring depth
   static constexpr int kBoxes = D / 64;
   static constexpr int kKvBoxBytes = kKvTile * 128;
   static constexpr int kKvTileBytes = kBoxes * kKvBoxBytes;
@@ -58,18 +61,18 @@ struct BwdSmem {
   static constexpr int kQTileBytes = kBoxes * kQBoxBytes;
   static constexpr int kKOff = 0;
   static constexpr int kVOff = kKvTileBytes;
-  static constexpr int kQOff = 2 * kKvTileBytes;               // 2 stages
-  static constexpr int kDoOff = kQOff + 2 * kQTileBytes;       // 2 stages
-  static constexpr int kDsOff = kDoOff + 2 * kQTileBytes;      // [128 keys][64 queries] fp16
+  static constexpr int kQOff = 2 * kKvTileBytes;
+  static constexpr int kDoOff = kQOff + kStages * kQTileBytes;
+  static constexpr int kDsOff = kDoOff + kStages * kQTileBytes;  // [128 keys][64 queries] fp16
   static constexpr int kDsBytes = kKvTile * 128;
-  static constexpr int kDqOff = kDsOff + kDsBytes;             // [64 queries][D] fp32
+  static constexpr int kDqOff = kDsOff + kDsBytes;               // [64 queries][D] fp32
   static constexpr int kDqBytes = kQTile * D * 4;
-  static constexpr int kStatOff = kDqOff + kDqBytes;           // 2 stages x (lse2[64], delta[64])
-  static constexpr int kStatBytes = 2 * 2 * kQTile * 4;
+  static constexpr int kStatOff = kDqOff + kDqBytes;             // per stage: lse2[64], delta[64]
+  static constexpr int kStatBytes = kStages * 2 * kQTile * 4;
   static constexpr int kBarOff = kStatOff + kStatBytes;
-  // k_full v_full q_full[2] do_full[2] stat_full[2] stage_empty[2] s_ready[2]
-  // dp_ready p_ready ds_ready ds_free dq_ready dq_free all_done
-  static constexpr int kNumBars = 2 + 2 + 2 + 2 + 2 + 2 + 7;
+  // k_full v_full q_full[3] do_full[3] stat_full[3] stage_empty[3] s_ready[2] dp_ready[2]
+  // dq_ready[2] dq_free[2] p_ready ds_ready ds_free all_done
+  static constexpr int kNumBars = 2 + 4 * kStages + 8 + 4;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kBytes = kMiscOff + 16;
   static constexpr int kAllocBytes = kBytes + 1024;
@@ -120,6 +123,21 @@ __device__ __forceinline__ bool bwd_decode_work(const BwdParams& p, BwdWork& w) 
   return false;
 }
 
+// Tuning aid, compiled in only with -DFAL_BWD_TIMING: cycles each role spends in each wait.
+#ifdef FAL_BWD_TIMING
+__device__ unsigned long long g_bwd_wait_cycles[32];
+#define BWD_WAIT(slot, ...)                           \
+  do {                                                \
+    const long long _t0 = clock64();                  \
+    mbar_wait(__VA_ARGS__);                           \
+    tacc[slot] += clock64() - _t0;                    \
+  } while (0)
+#define BWD_TIMING_ONLY(x) x
+#else
+#define BWD_WAIT(slot, ...) mbar_wait(__VA_ARGS__)
+#define BWD_TIMING_ONLY(x)
+#endif
+
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -139,15 +157,18 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t bar0 = sbase + L::kBarOff;
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  constexpr int iKFull = 0, iVFull = 1, iQFull = 2, iDoFull = 4, iStatFull = 6, iStageEmpty = 8,
-                iSReady = 10, iDpReady = 12, iPReady = 13, iDsReady = 14, iDsFree = 15,
-                iDqReady = 16, iDqFree = 17, iAllDone = 18;
+  constexpr int NS = L::kStages;
+  constexpr int iKFull = 0, iVFull = 1, iQFull = 2, iDoFull = 2 + NS, iStatFull = 2 + 2 * NS,
+                iStageEmpty = 2 + 3 * NS, iSReady = 2 + 4 * NS, iDpReady = iSReady + 2,
+                iDqReady = iSReady + 4, iDqFree = iSReady + 6, iPReady = iSReady + 8,
+                iDsReady = iSReady + 9, iDsFree = iSReady + 10, iAllDone = iSReady + 11;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kMiscOff + 4);
   const WaitCtx wctx{abort_flag, p.status};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  BWD_TIMING_ONLY(long long tacc[24] = {}; const long long t_cta0 = clock64();)
 
   const int group = p.heads_q / p.heads_kv;
   const int kv0 = wk.kvblk * kKvTile;                       // local index of the tile's first key
@@ -160,19 +181,21 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     *abort_flag = 0;
     mbar_init(bar(iKFull), 1);
     mbar_init(bar(iVFull), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(bar(iQFull + s), 1);
       mbar_init(bar(iDoFull + s), 1);
       mbar_init(bar(iStatFull + s), 32);
       mbar_init(bar(iStageEmpty + s), 1);
-      mbar_init(bar(iSReady + s), 1);
     }
-    mbar_init(bar(iDpReady), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(iSReady + s), 1);
+      mbar_init(bar(iDpReady + s), 1);
+      mbar_init(bar(iDqReady + s), 1);
+      mbar_init(bar(iDqFree + s), 128);
+    }
     mbar_init(bar(iPReady), 256);
     mbar_init(bar(iDsReady), 256);
     mbar_init(bar(iDsFree), 1);
-    mbar_init(bar(iDqReady), 1);
-    mbar_init(bar(iDqFree), 128);
     mbar_init(bar(iAllDone), 1);
     fence_mbar_init();
   }
@@ -184,7 +207,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t kColS = 0, kColDp = 128, kColDq = 192, kColDv = 256, kColDk = 256 + D;
+  constexpr uint32_t kColS = 0, kColDpq = 128, kColDv = 256, kColDk = 256 + D;
 
   if (warp == 8) {
     // ===================== producer: TMA + per-row statistics =================
@@ -203,10 +226,10 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     wk.k_row0 + kv0, wk.kv_head, wk.batch);
     }
     for (int i = 0; i < n_iter; ++i) {
-      const int st = i & 1;
+      const int st = i % NS;
       const int head = wk.kv_head * group + i / nq;
       const int qt = qt0 + i % nq;
-      if (i >= 2) mbar_wait(bar(iStageEmpty + st), ((i >> 1) - 1) & 1, wctx, kBbStageEmpty + st);
+      if (i >= NS) BWD_WAIT(0, bar(iStageEmpty + st), ((i / NS) - 1) & 1, wctx, kBbStageEmpty + st);
       if (lane == 0) {
         const int row = wk.q_row0 + qt * kQTile;
         mbar_arrive_expect_tx(bar(iQFull + st), L::kQTileBytes);
@@ -245,74 +268,99 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       constexpr uint32_t idesc_dq = make_idesc_f16(128, kQTile, 1, 1);       // dQ^T
       const uint32_t k_s = sbase + L::kKOff, v_s = sbase + L::kVOff, ds_s = sbase + L::kDsOff;
 
+      // Descriptors are stepped with 32-bit adds on their low words (address field = addr >> 4).
+      constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
+      const uint32_t k_lo_k = smem_desc_lo(k_s, 16);                    // K as K-major operand
+      const uint32_t v_lo_k = smem_desc_lo(v_s, 16);                    // V as K-major operand
+      const uint32_t k_lo_mn = smem_desc_lo(k_s, L::kKvBoxBytes);       // K^T (MN-major A of dQ^T)
+      const uint32_t ds_lo_k = smem_desc_lo(ds_s, 16);                  // dS^T as K-major A of dK
+      const uint32_t ds_lo_mn = smem_desc_lo(ds_s, 16);                 // dS^T as MN-major B of dQ^T
+
       // acc[128 keys x 64 queries] = X[keys x D] * Y[queries x D]^T, both head_dim-contiguous
-      auto issue_xyT = [&](uint32_t d_col, uint32_t x_s, uint32_t y_s) {
+      auto issue_xyT = [&](uint32_t d_col, uint32_t x_lo, uint32_t y_s) {
+        const uint32_t y_lo = smem_desc_lo(y_s, 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           umma_ss(tmem_base + d_col,
-                  make_smem_desc_sw128(x_s + (ks >> 2) * L::kKvBoxBytes + (ks & 3) * 32, 16, 1024),
-                  make_smem_desc_sw128(y_s + (ks >> 2) * L::kQBoxBytes + (ks & 3) * 32, 16, 1024),
+                  smem_desc_join(x_lo + (((ks >> 2) * L::kKvBoxBytes + (ks & 3) * 32) >> 4), kHi),
+                  smem_desc_join(y_lo + (((ks >> 2) * L::kQBoxBytes + (ks & 3) * 32) >> 4), kHi),
                   idesc_st, ks > 0 ? 1u : 0u);
         }
       };
 
+      // S^T and dP^T run one step ahead of the compute warps; each has two TMEM buffers.
       mbar_wait(bar(iKFull), 0, wctx, kBbKFull);
       mbar_wait(bar(iQFull + 0), 0, wctx, kBbQFull);
       tc_fence_after_sync();
-      issue_xyT(kColS, k_s, sbase + L::kQOff);
+      issue_xyT(kColS, k_lo_k, sbase + L::kQOff);
       tc_commit(bar(iSReady + 0));
       mbar_wait(bar(iVFull), 0, wctx, kBbVFull);
+      mbar_wait(bar(iDoFull + 0), 0, wctx, kBbDoFull);
+      tc_fence_after_sync();
+      issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff);
+      tc_commit(bar(iDpReady + 0));
 
       for (int i = 0; i < n_iter; ++i) {
-        const int st = i & 1;
-        const uint32_t q_s = sbase + L::kQOff + st * L::kQTileBytes;
-        const uint32_t do_s = sbase + L::kDoOff + st * L::kQTileBytes;
-        // dP^T(i)
-        mbar_wait(bar(iDoFull + st), (i >> 1) & 1, wctx, kBbDoFull + st);
-        if (i > 0) mbar_wait(bar(iDsReady), (i - 1) & 1, wctx, kBbDsReady);  // dP^T(i-1) consumed
-        tc_fence_after_sync();
-        issue_xyT(kColDp, v_s, do_s);
-        tc_commit(bar(iDpReady));
-        // S^T(i+1) into the other buffer
+        const int st = i % NS;
+        const int sb = i & 1;
+        const int st1 = (i + 1) % NS;
+        const int sb1 = (i + 1) & 1;
+        const uint32_t q_lo_mn = smem_desc_lo(sbase + L::kQOff + st * L::kQTileBytes, L::kQBoxBytes);
+        const uint32_t do_lo_mn = smem_desc_lo(sbase + L::kDoOff + st * L::kQTileBytes, L::kQBoxBytes);
+        // S^T(i+1): its buffer held P^T(i-1), which dV(i-1) (issued earlier) has read by then.
         if (i + 1 < n_iter) {
-          const int s1 = (i + 1) & 1;
-          mbar_wait(bar(iQFull + s1), ((i + 1) >> 1) & 1, wctx, kBbQFull + s1);
+          BWD_WAIT(1, bar(iQFull + st1), ((i + 1) / NS) & 1, wctx, kBbQFull + st1);
           tc_fence_after_sync();
-          issue_xyT(kColS + s1 * kQTile, k_s, sbase + L::kQOff + s1 * L::kQTileBytes);
-          tc_commit(bar(iSReady + s1));
+          BWD_TIMING_ONLY(const long long t_a = clock64();)
+          issue_xyT(kColS + sb1 * kQTile, k_lo_k, sbase + L::kQOff + st1 * L::kQTileBytes);
+          BWD_TIMING_ONLY(tacc[16] += clock64() - t_a;)
+          tc_commit(bar(iSReady + sb1));
+          BWD_TIMING_ONLY(tacc[20] += clock64() - t_a;)
         }
         // dV += P^T(i) dO(i): P^T as fp16 in TMEM, query columns [0,32) at +0, [32,64) at +32
-        mbar_wait(bar(iPReady), i & 1, wctx, kBbPReady);
+        BWD_WAIT(2, bar(iPReady), i & 1, wctx, kBbPReady);
         tc_fence_after_sync();
+        BWD_TIMING_ONLY(const long long t_b = clock64();)
 #pragma unroll
         for (int ks = 0; ks < kQTile / 16; ++ks) {
-          const uint32_t a_col = kColS + st * kQTile + (ks >> 1) * 32 + (ks & 1) * 8;
+          const uint32_t a_col = kColS + sb * kQTile + (ks >> 1) * 32 + (ks & 1) * 8;
           umma_ts(tmem_base + kColDv, tmem_base + a_col,
-                  make_smem_desc_sw128(do_s + ks * 2048, L::kQBoxBytes, 1024), idesc_dkv,
+                  smem_desc_join(do_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dkv,
                   (i > 0 || ks > 0) ? 1u : 0u);
+        }
+        BWD_TIMING_ONLY(tacc[17] += clock64() - t_b;)
+        // dP^T(i+1): its buffer last held dQ^T(i-1), which the write-back warps must have drained.
+        if (i + 1 < n_iter) {
+          BWD_WAIT(3, bar(iDoFull + st1), ((i + 1) / NS) & 1, wctx, kBbDoFull + st1);
+          if (i >= 1) BWD_WAIT(4, bar(iDqFree + sb1), ((i - 1) >> 1) & 1, wctx, kBbDqFree);
+          tc_fence_after_sync();
+          BWD_TIMING_ONLY(const long long t_c = clock64();)
+          issue_xyT(kColDpq + sb1 * kQTile, v_lo_k, sbase + L::kDoOff + st1 * L::kQTileBytes);
+          tc_commit(bar(iDpReady + sb1));
+          BWD_TIMING_ONLY(tacc[18] += clock64() - t_c;)
         }
         // dK += dS^T(i) Q(i)
-        mbar_wait(bar(iDsReady), i & 1, wctx, kBbDsReady);
+        BWD_WAIT(5, bar(iDsReady), i & 1, wctx, kBbDsReady);
         tc_fence_after_sync();
+        BWD_TIMING_ONLY(const long long t_d = clock64();)
 #pragma unroll
         for (int ks = 0; ks < kQTile / 16; ++ks) {
-          umma_ss(tmem_base + kColDk, make_smem_desc_sw128(ds_s + ks * 32, 16, 1024),
-                  make_smem_desc_sw128(q_s + ks * 2048, L::kQBoxBytes, 1024), idesc_dkv,
+          umma_ss(tmem_base + kColDk, smem_desc_join(ds_lo_k + ((ks * 32) >> 4), kHi),
+                  smem_desc_join(q_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dkv,
                   (i > 0 || ks > 0) ? 1u : 0u);
         }
-        // dQ^T(i) = K^T dS^T(i)
-        if (i > 0) {
-          mbar_wait(bar(iDqFree), (i - 1) & 1, wctx, kBbDqFree);
-          tc_fence_after_sync();
-        }
+        // dQ^T(i) = K^T dS^T(i), into the columns of the consumed dP^T(i)
 #pragma unroll
         for (int ks = 0; ks < kKvTile / 16; ++ks) {
-          umma_ss(tmem_base + kColDq, make_smem_desc_sw128(k_s + ks * 2048, L::kKvBoxBytes, 1024),
-                  make_smem_desc_sw128(ds_s + ks * 2048, 16, 1024), idesc_dq, ks > 0 ? 1u : 0u);
+          umma_ss(tmem_base + kColDpq + sb * kQTile,
+                  smem_desc_join(k_lo_mn + ((ks * 2048) >> 4), kHi),
+                  smem_desc_join(ds_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dq, ks > 0 ? 1u : 0u);
         }
-        tc_commit(bar(iDqReady));
+        BWD_TIMING_ONLY(tacc[19] += clock64() - t_d;)
+        tc_commit(bar(iDqReady + sb));
         tc_commit(bar(iStageEmpty + st));
         tc_commit(bar(iDsFree));
+        BWD_TIMING_ONLY(tacc[21] += clock64() - t_d;)
       }
       tc_commit(bar(iAllDone));
     }
@@ -329,28 +377,32 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint8_t* ds_row = sgen + L::kDsOff + kv_row * 128;
 
     for (int i = 0; i < n_iter; ++i) {
-      const int st = i & 1;
+      const int st = i % NS;
+      const int sb = i & 1;
       const int qt = qt0 + i % nq;
       const int q_col0 = qt * kQTile + half * 32;  // local query index of this thread's first column
       const float* stat = reinterpret_cast<const float*>(sgen + L::kStatOff) + st * 2 * kQTile + half * 32;
       const bool tile_mask = !kv_ok || (CAUSAL && (kv0 + kKvTile - 1 > qt * kQTile));
 
-      mbar_wait(bar(iStatFull + st), (i >> 1) & 1, wctx, kBbStatFull + st);
-      mbar_wait(bar(iSReady + st), (i >> 1) & 1, wctx, kBbSReady + st);
+      BWD_WAIT(6, bar(iStatFull + st), (i / NS) & 1, wctx, kBbStatFull + st);
+      BWD_WAIT(7, bar(iSReady + sb), (i >> 1) & 1, wctx, kBbSReady + sb);
       tc_fence_after_sync();
+      BWD_TIMING_ONLY(const long long t_p0 = clock64();)
 
       float pv[32];
       {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColS + st * kQTile + half * 32, r);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColS + sb * kQTile + half * 32, r);
+        float4 l4[8];  // the statistics load overlaps the TMEM load's latency
+#pragma unroll
+        for (int j = 0; j < 8; ++j) l4[j] = *reinterpret_cast<const float4*>(stat + 4 * j);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(stat + j);
-          pv[j + 0] = fast_exp2(fmaf(__uint_as_float(r[j + 0]), c2, -l4.x));
-          pv[j + 1] = fast_exp2(fmaf(__uint_as_float(r[j + 1]), c2, -l4.y));
-          pv[j + 2] = fast_exp2(fmaf(__uint_as_float(r[j + 2]), c2, -l4.z));
-          pv[j + 3] = fast_exp2(fmaf(__uint_as_float(r[j + 3]), c2, -l4.w));
+          pv[j + 0] = fast_exp2(fmaf(__uint_as_float(r[j + 0]), c2, -l4[j >> 2].x));
+          pv[j + 1] = fast_exp2(fmaf(__uint_as_float(r[j + 1]), c2, -l4[j >> 2].y));
+          pv[j + 2] = fast_exp2(fmaf(__uint_as_float(r[j + 2]), c2, -l4[j >> 2].z));
+          pv[j + 3] = fast_exp2(fmaf(__uint_as_float(r[j + 3]), c2, -l4[j >> 2].w));
         }
         if (tile_mask) {
 #pragma unroll
@@ -363,22 +415,27 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int j = 0; j < 16; ++j) pk[j] = pack_half2(pv[2 * j], pv[2 * j + 1]);
         // P^T overwrites this thread's own S^T columns: [32*half, 32*half+16)
-        tmem_st_32x32b_x16(tmem_base + lane_addr + kColS + st * kQTile + half * 32, pk);
+        tmem_st_32x32b_x16(tmem_base + lane_addr + kColS + sb * kQTile + half * 32, pk);
         tmem_wait_st();
       }
       tc_fence_before_sync();
       mbar_arrive(bar(iPReady));
+      BWD_TIMING_ONLY(tacc[22] += clock64() - t_p0;)
 
-      mbar_wait(bar(iDpReady), i & 1, wctx, kBbDpReady);
+      BWD_WAIT(8, bar(iDpReady + sb), (i >> 1) & 1, wctx, kBbDpReady);
       tc_fence_after_sync();
+      BWD_TIMING_ONLY(const long long t_s0 = clock64();)
       uint32_t dsp[16];
       {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDp + half * 32, r);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + sb * kQTile + half * 32, r);
+        float4 d4s[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d4s[j] = *reinterpret_cast<const float4*>(stat + kQTile + 4 * j);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(stat + kQTile + j);
+          const float4 d4 = d4s[j >> 2];
           const float a0 = pv[j + 0] * (__uint_as_float(r[j + 0]) - d4.x);
           const float a1 = pv[j + 1] * (__uint_as_float(r[j + 1]) - d4.y);
           const float a2 = pv[j + 2] * (__uint_as_float(r[j + 2]) - d4.z);
@@ -387,7 +444,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           dsp[(j >> 1) + 1] = pack_half2(a2, a3);
         }
       }
-      if (i > 0) mbar_wait(bar(iDsFree), (i - 1) & 1, wctx, kBbDsFree);
+      if (i > 0) BWD_WAIT(9, bar(iDsFree), (i - 1) & 1, wctx, kBbDsFree);
       // dS^T row -> shared memory, 128-byte XOR swizzle (16-byte chunk index ^ row % 8)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -398,6 +455,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(bar(iDsReady));
+      BWD_TIMING_ONLY(tacc[23] += clock64() - t_s0;)
     }
 
     // ---- epilogue: dV (warps 0-3) and dK (warps 4-7) -------------------------
@@ -439,44 +497,65 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int quarter = warp & 3;
     const int drow = quarter * 32 + lane;  // head_dim index = TMEM lane of dQ^T
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    float* stage = reinterpret_cast<float*>(sgen + L::kDqOff);
+    // The 64-row tile leaves in two 32-row halves, each with its own staging buffer, so that
+    // the bulk reduction of one half reads shared memory while the other half is being written.
+    float* stage_half[2] = {reinterpret_cast<float*>(sgen + L::kDqOff),
+                            reinterpret_cast<float*>(sgen + L::kDqOff) + (kQTile / 2) * D};
+    const bool issuer = warp == 10 && lane == 0;
     for (int i = 0; i < n_iter; ++i) {
       const int head = wk.kv_head * group + i / nq;
       const int qt = qt0 + i % nq;
-      mbar_wait(bar(iDqReady), i & 1, wctx, kBbDqReady);
+      const int sb = i & 1;
+      BWD_WAIT(10, bar(iDqReady + sb), (i >> 1) & 1, wctx, kBbDqReady);
       tc_fence_after_sync();
-      uint32_t r0[32], r1[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDq, r0);
-      tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDq + 32, r1);
+      uint32_t r[2][32];
+      tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + sb * kQTile, r[0]);
+      tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + sb * kQTile + 32, r[1]);
       tmem_wait_ld();
       tc_fence_before_sync();
-      mbar_arrive(bar(iDqFree));
-      if (drow < D) {
+      mbar_arrive(bar(iDqFree + sb));
+      BWD_TIMING_ONLY(const long long t_red0 = clock64();)
+      float* dst_tile = p.dq_accum + wk.batch * p.dq_accum_batch_stride + head * p.dq_accum_head_stride +
+                        (static_cast<int64_t>(wk.q_row0) + qt * kQTile) * D;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          stage[j * D + drow] = __uint_as_float(r0[j]);
-          stage[(j + 32) * D + drow] = __uint_as_float(r1[j]);
+      for (int hf = 0; hf < 2; ++hf) {
+        // The reduction that last read this half's buffer (two groups ago) must be done with it.
+        if (issuer) bulk_wait_group_read<1>();
+        named_barrier_sync(1, 128);
+        if (drow < D) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stage_half[hf][j * D + drow] = __uint_as_float(r[hf][j]);
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1, 128);
+        if (issuer) {
+          const int rows = min(kQTile / 2, wk.seqlen_q - qt * kQTile - hf * (kQTile / 2));
+          if (rows > 0) {
+            bulk_reduce_add_f32(dst_tile + hf * (kQTile / 2) * D,
+                                sbase + L::kDqOff + hf * (kQTile / 2) * D * 4,
+                                static_cast<uint32_t>(rows) * D * 4u);
+          }
+          bulk_commit_group();  // one group per half, empty or not: keeps the group count uniform
         }
       }
-      fence_proxy_async_smem();
-      named_barrier_sync(1, 128);
-      if (warp == 10 && lane == 0) {
-        const int q_local = qt * kQTile;
-        const int rows = min(kQTile, wk.seqlen_q - q_local);
-        if (rows > 0) {
-          float* dst = p.dq_accum + wk.batch * p.dq_accum_batch_stride +
-                       head * p.dq_accum_head_stride +
-                       (static_cast<int64_t>(wk.q_row0) + q_local) * D;
-          bulk_reduce_add_f32(dst, sbase + L::kDqOff, static_cast<uint32_t>(rows) * D * 4u);
-          bulk_commit_group();
-          bulk_wait_group_read0();
-        }
-      }
-      named_barrier_sync(1, 128);
+      BWD_TIMING_ONLY(tacc[11] += clock64() - t_red0;)
     }
     if (warp == 10 && lane == 0) bulk_wait_group0();
   }
 
+#ifdef FAL_BWD_TIMING
+  if (lane == 0 && (warp == 0 || warp == 8 || warp == 9 || warp == 10)) {
+    for (int i = 0; i < 12; ++i)
+      if (tacc[i]) atomicAdd(&g_bwd_wait_cycles[i], static_cast<unsigned long long>(tacc[i]));
+    for (int i = 16; i < 24; ++i)
+      if (tacc[i]) atomicAdd(&g_bwd_wait_cycles[i], static_cast<unsigned long long>(tacc[i]));
+    if (warp == 0) {
+      atomicAdd(&g_bwd_wait_cycles[12], static_cast<unsigned long long>(clock64() - t_cta0));
+      atomicAdd(&g_bwd_wait_cycles[13], static_cast<unsigned long long>(n_iter));
+      atomicAdd(&g_bwd_wait_cycles[14], 1ull);
+    }
+  }
+#endif
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 9) {
@@ -484,6 +563,21 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tmem_dealloc(tmem_base, 512);
   }
 }
+
+#ifdef FAL_BWD_TIMING
+}  // namespace
+}  // namespace fal
+extern "C" __attribute__((visibility("default"))) int fal_debug_bwd_waits(unsigned long long* out32, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out32, fal::g_bwd_wait_cycles, sizeof(unsigned long long) * 32);
+  if (e == cudaSuccess && reset) {
+    unsigned long long z[32] = {};
+    e = cudaMemcpyToSymbol(fal::g_bwd_wait_cycles, z, sizeof(z));
+  }
+  return static_cast<int>(e);
+}
+namespace fal {
+namespace {
+#endif
 
 // ---------------------------------------------------------------------------
 // Pre-pass: delta[row] = sum_d dO*O  (precompute_D_kernel, bwd.cu:76-107 of the reference).

@@ -17,6 +17,8 @@
 //   warps 4-7   softmax + output for rows 128..255
 //   warp  8     TMA producer (one elected lane)
 //   warp  9     tcgen05.mma issuer (one elected lane), TMEM owner
+//   warps 10-11 idle (they complete the third warpgroup so that registers can be
+//               moved from it to the softmax warpgroups with setmaxnreg)
 //
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
 // P (fp16) overwrites the first 64 columns of its S tile and feeds the PV MMA
@@ -29,13 +31,39 @@ namespace fal {
 
 namespace {
 
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;  // three warpgroups: softmax 0, softmax 1, {producer, issuer, 2 idle}
 constexpr int kTileM = 128;   // query rows per softmax warpgroup
 constexpr int kTileN = 128;   // keys per step
 constexpr int kCtaRows = 2 * kTileM;
 constexpr float kNegInf = -INFINITY;
 // Skip the O rescale while the running maximum grows by less than 2^8.
 constexpr float kRescaleThreshold = 8.0f;
+
+// Of every 8 consecutive score columns, this many take the FMA-pipe exp2 instead of the
+// special-function unit (16 ex2/clk/SM would otherwise cap the kernel at d=128).
+#ifndef FAL_EXP_EMU_PER8
+#define FAL_EXP_EMU_PER8 0
+#endif
+template <int K>
+__device__ __forceinline__ float tile_exp2(int i, float x) {
+  // i is a multiple of 4 under full unrolling, so the choice folds at compile time.
+  return (((i + K) & 7) < FAL_EXP_EMU_PER8) ? exp2_fma(x) : fast_exp2(x);
+}
+
+// Register split after launch (setmaxnreg).  The kernel launches with 168 registers for each of
+// its 384 threads = 64512; the two softmax warpgroups and the third warpgroup must not ask for
+// more than that in total, or setmaxnreg.inc would wait forever.
+#ifndef FAL_FWD_REGS_SOFTMAX
+#define FAL_FWD_REGS_SOFTMAX 216
+#endif
+#ifndef FAL_FWD_REGS_OTHER
+#define FAL_FWD_REGS_OTHER 72
+#endif
+constexpr int kRegsSoftmax = FAL_FWD_REGS_SOFTMAX;
+constexpr int kRegsOther = FAL_FWD_REGS_OTHER;
+static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 168 * 384,
+              "setmaxnreg split exceeds the registers the CTA was launched with");
+static_assert(kRegsSoftmax % 8 == 0 && kRegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
 
 // Barrier ids (only used to label a wait that gave up).
 enum FwdBarrier : int {
@@ -194,7 +222,11 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  // Register rebalancing between warpgroups (first statement of every role): the softmax warps
+  // keep a whole 128-wide score row in registers, the producer / issuer warpgroup needs few.
+  if (warp >= 8) {
+    setmaxnreg_dec<kRegsOther>();
+    if (warp == 8) {
     // ===================== TMA producer =====================================
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
@@ -230,27 +262,30 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(kTileM, kTileN, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(kTileM, D, 0, 1);
+      // Descriptors are stepped with 32-bit adds on their low words (address field = addr >> 4).
+      constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
+      const uint32_t q_lo[2] = {smem_desc_lo(sbase + L::kQOff, 16),
+                                smem_desc_lo(sbase + L::kQOff + L::kTileBytes, 16)};
       // S[w] = Q[w] K_j^T : both operands K-major (head_dim contiguous), 16 head-dim
       // elements (32 bytes inside the 128-byte swizzle row) per instruction.
       auto issue_qk = [&](int w, int j) {
-        const uint32_t qa = sbase + L::kQOff + w * L::kTileBytes;
-        const uint32_t ka = sbase + L::kKOff + (j % NS) * L::kTileBytes;
+        const uint32_t k_lo = smem_desc_lo(sbase + L::kKOff + (j % NS) * L::kTileBytes, 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * L::kBoxBytes + (ks & 3) * 32;
-          umma_ss(tmem_base + w * kTileN, make_smem_desc_sw128(qa + off, 16, 1024),
-                  make_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
+          umma_ss(tmem_base + w * kTileN, smem_desc_join(q_lo[w] + off, kHi),
+                  smem_desc_join(k_lo + off, kHi), idesc_qk, ks > 0 ? 1u : 0u);
         }
       };
       // O[w] += P[w] V_j : A = P from TMEM (8 columns of packed fp16 per 16 keys), B = V
       // MN-major (head_dim contiguous): 16 keys = 2048 bytes per step, 64-column halves
       // kBoxBytes apart (LBO), 8-key groups 1024 bytes apart (SBO).
       auto issue_pv = [&](int w, int j) {
-        const uint32_t va = sbase + L::kVOff + (j % NS) * L::kTileBytes;
+        const uint32_t v_lo = smem_desc_lo(sbase + L::kVOff + (j % NS) * L::kTileBytes, L::kBoxBytes);
 #pragma unroll
         for (int ks = 0; ks < kTileN / 16; ++ks) {
           umma_ts(tmem_base + 256 + w * D, tmem_base + w * kTileN + ks * 8,
-                  make_smem_desc_sw128(va + ks * 2048, L::kBoxBytes, 1024), idesc_pv,
+                  smem_desc_join(v_lo + ((ks * 2048) >> 4), kHi), idesc_pv,
                   (j > 0 || ks > 0) ? 1u : 0u);
         }
       };
@@ -289,8 +324,10 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
     __syncwarp();
+  }
   } else {
     // ===================== softmax + output =================================
+    setmaxnreg_inc<kRegsSoftmax>();
     const int wg = warp >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -314,23 +351,37 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const bool tile_mask =
           (kv0 + kTileN > wk.seqlen_k) || (CAUSAL && (kv0 + kTileN - 1 > q_tile0));
 
-      // pass 1: row maximum of the raw scores
-      float mx = kNegInf;
+      // All 128 scores of this thread's row, one TMEM round trip.
+      uint32_t sr[4][32];
 #pragma unroll
-      for (int c = 0; c < kTileN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tS + c * 32, r);
-        tmem_wait_ld();
-        if (tile_mask) {
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tS + c * 32, sr[c]);
+      tmem_wait_ld();
+      if (tile_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = (c * 32 + i < limit) ? __uint_as_float(r[i]) : kNegInf;
-            mx = fmaxf(mx, v);
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i >= limit) sr[c][i] = __float_as_uint(kNegInf);
+      }
+      // Row maximum: eight independent 3-input chains instead of one 128-long chain.
+      float mx;
+      {
+        float part[8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            const int b0 = hlf * 16;
+            float a = fmax3(__uint_as_float(sr[c][b0]), __uint_as_float(sr[c][b0 + 1]),
+                            __uint_as_float(sr[c][b0 + 2]));
+#pragma unroll
+            for (int i = 3; i + 1 < 16; i += 2)
+              a = fmax3(a, __uint_as_float(sr[c][b0 + i]), __uint_as_float(sr[c][b0 + i + 1]));
+            a = fmaxf(a, __uint_as_float(sr[c][b0 + 15]));
+            part[c * 2 + hlf] = a;
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+        mx = fmaxf(fmax3(part[0], part[1], part[2]), fmax3(part[3], part[4], part[5]));
+        mx = fmax3(mx, part[6], part[7]);
       }
       const float m_new = fmaxf(m_ref, mx);
 
@@ -358,31 +409,30 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       const float moff = (m_ref == kNegInf) ? 0.f : m_ref * c2;
 
-      // pass 2: P = exp2(s * c2 - m * c2), row sum, fp16 P back into TMEM
-      float sum0 = 0.f, sum1 = 0.f;
+      // P = exp2(s * c2 - m * c2) from the registers, four independent row-sum chains,
+      // fp16 P back into TMEM over the first half of S.
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < kTileN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tS + c * 32, r);
-        tmem_wait_ld();
+      for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float x0 = fmaf(__uint_as_float(r[i]), c2, -moff);
-          float x1 = fmaf(__uint_as_float(r[i + 1]), c2, -moff);
-          if (tile_mask) {
-            if (c * 32 + i >= limit) x0 = kNegInf;
-            if (c * 32 + i + 1 >= limit) x1 = kNegInf;
-          }
-          const float p0 = fast_exp2(x0);
-          const float p1 = fast_exp2(x1);
+        for (int i = 0; i < 32; i += 4) {
+          const float p0 = tile_exp2<0>(i, fmaf(__uint_as_float(sr[c][i + 0]), c2, -moff));
+          const float p1 = tile_exp2<1>(i, fmaf(__uint_as_float(sr[c][i + 1]), c2, -moff));
+          const float p2 = tile_exp2<2>(i, fmaf(__uint_as_float(sr[c][i + 2]), c2, -moff));
+          const float p3 = tile_exp2<3>(i, fmaf(__uint_as_float(sr[c][i + 3]), c2, -moff));
           sum0 += p0;
           sum1 += p1;
-          pk[i >> 1] = pack_half2(p0, p1);
+          sum2 += p2;
+          sum3 += p3;
+          pk[(i >> 1) + 0] = pack_half2(p0, p1);
+          pk[(i >> 1) + 1] = pack_half2(p2, p3);
         }
         tmem_st_32x32b_x16(tS + c * 16, pk);
       }
-      l += sum0 + sum1;
+      const float sum_lo = sum0 + sum1, sum_hi = sum2 + sum3;
+      const float sum01 = sum_lo + sum_hi;
+      l += sum01;
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar(iPReady + wg));

@@ -132,6 +132,12 @@ __device__ __forceinline__ void bulk_wait_group_read0() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
+// Same, but lets the N most recent groups stay in flight.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 // Waits until the bulk groups issued by this thread have completed entirely.
 __device__ __forceinline__ void bulk_wait_group0() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -238,6 +244,21 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t addr, uint32_t
          (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// The same descriptor split into its 32-bit halves, so that an issuing thread can keep the low
+// word of a tile's base descriptor in a register and step through a tile with one 32-bit add
+// per MMA (the address field holds addr >> 4 and shared-memory addresses never carry out of it).
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo) {
+  return ((addr & 0x3FFFFu) >> 4) | (((lbo >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo) {
+  return ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint64_t smem_desc_join(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                         uint32_t idesc, uint32_t accumulate) {
@@ -264,6 +285,16 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       : "memory");
 }
 
+// Warpgroup-wide register reallocation (all four warps of a warpgroup must execute it).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---------------------------------------------------------------------------
 // Small math helpers
 // ---------------------------------------------------------------------------
@@ -271,6 +302,26 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// exp2 on the FMA / ALU pipes instead of the special-function unit: 2^x = 2^floor(x) * 2^frac(x),
+// frac part by a degree-3 polynomial (max relative error 8.6e-5, below fp16 rounding), integer
+// part added into the exponent field.  Valid for x <= 127; x below -126 (masked scores are -inf)
+// is clamped and yields about 1e-38.
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -126.f);
+  float t;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.f));  // low mantissa bits = floor(x)
+  const float fr = x - (t - 12582912.f);
+  const float p = fmaf(fmaf(fmaf(0.07706618f, fr, 0.22764593f), fr, 0.69511657f), fr, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// Three-input maximum (one instruction on sm_100).
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {

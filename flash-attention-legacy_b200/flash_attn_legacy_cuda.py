@@ -17,7 +17,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libfal_b200.so")
+# FAL_B200_LIB selects another build of the same library (e.g. a tuning variant).
+LIB_PATH = os.environ.get("FAL_B200_LIB") or os.path.join(_HERE, "lib", "libfal_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
