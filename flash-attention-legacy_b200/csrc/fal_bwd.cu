@@ -32,6 +32,7 @@
 //               columns of that step's consumed dP^T), dV [256,256+D), dK [256+D,256+2D).
 // Q/dO tiles and their row statistics go through a 3-deep shared-memory ring, and the
 // issuer runs S^T and dP^T one step ahead of the compute warps.
+#define FAL_WAIT_SLOW_PATH_INLINE  // measured: the out-of-line wait path is slower for this kernel
 #include "fal_common.h"
 #include "fal_launch.h"
 #include "sm100_ptx.cuh"

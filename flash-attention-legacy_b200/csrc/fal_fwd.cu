@@ -23,6 +23,7 @@
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
 // P (fp16) overwrites the first 64 columns of its S tile and feeds the PV MMA
 // straight from TMEM.
+#define FAL_WAIT_SLOW_PATH_INLINE  // this kernel uses setmaxnreg, which rules out calls
 #include "fal_common.h"
 #include "fal_launch.h"
 #include "sm100_ptx.cuh"

@@ -76,25 +76,39 @@ struct WaitCtx {
   int* status;               // device status word (may be nullptr)
 };
 
+// Slow path of mbar_wait, kept out of line: the kernels have dozens of wait sites and their hot
+// loops must stay small enough for the instruction cache.
+// (A kernel that re-balances registers with setmaxnreg cannot make calls: it defines
+// FAL_WAIT_SLOW_PATH_INLINE before including this header.)
+#ifdef FAL_WAIT_SLOW_PATH_INLINE
+#define FAL_WAIT_SLOW_ATTR __forceinline__
+#else
+#define FAL_WAIT_SLOW_ATTR __noinline__
+#endif
+static __device__ FAL_WAIT_SLOW_ATTR bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_smem,
+                                            int* status, int barrier_id) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0u) {
+      if (*abort_smem) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_smem = 1;
+        if (status) atomicCAS(status, 0, kDevWaitTimeout + barrier_id);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // Waits for the phase with the given parity to complete.  Returns false when
 // the CTA is aborting; callers carry on (results are then garbage, and the
 // status word says so) so that every thread still reaches the kernel's end.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           int barrier_id) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 255u) == 0u) {
-      if (*ctx.abort_smem) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        *ctx.abort_smem = 1;
-        if (ctx.status) atomicCAS(ctx.status, 0, kDevWaitTimeout + barrier_id);
-        return false;
-      }
-    }
-  }
-  return true;
+  return mbar_wait_slow(bar, parity, ctx.abort_smem, ctx.status, barrier_id);
 }
 
 // ---------------------------------------------------------------------------
@@ -196,6 +210,17 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
