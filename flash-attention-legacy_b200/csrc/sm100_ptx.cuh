@@ -112,7 +112,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 }
 
 // ---------------------------------------------------------------------------
-// TMA (cp.async.bulk.tensor) loads, no multicast anywhere.
+// TMA (cp.async.bulk.tensor) loads: plain single-CTA loads only.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
