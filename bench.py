@@ -54,9 +54,13 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs.
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    Only samples whose timestamp falls inside [mark_begin(), mark_end()] are used, so that idle
+    clocks before and after the timed region do not leak into the median.
+    """
+
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
@@ -64,12 +68,13 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.proc = None
         self.lines = []
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -80,6 +85,20 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
+
+    @staticmethod
+    def _parse_ts(text):
+        import datetime
+        try:
+            return datetime.datetime.strptime(text.strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -88,26 +107,30 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        inside, everything, mx, reasons = [], [], [], set()
         for line in self.lines:
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                clk, clk_max = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        # Samples taken while the GPU was actually busy: the upper half of the observed clocks.
-        sm.sort()
-        busy = sm[len(sm) // 2:] if sm else []
-        med = busy[len(busy) // 2] if busy else None
+            ts = self._parse_ts(parts[0])
+            in_window = (ts is not None and self.t_begin is not None and self.t_end is not None
+                         and self.t_begin - 0.02 <= ts <= self.t_end + 0.02)
+            everything.append(clk)
+            mx.append(clk_max)
+            if in_window:
+                inside.append(clk)
+                for name, val in zip(names, parts[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        used = sorted(inside if inside else everything)
+        med = used[len(used) // 2] if used else None
         return {"sm_mhz": med, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples_in_timed_region": len(inside), "samples_total": len(everything)}
 
 
 def dist_setup(n_gpus):
@@ -155,6 +178,8 @@ def run_reference(args):
     if rank != 0:
         return
     slices_per_step = 1
+    # All the host cores this process may use (torchrun exports OMP_NUM_THREADS=1 by default).
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     for _ in range(min(args.warmup, 1)):
         cpu_baseline_sample(1)
     t_total, tf_list = 0.0, []
@@ -280,13 +305,15 @@ def main():
     time.sleep(0.3)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark_begin()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
+    sampler.mark_end()
     ms_total = e0.elapsed_time(e1)
-    time.sleep(0.2)
+    time.sleep(0.1)
     clocks = sampler.stop()
     fwd_ms, fwd_n = ext.profile_read(ext.KERNEL_FWD)
     bwd_ms, bwd_n = ext.profile_read(ext.KERNEL_BWD)
@@ -356,6 +383,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_extras:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
         tf, dt, threads = cpu_baseline_sample(6)
         cpu_baseline = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
                         "sample": f"6 of 32 (batch, kv-head-group) slices of the same workload, {dt:.1f} s, "
