@@ -76,6 +76,28 @@ int make_tensor_map(CUtensorMap* map, const void* base, int head_dim, int64_t ro
   return FAL_OK;
 }
 
+// fp32 accumulator [batch, head, row, head_dim] (contiguous rows); box = 32 floats x 128 rows,
+// 128-byte swizzle: the shape of one dQ staging box of the backward kernel.
+int make_accum_tensor_map(CUtensorMap* map, const float* base, int head_dim, int64_t padded_rows,
+                          int64_t heads, int64_t batch) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return FAL_ERR_TENSOR_MAP;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(padded_rows),
+                              static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(head_dim) * 4u;
+  const cuuint64_t strides[3] = {row_bytes, row_bytes * padded_rows, row_bytes * padded_rows * heads};
+  const cuuint32_t box[4] = {32u, 128u, 1u, 1u};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = 100000 + static_cast<int>(r);
+    return FAL_ERR_TENSOR_MAP;
+  }
+  return FAL_OK;
+}
+
 fal::RowStrides to_rs(const fal_strides* s) { return fal::RowStrides{s->batch, s->head, s->row}; }
 
 int check_device() {
@@ -118,8 +140,9 @@ struct BwdWorkspace {
 
 BwdWorkspace bwd_workspace_layout(int batch, int heads_q, int rows, int head_dim) {
   BwdWorkspace w;
-  // One extra 64-row tile of slack: packed sequences start at arbitrary rows.
-  w.padded_rows = round_up(rows, 64) + 64;
+  // One extra 128-row tile of slack: packed sequences start at arbitrary rows, and a tile's
+  // reduction may touch (with zeros) up to 127 rows past the last query.
+  w.padded_rows = round_up(rows, 128) + 128;
   w.dq_bytes = static_cast<size_t>(batch) * heads_q * w.padded_rows * head_dim * sizeof(float);
   w.delta_bytes = round_up(static_cast<int64_t>(batch) * heads_q * w.padded_rows * sizeof(float), 256);
   return w;
@@ -340,9 +363,11 @@ int run_bwd(const BwdCall& c) {
   const int64_t acc_head = w.padded_rows * c.head_dim;
   const int64_t acc_batch = acc_head * c.heads_q;
 
-  CUtensorMap tq, tk, tv, tdo;
-  if ((rc = make_tensor_map(&tq, c.q, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_q, 64))) return rc;
-  if ((rc = make_tensor_map(&tdo, c.d_out, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_do, 64)))
+  CUtensorMap tq, tk, tv, tdo, tdq;
+  if ((rc = make_tensor_map(&tq, c.q, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_q, 128))) return rc;
+  if ((rc = make_tensor_map(&tdo, c.d_out, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_do, 128)))
+    return rc;
+  if ((rc = make_accum_tensor_map(&tdq, dq_accum, c.head_dim, w.padded_rows, c.heads_q, c.batch)))
     return rc;
   if ((rc = make_tensor_map(&tk, c.k, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_k, 128))) return rc;
   if ((rc = make_tensor_map(&tv, c.v, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_v, 128))) return rc;
@@ -394,7 +419,8 @@ int run_bwd(const BwdCall& c) {
   const int64_t grid = static_cast<int64_t>(p.num_kvblk) * c.batch * c.heads_kv;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_BWD, c.stream);
-  e = fal::launch_bwd(c.head_dim, c.causal != 0, tq, tk, tv, tdo, p, static_cast<int>(grid), c.stream);
+  e = fal::launch_bwd(c.head_dim, c.causal != 0, tq, tk, tv, tdo, tdq, p, static_cast<int>(grid),
+                      c.stream);
   g_timer.end(FAL_KERNEL_BWD, rec, c.stream);
   if (e != cudaSuccess) return cuda_fail(e);
 

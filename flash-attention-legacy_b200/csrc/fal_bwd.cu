@@ -12,27 +12,27 @@
 //   dK += dS^T Q                   dQ += dS K
 // with P and dS rounded to fp16 before they feed a GEMM.
 //
-// Everything is computed transposed, keys on the 128 TMEM lanes:
-//   S^T  = K Q^T      (M=128 keys, N=64 queries, K=head_dim)   smem x smem
-//   dP^T = V dO^T     (same shape)                             smem x smem
-//   dV  += P^T dO     (M=128, N=head_dim, K=64)                TMEM x smem
-//   dK  += dS^T Q     (M=128, N=head_dim, K=64)                smem x smem
-//   dQ^T = K^T dS^T   (M=head_dim, N=64, K=128)                smem x smem
-// so P^T is produced in place over S^T, each compute thread owns one key row,
-// and dS^T is written to shared memory once and serves both dK and dQ.
-// dQ^T tiles leave through a shared-memory transpose and one bulk fp32
-// add-reduction per tile into the accumulator that the post-pass casts.
+// S, dP, dV and dK are computed transposed (keys on the 128 TMEM lanes), 128 queries per step,
+// so that every MMA is a full M=128 x N=128 instruction (an N=64 instruction costs the same
+// tensor-pipe time as an N=128 one):
+//   S^T  = K Q^T      (M=128 keys, N=128 queries, K=head_dim)   smem x smem
+//   dP^T = V dO^T     (same shape)                              smem x smem
+//   dV  += P^T dO     (M=128, N=head_dim, K=128)                TMEM x smem
+//   dK  += dS^T Q     (M=128, N=head_dim, K=128)                smem x smem
+//   dQ   = dS K       (M=128 queries, N=head_dim, K=128)        smem x smem (dS^T read M-contiguous)
+// P^T is produced in place over S^T, each compute thread owns one key row, and dS^T is
+// written to shared memory once and serves both dK and dQ.  The dQ tile leaves TMEM through
+// a swizzled shared-memory staging buffer and TMA tensor reductions (fp32 add) into the
+// accumulator that the post-pass casts.
 //
-//   warps 0-7    compute (two per TMEM lane quarter, 32 query columns each)
+//   warps 0-7    compute (two per TMEM lane quarter, 64 query columns each)
 //   warp  8      TMA producer, LSE / delta staging
 //   warp  9      tcgen05.mma issuer, TMEM owner
-//   warps 10-13  dQ tile write-back
+//   warps 10-13  dQ write-back
 //
-// TMEM columns: S^T/P^T x2 [0,128), dP^T/dQ^T x2 [128,256) (dQ^T of a step reuses the
-//               columns of that step's consumed dP^T), dV [256,256+D), dK [256+D,256+2D).
-// Q/dO tiles and their row statistics go through a 3-deep shared-memory ring, and the
-// issuer runs S^T and dP^T one step ahead of the compute warps.
-#define FAL_WAIT_SLOW_PATH_INLINE  // measured: the out-of-line wait path is slower for this kernel
+// TMEM columns: S^T/P^T [0,128), dP^T/dQ [128,256) (the dQ tile of a step reuses the columns of
+//               that step's consumed dP^T), dV [256,256+D), dK [256+D,256+2D).
+// Shared memory at head_dim 128: K 32K, V 32K, Q 2 x 32K, dO 32K, dS^T 32K, dQ staging 2 x 16K.
 #include "fal_common.h"
 #include "fal_launch.h"
 #include "sm100_ptx.cuh"
@@ -43,40 +43,42 @@ namespace {
 
 constexpr int kBwdThreads = 448;
 constexpr int kKvTile = 128;
-constexpr int kQTile = 64;
+constexpr int kQTile = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 
 enum BwdBarrier : int {
   kBbKFull = 100, kBbVFull = 101, kBbQFull = 110, kBbDoFull = 120, kBbStatFull = 130,
-  kBbStageEmpty = 140, kBbSReady = 150, kBbDpReady = 160, kBbPReady = 161, kBbDsReady = 162,
-  kBbDsFree = 163, kBbDqReady = 164, kBbDqFree = 165, kBbAllDone = 166,
+  kBbQEmpty = 140, kBbDoEmpty = 145, kBbSReady = 150, kBbDpReady = 160, kBbPReady = 161,
+  kBbDsReady = 162, kBbDqReady = 164, kBbDqFree = 165, kBbAllDone = 166,
 };
 
 template <int D>
 struct BwdSmem {
-  static constexpr int kStages = 3;                            // Q / dO / statistics ring depth
+  static constexpr int kQStages = 2;                           // Q tiles and row statistics
   static constexpr int kBoxes = D / 64;
-  static constexpr int kKvBoxBytes = kKvTile * 128;
-  static constexpr int kKvTileBytes = kBoxes * kKvBoxBytes;
-  static constexpr int kQBoxBytes = kQTile * 128;
-  static constexpr int kQTileBytes = kBoxes * kQBoxBytes;
+  static constexpr int kBoxBytes = 128 * 128;                  // one 128-row x 128-byte box
+  static constexpr int kTileBytes = kBoxes * kBoxBytes;        // K, V, Q and dO tiles are 128 x D
   static constexpr int kKOff = 0;
-  static constexpr int kVOff = kKvTileBytes;
-  static constexpr int kQOff = 2 * kKvTileBytes;
-  static constexpr int kDoOff = kQOff + kStages * kQTileBytes;
-  static constexpr int kDsOff = kDoOff + kStages * kQTileBytes;  // [128 keys][64 queries] fp16
-  static constexpr int kDsBytes = kKvTile * 128;
-  static constexpr int kDqOff = kDsOff + kDsBytes;               // [64 queries][D] fp32
-  static constexpr int kDqBytes = kQTile * D * 4;
-  static constexpr int kStatOff = kDqOff + kDqBytes;             // per stage: lse2[64], delta[64]
-  static constexpr int kStatBytes = kStages * 2 * kQTile * 4;
+  static constexpr int kVOff = kTileBytes;
+  static constexpr int kQOff = 2 * kTileBytes;
+  static constexpr int kDoOff = kQOff + kQStages * kTileBytes;  // single stage
+  static constexpr int kDsOff = kDoOff + kTileBytes;            // [2 boxes][128 keys][64 queries] fp16
+  static constexpr int kDsBytes = 2 * kBoxBytes;
+  static constexpr int kStageOff = kDsOff + kDsBytes;           // dQ staging: 2 x [128 rows][32 fp32]
+  static constexpr int kStageBytes = 2 * kBoxBytes;
+  static constexpr int kStatOff = kStageOff + kStageBytes;      // per Q stage: lse2[128], delta[128]
+  static constexpr int kStatBytes = kQStages * 2 * kQTile * 4;
   static constexpr int kBarOff = kStatOff + kStatBytes;
-  // k_full v_full q_full[3] do_full[3] stat_full[3] stage_empty[3] s_ready[2] dp_ready[2]
-  // dq_ready[2] dq_free[2] p_ready ds_ready ds_free all_done
-  static constexpr int kNumBars = 2 + 4 * kStages + 8 + 4;
+  // k_full v_full q_full[2] q_empty[2] stat_full[2] do_full do_empty
+  // s_ready dp_ready dq_ready dq_free p_ready ds_ready all_done
+  static constexpr int kNumBars = 2 + 6 + 2 + 7;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kBytes = kMiscOff + 16;
-  static constexpr int kAllocBytes = kBytes + 1024;
+  // No slack for re-aligning the base: at head_dim 128 the layout fills the 227 KB limit, so the
+  // kernel requires the dynamic shared memory window itself to be 1024-byte aligned and reports
+  // an error otherwise.
+  static constexpr int kAllocBytes = kBytes;
+  static_assert(kAllocBytes <= 232448, "exceeds the per-CTA shared memory limit");
 };
 
 struct BwdWork {
@@ -139,6 +141,15 @@ __device__ unsigned long long g_bwd_wait_cycles[32];
 #define BWD_TIMING_ONLY(x)
 #endif
 
+// fp32 add-reduction of one swizzled shared-memory box into a 4-D tensor (TMA).
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1,
+                                                  int c2, int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -147,22 +158,25 @@ template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-               const BwdParams p) {
+               const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
   using L = BwdSmem<D>;
+  constexpr int NS = L::kQStages;
 
   BwdWork wk;
   if (!bwd_decode_work(p, wk)) return;
 
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t sbase = smem_u32(smem_raw);
+  uint8_t* sgen = smem_raw;
+  if ((sbase & 1023u) != 0) {  // the 128-byte swizzle needs 1024-byte aligned tiles
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kDevWaitTimeout + 999);
+    return;
+  }
   const uint32_t bar0 = sbase + L::kBarOff;
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  constexpr int NS = L::kStages;
-  constexpr int iKFull = 0, iVFull = 1, iQFull = 2, iDoFull = 2 + NS, iStatFull = 2 + 2 * NS,
-                iStageEmpty = 2 + 3 * NS, iSReady = 2 + 4 * NS, iDpReady = iSReady + 2,
-                iDqReady = iSReady + 4, iDqFree = iSReady + 6, iPReady = iSReady + 8,
-                iDsReady = iSReady + 9, iDsFree = iSReady + 10, iAllDone = iSReady + 11;
+  constexpr int iKFull = 0, iVFull = 1, iQFull = 2, iQEmpty = 4, iStatFull = 6, iDoFull = 8, iDoEmpty = 9,
+                iSReady = 10, iDpReady = 11, iDqReady = 12, iDqFree = 13, iPReady = 14, iDsReady = 15,
+                iAllDone = 16;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kMiscOff + 4);
   const WaitCtx wctx{abort_flag, p.status};
@@ -184,19 +198,17 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(bar(iVFull), 1);
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar(iQFull + s), 1);
-      mbar_init(bar(iDoFull + s), 1);
+      mbar_init(bar(iQEmpty + s), 1);
       mbar_init(bar(iStatFull + s), 32);
-      mbar_init(bar(iStageEmpty + s), 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar(iSReady + s), 1);
-      mbar_init(bar(iDpReady + s), 1);
-      mbar_init(bar(iDqReady + s), 1);
-      mbar_init(bar(iDqFree + s), 128);
-    }
+    mbar_init(bar(iDoFull), 1);
+    mbar_init(bar(iDoEmpty), 1);
+    mbar_init(bar(iSReady), 1);
+    mbar_init(bar(iDpReady), 1);
+    mbar_init(bar(iDqReady), 1);
+    mbar_init(bar(iDqFree), 128);
     mbar_init(bar(iPReady), 256);
     mbar_init(bar(iDsReady), 256);
-    mbar_init(bar(iDsFree), 1);
     mbar_init(bar(iAllDone), 1);
     fence_mbar_init();
   }
@@ -217,34 +229,31 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_do);
-      mbar_arrive_expect_tx(bar(iKFull), L::kKvTileBytes);
+      tma_prefetch_desc(&tm_dq);
+      mbar_arrive_expect_tx(bar(iKFull), L::kTileBytes);
       for (int bx = 0; bx < L::kBoxes; ++bx)
-        tma_load_4d(sbase + L::kKOff + bx * L::kKvBoxBytes, &tm_k, bar(iKFull), bx * 64,
+        tma_load_4d(sbase + L::kKOff + bx * L::kBoxBytes, &tm_k, bar(iKFull), bx * 64,
                     wk.k_row0 + kv0, wk.kv_head, wk.batch);
-      mbar_arrive_expect_tx(bar(iVFull), L::kKvTileBytes);
+      mbar_arrive_expect_tx(bar(iVFull), L::kTileBytes);
       for (int bx = 0; bx < L::kBoxes; ++bx)
-        tma_load_4d(sbase + L::kVOff + bx * L::kKvBoxBytes, &tm_v, bar(iVFull), bx * 64,
+        tma_load_4d(sbase + L::kVOff + bx * L::kBoxBytes, &tm_v, bar(iVFull), bx * 64,
                     wk.k_row0 + kv0, wk.kv_head, wk.batch);
     }
     for (int i = 0; i < n_iter; ++i) {
       const int st = i % NS;
       const int head = wk.kv_head * group + i / nq;
       const int qt = qt0 + i % nq;
-      if (i >= NS) BWD_WAIT(0, bar(iStageEmpty + st), ((i / NS) - 1) & 1, wctx, kBbStageEmpty + st);
+      const int row = wk.q_row0 + qt * kQTile;
+      if (i >= NS) BWD_WAIT(0, bar(iQEmpty + st), ((i / NS) - 1) & 1, wctx, kBbQEmpty + st);
       if (lane == 0) {
-        const int row = wk.q_row0 + qt * kQTile;
-        mbar_arrive_expect_tx(bar(iQFull + st), L::kQTileBytes);
+        mbar_arrive_expect_tx(bar(iQFull + st), L::kTileBytes);
         for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_load_4d(sbase + L::kQOff + st * L::kQTileBytes + bx * L::kQBoxBytes, &tm_q,
+          tma_load_4d(sbase + L::kQOff + st * L::kTileBytes + bx * L::kBoxBytes, &tm_q,
                       bar(iQFull + st), bx * 64, row, head, wk.batch);
-        mbar_arrive_expect_tx(bar(iDoFull + st), L::kQTileBytes);
-        for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_load_4d(sbase + L::kDoOff + st * L::kQTileBytes + bx * L::kQBoxBytes, &tm_do,
-                      bar(iDoFull + st), bx * 64, row, head, wk.batch);
       }
       float* stat = reinterpret_cast<float*>(sgen + L::kStatOff) + st * 2 * kQTile;
 #pragma unroll
-      for (int rr = 0; rr < 2; ++rr) {
+      for (int rr = 0; rr < kQTile / 32; ++rr) {
         const int r = lane + rr * 32;
         const int q_local = qt * kQTile + r;
         float lse2 = INFINITY;  // exp2(x - inf) = 0: rows past the sequence contribute nothing
@@ -260,108 +269,103 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         stat[kQTile + r] = dl;
       }
       mbar_arrive(bar(iStatFull + st));
+      // dO has a single buffer: it is reloaded as soon as dV of the previous step has read it.
+      if (lane == 0) {
+        if (i >= 1) BWD_WAIT(21, bar(iDoEmpty), (i - 1) & 1, wctx, kBbDoEmpty);
+        mbar_arrive_expect_tx(bar(iDoFull), L::kTileBytes);
+        for (int bx = 0; bx < L::kBoxes; ++bx)
+          tma_load_4d(sbase + L::kDoOff + bx * L::kBoxBytes, &tm_do, bar(iDoFull), bx * 64, row, head,
+                      wk.batch);
+      }
+      __syncwarp();
     }
   } else if (warp == 9) {
     // ===================== MMA issuer =========================================
     if (lane == 0 && n_iter > 0) {
       constexpr uint32_t idesc_st = make_idesc_f16(kKvTile, kQTile, 0, 0);   // S^T, dP^T
       constexpr uint32_t idesc_dkv = make_idesc_f16(kKvTile, D, 0, 1);       // dV, dK
-      constexpr uint32_t idesc_dq = make_idesc_f16(128, kQTile, 1, 1);       // dQ^T
+      constexpr uint32_t idesc_dq = make_idesc_f16(kQTile, D, 1, 1);         // dQ = dS K (queries on lanes)
       const uint32_t k_s = sbase + L::kKOff, v_s = sbase + L::kVOff, ds_s = sbase + L::kDsOff;
-
       // Descriptors are stepped with 32-bit adds on their low words (address field = addr >> 4).
       constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
-      const uint32_t k_lo_k = smem_desc_lo(k_s, 16);                    // K as K-major operand
-      const uint32_t v_lo_k = smem_desc_lo(v_s, 16);                    // V as K-major operand
-      const uint32_t k_lo_mn = smem_desc_lo(k_s, L::kKvBoxBytes);       // K^T (MN-major A of dQ^T)
-      const uint32_t ds_lo_k = smem_desc_lo(ds_s, 16);                  // dS^T as K-major A of dK
-      const uint32_t ds_lo_mn = smem_desc_lo(ds_s, 16);                 // dS^T as MN-major B of dQ^T
+      const uint32_t k_lo_k = smem_desc_lo(k_s, 16);                // K as K-major A of S^T
+      const uint32_t v_lo_k = smem_desc_lo(v_s, 16);                // V as K-major A of dP^T
+      const uint32_t k_lo_mn = smem_desc_lo(k_s, L::kBoxBytes);     // K^T, MN-major A of dQ^T
+      const uint32_t ds_lo_k = smem_desc_lo(ds_s, 16);              // dS^T, K-major A of dK
+      const uint32_t ds_lo_mn = smem_desc_lo(ds_s, L::kBoxBytes);   // dS^T, MN-major B of dQ^T
 
-      // acc[128 keys x 64 queries] = X[keys x D] * Y[queries x D]^T, both head_dim-contiguous
+      // acc[128 keys x 128 queries] = X[keys x D] * Y[queries x D]^T, both head_dim-contiguous
       auto issue_xyT = [&](uint32_t d_col, uint32_t x_lo, uint32_t y_s) {
         const uint32_t y_lo = smem_desc_lo(y_s, 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          umma_ss(tmem_base + d_col,
-                  smem_desc_join(x_lo + (((ks >> 2) * L::kKvBoxBytes + (ks & 3) * 32) >> 4), kHi),
-                  smem_desc_join(y_lo + (((ks >> 2) * L::kQBoxBytes + (ks & 3) * 32) >> 4), kHi),
+          const uint32_t off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
+          umma_ss(tmem_base + d_col, smem_desc_join(x_lo + off, kHi), smem_desc_join(y_lo + off, kHi),
                   idesc_st, ks > 0 ? 1u : 0u);
         }
       };
 
-      // S^T and dP^T run one step ahead of the compute warps; each has two TMEM buffers.
       mbar_wait(bar(iKFull), 0, wctx, kBbKFull);
       mbar_wait(bar(iQFull + 0), 0, wctx, kBbQFull);
       tc_fence_after_sync();
       issue_xyT(kColS, k_lo_k, sbase + L::kQOff);
-      tc_commit(bar(iSReady + 0));
+      tc_commit(bar(iSReady));
       mbar_wait(bar(iVFull), 0, wctx, kBbVFull);
-      mbar_wait(bar(iDoFull + 0), 0, wctx, kBbDoFull);
+      mbar_wait(bar(iDoFull), 0, wctx, kBbDoFull);
       tc_fence_after_sync();
       issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff);
-      tc_commit(bar(iDpReady + 0));
+      tc_commit(bar(iDpReady));
+      const uint32_t do_lo_mn = smem_desc_lo(sbase + L::kDoOff, L::kBoxBytes);
 
       for (int i = 0; i < n_iter; ++i) {
         const int st = i % NS;
-        const int sb = i & 1;
         const int st1 = (i + 1) % NS;
-        const int sb1 = (i + 1) & 1;
-        const uint32_t q_lo_mn = smem_desc_lo(sbase + L::kQOff + st * L::kQTileBytes, L::kQBoxBytes);
-        const uint32_t do_lo_mn = smem_desc_lo(sbase + L::kDoOff + st * L::kQTileBytes, L::kQBoxBytes);
-        // S^T(i+1): its buffer held P^T(i-1), which dV(i-1) (issued earlier) has read by then.
-        if (i + 1 < n_iter) {
-          BWD_WAIT(1, bar(iQFull + st1), ((i + 1) / NS) & 1, wctx, kBbQFull + st1);
-          tc_fence_after_sync();
-          BWD_TIMING_ONLY(const long long t_a = clock64();)
-          issue_xyT(kColS + sb1 * kQTile, k_lo_k, sbase + L::kQOff + st1 * L::kQTileBytes);
-          BWD_TIMING_ONLY(tacc[16] += clock64() - t_a;)
-          tc_commit(bar(iSReady + sb1));
-          BWD_TIMING_ONLY(tacc[20] += clock64() - t_a;)
-        }
-        // dV += P^T(i) dO(i): P^T as fp16 in TMEM, query columns [0,32) at +0, [32,64) at +32
+        const uint32_t q_lo_mn = smem_desc_lo(sbase + L::kQOff + st * L::kTileBytes, L::kBoxBytes);
+        // dV += P^T(i) dO(i): P^T as packed fp16 in TMEM; query columns [0,64) at +0, [64,128) at +64
         BWD_WAIT(2, bar(iPReady), i & 1, wctx, kBbPReady);
         tc_fence_after_sync();
-        BWD_TIMING_ONLY(const long long t_b = clock64();)
 #pragma unroll
         for (int ks = 0; ks < kQTile / 16; ++ks) {
-          const uint32_t a_col = kColS + sb * kQTile + (ks >> 1) * 32 + (ks & 1) * 8;
+          const uint32_t a_col = kColS + (ks >> 2) * 64 + (ks & 3) * 8;
           umma_ts(tmem_base + kColDv, tmem_base + a_col,
                   smem_desc_join(do_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dkv,
                   (i > 0 || ks > 0) ? 1u : 0u);
         }
-        BWD_TIMING_ONLY(tacc[17] += clock64() - t_b;)
-        // dP^T(i+1): its buffer last held dQ^T(i-1), which the write-back warps must have drained.
+        tc_commit(bar(iDoEmpty));  // dO(i) has no reader left once dV(i) is done
+        // S^T(i+1) overwrites P^T(i): issued after dV(i), which reads it.
         if (i + 1 < n_iter) {
-          BWD_WAIT(3, bar(iDoFull + st1), ((i + 1) / NS) & 1, wctx, kBbDoFull + st1);
-          if (i >= 1) BWD_WAIT(4, bar(iDqFree + sb1), ((i - 1) >> 1) & 1, wctx, kBbDqFree);
+          BWD_WAIT(3, bar(iQFull + st1), ((i + 1) / NS) & 1, wctx, kBbQFull + st1);
           tc_fence_after_sync();
-          BWD_TIMING_ONLY(const long long t_c = clock64();)
-          issue_xyT(kColDpq + sb1 * kQTile, v_lo_k, sbase + L::kDoOff + st1 * L::kQTileBytes);
-          tc_commit(bar(iDpReady + sb1));
-          BWD_TIMING_ONLY(tacc[18] += clock64() - t_c;)
+          issue_xyT(kColS, k_lo_k, sbase + L::kQOff + st1 * L::kTileBytes);
+          tc_commit(bar(iSReady));
         }
         // dK += dS^T(i) Q(i)
         BWD_WAIT(5, bar(iDsReady), i & 1, wctx, kBbDsReady);
         tc_fence_after_sync();
-        BWD_TIMING_ONLY(const long long t_d = clock64();)
 #pragma unroll
         for (int ks = 0; ks < kQTile / 16; ++ks) {
-          umma_ss(tmem_base + kColDk, smem_desc_join(ds_lo_k + ((ks * 32) >> 4), kHi),
+          const uint32_t a_off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
+          umma_ss(tmem_base + kColDk, smem_desc_join(ds_lo_k + a_off, kHi),
                   smem_desc_join(q_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dkv,
                   (i > 0 || ks > 0) ? 1u : 0u);
         }
-        // dQ^T(i) = K^T dS^T(i), into the columns of the consumed dP^T(i)
+        tc_commit(bar(iQEmpty + st));  // Q(i) has no reader left once dK(i) is done
+        // dQ(i) = dS(i) K: the dS^T buffer read as an M-contiguous A operand; the result (queries on
+        // the lanes, head_dim on the columns) goes into the columns of the consumed dP^T(i)
 #pragma unroll
         for (int ks = 0; ks < kKvTile / 16; ++ks) {
-          umma_ss(tmem_base + kColDpq + sb * kQTile,
-                  smem_desc_join(k_lo_mn + ((ks * 2048) >> 4), kHi),
-                  smem_desc_join(ds_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dq, ks > 0 ? 1u : 0u);
+          umma_ss(tmem_base + kColDpq, smem_desc_join(ds_lo_mn + ((ks * 2048) >> 4), kHi),
+                  smem_desc_join(k_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dq, ks > 0 ? 1u : 0u);
         }
-        BWD_TIMING_ONLY(tacc[19] += clock64() - t_d;)
-        tc_commit(bar(iDqReady + sb));
-        tc_commit(bar(iStageEmpty + st));
-        tc_commit(bar(iDsFree));
-        BWD_TIMING_ONLY(tacc[21] += clock64() - t_d;)
+        tc_commit(bar(iDqReady));  // also tells the compute warps that the dS^T buffer is free again
+        // dP^T(i+1) goes where dQ(i) is: the write-back warps must have read it out first.
+        if (i + 1 < n_iter) {
+          BWD_WAIT(1, bar(iDoFull), (i + 1) & 1, wctx, kBbDoFull);
+          BWD_WAIT(4, bar(iDqFree), i & 1, wctx, kBbDqFree);
+          tc_fence_after_sync();
+          issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff);
+          tc_commit(bar(iDpReady));
+        }
       }
       tc_commit(bar(iAllDone));
     }
@@ -369,88 +373,108 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp < 8) {
     // ===================== compute ============================================
     const int quarter = warp & 3;
-    const int half = warp >> 2;                       // query columns [32*half, 32*half+32)
+    const int half = warp >> 2;                       // query columns [64*half, 64*half+64)
     const int kv_row = quarter * 32 + lane;           // key row inside the tile (= TMEM lane)
     const int kv_local = kv0 + kv_row;
     const bool kv_ok = kv_local < wk.seqlen_k;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c2 = p.scale_log2;
-    uint8_t* ds_row = sgen + L::kDsOff + kv_row * 128;
+    // this thread's dS^T row: box `half` (64 query columns = 128 bytes per key row)
+    uint8_t* ds_row = sgen + L::kDsOff + half * L::kBoxBytes + kv_row * 128;
 
     for (int i = 0; i < n_iter; ++i) {
       const int st = i % NS;
-      const int sb = i & 1;
       const int qt = qt0 + i % nq;
-      const int q_col0 = qt * kQTile + half * 32;  // local query index of this thread's first column
-      const float* stat = reinterpret_cast<const float*>(sgen + L::kStatOff) + st * 2 * kQTile + half * 32;
+      const int q_col0 = qt * kQTile + half * 64;  // local query index of this thread's first column
+      const float* stat = reinterpret_cast<const float*>(sgen + L::kStatOff) + st * 2 * kQTile + half * 64;
       const bool tile_mask = !kv_ok || (CAUSAL && (kv0 + kKvTile - 1 > qt * kQTile));
 
       BWD_WAIT(6, bar(iStatFull + st), (i / NS) & 1, wctx, kBbStatFull + st);
-      BWD_WAIT(7, bar(iSReady + sb), (i >> 1) & 1, wctx, kBbSReady + sb);
+      BWD_WAIT(7, bar(iSReady), i & 1, wctx, kBbSReady);
       tc_fence_after_sync();
       BWD_TIMING_ONLY(const long long t_p0 = clock64();)
 
-      float pv[32];
+      // ---- P^T = exp2(S^T * c2 - lse2), kept as packed fp16 for the dS step ----
+      uint32_t pk[32];
       {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColS + sb * kQTile + half * 32, r);
-        float4 l4[8];  // the statistics load overlaps the TMEM load's latency
-#pragma unroll
-        for (int j = 0; j < 8; ++j) l4[j] = *reinterpret_cast<const float4*>(stat + 4 * j);
+        uint32_t r[2][32];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColS + half * 64, r[0]);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColS + half * 64 + 32, r[1]);
         tmem_wait_ld();
+        BWD_TIMING_ONLY(tacc[16] += clock64() - t_p0; const long long t_p1 = clock64();)
+        if (tile_mask) {  // hidden scores become -inf before the exponential (exp2(-inf) = 0)
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          pv[j + 0] = fast_exp2(fmaf(__uint_as_float(r[j + 0]), c2, -l4[j >> 2].x));
-          pv[j + 1] = fast_exp2(fmaf(__uint_as_float(r[j + 1]), c2, -l4[j >> 2].y));
-          pv[j + 2] = fast_exp2(fmaf(__uint_as_float(r[j + 2]), c2, -l4[j >> 2].z));
-          pv[j + 3] = fast_exp2(fmaf(__uint_as_float(r[j + 3]), c2, -l4[j >> 2].w));
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const bool vis = kv_ok && (!CAUSAL || kv_local <= q_col0 + c * 32 + j);
+              r[c][j] = vis ? r[c][j] : 0xff800000u;
+            }
         }
-        if (tile_mask) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const bool vis = kv_ok && (!CAUSAL || kv_local <= q_col0 + j);
-            pv[j] = vis ? pv[j] : 0.f;
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(stat + c * 32 + j);
+#ifdef FAL_BWD_EXP_F16X2
+            // exponent rounded to fp16 first, two exponentials per MUFU instruction
+            pk[c * 16 + (j >> 1) + 0] = exp2_f16x2(pack_half2(fmaf(__uint_as_float(r[c][j + 0]), c2, -l4.x),
+                                                              fmaf(__uint_as_float(r[c][j + 1]), c2, -l4.y)));
+            pk[c * 16 + (j >> 1) + 1] = exp2_f16x2(pack_half2(fmaf(__uint_as_float(r[c][j + 2]), c2, -l4.z),
+                                                              fmaf(__uint_as_float(r[c][j + 3]), c2, -l4.w)));
+#else
+            const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][j + 0]), c2, -l4.x));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][j + 1]), c2, -l4.y));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(r[c][j + 2]), c2, -l4.z));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(r[c][j + 3]), c2, -l4.w));
+            pk[c * 16 + (j >> 1) + 0] = pack_half2(p0, p1);
+            pk[c * 16 + (j >> 1) + 1] = pack_half2(p2, p3);
+#endif
           }
         }
-        uint32_t pk[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) pk[j] = pack_half2(pv[2 * j], pv[2 * j + 1]);
-        // P^T overwrites this thread's own S^T columns: [32*half, 32*half+16)
-        tmem_st_32x32b_x16(tmem_base + lane_addr + kColS + sb * kQTile + half * 32, pk);
+        // P^T overwrites this thread's own S^T columns: 32 packed columns at [64*half, 64*half+32)
+        BWD_TIMING_ONLY(tacc[17] += clock64() - t_p1; const long long t_p2 = clock64();)
+        tmem_st_32x32b_x32(tmem_base + lane_addr + kColS + half * 64, pk);
         tmem_wait_st();
+        BWD_TIMING_ONLY(tacc[18] += clock64() - t_p2;)
       }
       tc_fence_before_sync();
       mbar_arrive(bar(iPReady));
       BWD_TIMING_ONLY(tacc[22] += clock64() - t_p0;)
 
-      BWD_WAIT(8, bar(iDpReady + sb), (i >> 1) & 1, wctx, kBbDpReady);
+      // ---- dS^T = P^T o (dP^T - delta) ------------------------------------------
+      BWD_WAIT(8, bar(iDpReady), i & 1, wctx, kBbDpReady);
       tc_fence_after_sync();
       BWD_TIMING_ONLY(const long long t_s0 = clock64();)
-      uint32_t dsp[16];
+      uint32_t dsp[32];
       {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + sb * kQTile + half * 32, r);
-        float4 d4s[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) d4s[j] = *reinterpret_cast<const float4*>(stat + kQTile + 4 * j);
+        uint32_t r[2][32];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + half * 64, r[0]);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + half * 64 + 32, r[1]);
         tmem_wait_ld();
+        BWD_TIMING_ONLY(tacc[19] += clock64() - t_s0;)
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 d4 = d4s[j >> 2];
-          const float a0 = pv[j + 0] * (__uint_as_float(r[j + 0]) - d4.x);
-          const float a1 = pv[j + 1] * (__uint_as_float(r[j + 1]) - d4.y);
-          const float a2 = pv[j + 2] * (__uint_as_float(r[j + 2]) - d4.z);
-          const float a3 = pv[j + 3] * (__uint_as_float(r[j + 3]) - d4.w);
-          dsp[(j >> 1) + 0] = pack_half2(a0, a1);
-          dsp[(j >> 1) + 1] = pack_half2(a2, a3);
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 d4 = *reinterpret_cast<const float4*>(stat + kQTile + c * 32 + j);
+            const float2 pa = __half22float2(*reinterpret_cast<const __half2*>(&pk[c * 16 + (j >> 1)]));
+            const float2 pb = __half22float2(*reinterpret_cast<const __half2*>(&pk[c * 16 + (j >> 1) + 1]));
+            const float a0 = pa.x * (__uint_as_float(r[c][j + 0]) - d4.x);
+            const float a1 = pa.y * (__uint_as_float(r[c][j + 1]) - d4.y);
+            const float a2 = pb.x * (__uint_as_float(r[c][j + 2]) - d4.z);
+            const float a3 = pb.y * (__uint_as_float(r[c][j + 3]) - d4.w);
+            dsp[c * 16 + (j >> 1) + 0] = pack_half2(a0, a1);
+            dsp[c * 16 + (j >> 1) + 1] = pack_half2(a2, a3);
+          }
         }
       }
-      if (i > 0) BWD_WAIT(9, bar(iDsFree), (i - 1) & 1, wctx, kBbDsFree);
+      BWD_TIMING_ONLY(tacc[20] += clock64() - t_s0;)
+      if (i > 0) BWD_WAIT(9, bar(iDqReady), (i - 1) & 1, wctx, kBbDqReady);
       // dS^T row -> shared memory, 128-byte XOR swizzle (16-byte chunk index ^ row % 8)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int chunk = half * 4 + c;
-        *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (kv_row & 7)) << 4)) =
+      for (int c = 0; c < 8; ++c) {
+        *reinterpret_cast<uint4*>(ds_row + ((c ^ (kv_row & 7)) << 4)) =
             make_uint4(dsp[4 * c + 0], dsp[4 * c + 1], dsp[4 * c + 2], dsp[4 * c + 3]);
       }
       fence_proxy_async_smem();
@@ -495,53 +519,53 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
   } else {
     // ===================== dQ write-back ======================================
+    // dQ tile: TMEM lane = query row, column = head_dim.  It leaves in 64-column halves.  For each
+    // half a thread reads its row's 64 values, writes them as two 32-float slices into the two
+    // swizzled [128 rows][128 bytes] staging boxes, and one thread issues two TMA tensor reductions
+    // that add the boxes to the fp32 accumulator.  The second half is pulled into registers (and the
+    // TMEM columns handed back to the issuer) before waiting for the first half's reductions.
     const int quarter = warp & 3;
-    const int drow = quarter * 32 + lane;  // head_dim index = TMEM lane of dQ^T
+    const int qrow = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    // The 64-row tile leaves in two 32-row halves, each with its own staging buffer, so that
-    // the bulk reduction of one half reads shared memory while the other half is being written.
-    float* stage_half[2] = {reinterpret_cast<float*>(sgen + L::kDqOff),
-                            reinterpret_cast<float*>(sgen + L::kDqOff) + (kQTile / 2) * D};
     const bool issuer = warp == 10 && lane == 0;
+    uint8_t* box_row = sgen + L::kStageOff + qrow * 128;
     for (int i = 0; i < n_iter; ++i) {
       const int head = wk.kv_head * group + i / nq;
       const int qt = qt0 + i % nq;
-      const int sb = i & 1;
-      BWD_WAIT(10, bar(iDqReady + sb), (i >> 1) & 1, wctx, kBbDqReady);
+      BWD_WAIT(10, bar(iDqReady), i & 1, wctx, kBbDqReady);
       tc_fence_after_sync();
-      uint32_t r[2][32];
-      tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + sb * kQTile, r[0]);
-      tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + sb * kQTile + 32, r[1]);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(bar(iDqFree + sb));
       BWD_TIMING_ONLY(const long long t_red0 = clock64();)
-      float* dst_tile = p.dq_accum + wk.batch * p.dq_accum_batch_stride + head * p.dq_accum_head_stride +
-                        (static_cast<int64_t>(wk.q_row0) + qt * kQTile) * D;
+      const int grow = wk.q_row0 + qt * kQTile;  // accumulator row of the tile's first query
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        // The reduction that last read this half's buffer (two groups ago) must be done with it.
-        if (issuer) bulk_wait_group_read<1>();
-        named_barrier_sync(1, 128);
-        if (drow < D) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) stage_half[hf][j * D + drow] = __uint_as_float(r[hf][j]);
+      for (int hf = 0; hf < D / 64; ++hf) {
+        uint32_t r[2][32];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + hf * 64, r[0]);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + hf * 64 + 32, r[1]);
+        tmem_wait_ld();
+        if (hf == D / 64 - 1) {  // everything is in registers: the issuer may overwrite the columns
+          tc_fence_before_sync();
+          mbar_arrive(bar(iDqFree));
         }
+        // Earlier reductions must be done reading the staging boxes.
+        if (issuer) bulk_wait_group_read<0>();
+        named_barrier_sync(1, 128);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            *reinterpret_cast<uint4*>(box_row + c * L::kBoxBytes + ((v ^ (qrow & 7)) << 4)) =
+                make_uint4(r[c][4 * v + 0], r[c][4 * v + 1], r[c][4 * v + 2], r[c][4 * v + 3]);
         fence_proxy_async_smem();
         named_barrier_sync(1, 128);
         if (issuer) {
-          const int rows = min(kQTile / 2, wk.seqlen_q - qt * kQTile - hf * (kQTile / 2));
-          if (rows > 0) {
-            bulk_reduce_add_f32(dst_tile + hf * (kQTile / 2) * D,
-                                sbase + L::kDqOff + hf * (kQTile / 2) * D * 4,
-                                static_cast<uint32_t>(rows) * D * 4u);
-          }
-          bulk_commit_group();  // one group per half, empty or not: keeps the group count uniform
+          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff, hf * 64, grow, head, wk.batch);
+          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff + L::kBoxBytes, hf * 64 + 32, grow, head, wk.batch);
+          bulk_commit_group();
         }
       }
       BWD_TIMING_ONLY(tacc[11] += clock64() - t_red0;)
     }
-    if (warp == 10 && lane == 0) bulk_wait_group0();
+    if (issuer) bulk_wait_group0();
   }
 
 #ifdef FAL_BWD_TIMING
@@ -649,7 +673,8 @@ __global__ void __launch_bounds__(256) fal_bwd_post_kernel(const BwdPostParams p
 
 template <int D, bool CAUSAL>
 cudaError_t launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const CUtensorMap& tdo, const BwdParams& p, int grid, cudaStream_t stream) {
+                         const CUtensorMap& tdo, const CUtensorMap& tdq, const BwdParams& p, int grid,
+                         cudaStream_t stream) {
   auto kern = fal_bwd_kernel<D, CAUSAL>;
   static DeviceOnce configured;
   cudaError_t e = configured.run([&] {
@@ -657,7 +682,7 @@ cudaError_t launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
                                 BwdSmem<D>::kAllocBytes);
   });
   if (e != cudaSuccess) return e;
-  kern<<<grid, kBwdThreads, BwdSmem<D>::kAllocBytes, stream>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, kBwdThreads, BwdSmem<D>::kAllocBytes, stream>>>(tq, tk, tv, tdo, tdq, p);
   return cudaGetLastError();
 }
 
@@ -682,15 +707,15 @@ cudaError_t launch_bwd_prep(const BwdPrepParams& p, cudaStream_t stream) {
 }
 
 cudaError_t launch_bwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const CUtensorMap& tdo, const BwdParams& p, int grid,
-                       cudaStream_t stream) {
+                       const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq,
+                       const BwdParams& p, int grid, cudaStream_t stream) {
   if (head_dim == 128) {
-    return causal ? launch_bwd_t<128, true>(tq, tk, tv, tdo, p, grid, stream)
-                  : launch_bwd_t<128, false>(tq, tk, tv, tdo, p, grid, stream);
+    return causal ? launch_bwd_t<128, true>(tq, tk, tv, tdo, tdq, p, grid, stream)
+                  : launch_bwd_t<128, false>(tq, tk, tv, tdo, tdq, p, grid, stream);
   }
   if (head_dim == 64) {
-    return causal ? launch_bwd_t<64, true>(tq, tk, tv, tdo, p, grid, stream)
-                  : launch_bwd_t<64, false>(tq, tk, tv, tdo, p, grid, stream);
+    return causal ? launch_bwd_t<64, true>(tq, tk, tv, tdo, tdq, p, grid, stream)
+                  : launch_bwd_t<64, false>(tq, tk, tv, tdo, tdq, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

@@ -60,9 +60,10 @@ struct BwdPrepParams {
 cudaError_t launch_bwd_prep(const BwdPrepParams& p, cudaStream_t stream);
 
 // Backward main kernel: grid = number of (128-key block, batch*kv_head) units.
+// tdq: fp32 tensor map of the dQ accumulator (head_dim, padded rows, heads, batch), 32 x 128 boxes.
 cudaError_t launch_bwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const CUtensorMap& tdo, const BwdParams& p, int grid,
-                       cudaStream_t stream);
+                       const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq,
+                       const BwdParams& p, int grid, cudaStream_t stream);
 
 // Backward post-pass: dQ = fp16(scale * dq_accum).
 struct BwdPostParams {

@@ -342,6 +342,13 @@ __device__ __forceinline__ float exp2_fma(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
+// Two exponentials per instruction on packed fp16 (input and result are half2 bit patterns).
+__device__ __forceinline__ uint32_t exp2_f16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
 // Three-input maximum (one instruction on sm_100).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;

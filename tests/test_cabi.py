@@ -53,8 +53,8 @@ def test_strerror_and_version(lib):
 def test_workspace_sizes(lib):
     lib.fal_bwd_workspace_bytes.restype = ctypes.c_size_t
     lib.fal_decode_workspace_bytes.restype = ctypes.c_size_t
-    # rows padded to a multiple of 64 plus one spare tile; fp32 accumulator + fp32 delta
-    rows = 4096 + 64
+    # rows padded to a multiple of 128 plus one spare 128-row tile; fp32 accumulator + fp32 delta
+    rows = 4096 + 128
     expect = 4 * 32 * rows * 128 * 4 + 4 * 32 * rows * 4
     assert lib.fal_bwd_workspace_bytes(4, 32, 4096, 128) == expect
     assert lib.fal_bwd_workspace_bytes(0, 32, 4096, 128) == 0
