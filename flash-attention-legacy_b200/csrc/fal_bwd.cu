@@ -26,9 +26,12 @@
 // accumulator that the post-pass casts.
 //
 //   warps 0-7    compute (two per TMEM lane quarter, 64 query columns each)
-//   warp  8      TMA producer, LSE / delta staging
+//   warp  8      TMA producer
 //   warp  9      tcgen05.mma issuer, TMEM owner
 //   warps 10-13  dQ write-back
+//   warp  14     LSE / delta staging (kept apart from the TMA producer so that neither waits
+//                behind the other's global-memory latency)
+//   warp  15     idle
 //
 // TMEM columns: S^T/P^T [0,128), dP^T/dQ [128,256) (the dQ tile of a step reuses the columns of
 //               that step's consumed dP^T), dV [256,256+D), dK [256+D,256+2D).
@@ -41,7 +44,7 @@ namespace fal {
 
 namespace {
 
-constexpr int kBwdThreads = 448;
+constexpr int kBwdThreads = 512;
 constexpr int kKvTile = 128;
 constexpr int kQTile = 128;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -124,6 +127,17 @@ __device__ __forceinline__ bool bwd_decode_work(const BwdParams& p, BwdWork& w) 
     first += nblk;
   }
   return false;
+}
+
+// Of every 8 consecutive score columns, this many take the FMA-pipe exp2 instead of the
+// special-function unit (two compute warps per scheduler share 4 ex2 lanes per clock).
+#ifndef FAL_BWD_EXP_EMU_PER8
+#define FAL_BWD_EXP_EMU_PER8 0
+#endif
+template <int K>
+__device__ __forceinline__ float bwd_exp2(int j, float x) {
+  // j is a multiple of 4 under full unrolling, so the choice folds at compile time.
+  return (((j + K) & 7) < FAL_BWD_EXP_EMU_PER8) ? exp2_fma(x) : fast_exp2(x);
 }
 
 // Tuning aid, compiled in only with -DFAL_BWD_TIMING: cycles each role spends in each wait.
@@ -251,6 +265,23 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tma_load_4d(sbase + L::kQOff + st * L::kTileBytes + bx * L::kBoxBytes, &tm_q,
                       bar(iQFull + st), bx * 64, row, head, wk.batch);
       }
+      // dO has a single buffer: it is reloaded as soon as dV of the previous step has read it.
+      if (lane == 0) {
+        if (i >= 1) BWD_WAIT(21, bar(iDoEmpty), (i - 1) & 1, wctx, kBbDoEmpty);
+        mbar_arrive_expect_tx(bar(iDoFull), L::kTileBytes);
+        for (int bx = 0; bx < L::kBoxes; ++bx)
+          tma_load_4d(sbase + L::kDoOff + bx * L::kBoxBytes, &tm_do, bar(iDoFull), bx * 64, row, head,
+                      wk.batch);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 14) {
+    // ===================== per-row statistics: lse * log2(e) and delta ========
+    for (int i = 0; i < n_iter; ++i) {
+      const int st = i % NS;
+      const int head = wk.kv_head * group + i / nq;
+      const int qt = qt0 + i % nq;
+      if (i >= NS) mbar_wait(bar(iQEmpty + st), ((i / NS) - 1) & 1, wctx, kBbQEmpty + st);
       float* stat = reinterpret_cast<float*>(sgen + L::kStatOff) + st * 2 * kQTile;
 #pragma unroll
       for (int rr = 0; rr < kQTile / 32; ++rr) {
@@ -269,15 +300,6 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         stat[kQTile + r] = dl;
       }
       mbar_arrive(bar(iStatFull + st));
-      // dO has a single buffer: it is reloaded as soon as dV of the previous step has read it.
-      if (lane == 0) {
-        if (i >= 1) BWD_WAIT(21, bar(iDoEmpty), (i - 1) & 1, wctx, kBbDoEmpty);
-        mbar_arrive_expect_tx(bar(iDoFull), L::kTileBytes);
-        for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_load_4d(sbase + L::kDoOff + bx * L::kBoxBytes, &tm_do, bar(iDoFull), bx * 64, row, head,
-                      wk.batch);
-      }
-      __syncwarp();
     }
   } else if (warp == 9) {
     // ===================== MMA issuer =========================================
@@ -423,10 +445,10 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             pk[c * 16 + (j >> 1) + 1] = exp2_f16x2(pack_half2(fmaf(__uint_as_float(r[c][j + 2]), c2, -l4.z),
                                                               fmaf(__uint_as_float(r[c][j + 3]), c2, -l4.w)));
 #else
-            const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][j + 0]), c2, -l4.x));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][j + 1]), c2, -l4.y));
-            const float p2 = fast_exp2(fmaf(__uint_as_float(r[c][j + 2]), c2, -l4.z));
-            const float p3 = fast_exp2(fmaf(__uint_as_float(r[c][j + 3]), c2, -l4.w));
+            const float p0 = bwd_exp2<0>(j, fmaf(__uint_as_float(r[c][j + 0]), c2, -l4.x));
+            const float p1 = bwd_exp2<1>(j, fmaf(__uint_as_float(r[c][j + 1]), c2, -l4.y));
+            const float p2 = bwd_exp2<2>(j, fmaf(__uint_as_float(r[c][j + 2]), c2, -l4.z));
+            const float p3 = bwd_exp2<3>(j, fmaf(__uint_as_float(r[c][j + 3]), c2, -l4.w));
             pk[c * 16 + (j >> 1) + 0] = pack_half2(p0, p1);
             pk[c * 16 + (j >> 1) + 1] = pack_half2(p2, p3);
 #endif
@@ -457,15 +479,13 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
+            // (dP - delta) in fp32 (it cancels), rounded to fp16, then one packed multiply by the
+            // fp16 P: the product is the fp16 dS the GEMMs consume.
             const float4 d4 = *reinterpret_cast<const float4*>(stat + kQTile + c * 32 + j);
-            const float2 pa = __half22float2(*reinterpret_cast<const __half2*>(&pk[c * 16 + (j >> 1)]));
-            const float2 pb = __half22float2(*reinterpret_cast<const __half2*>(&pk[c * 16 + (j >> 1) + 1]));
-            const float a0 = pa.x * (__uint_as_float(r[c][j + 0]) - d4.x);
-            const float a1 = pa.y * (__uint_as_float(r[c][j + 1]) - d4.y);
-            const float a2 = pb.x * (__uint_as_float(r[c][j + 2]) - d4.z);
-            const float a3 = pb.y * (__uint_as_float(r[c][j + 3]) - d4.w);
-            dsp[c * 16 + (j >> 1) + 0] = pack_half2(a0, a1);
-            dsp[c * 16 + (j >> 1) + 1] = pack_half2(a2, a3);
+            const uint32_t e0 = pack_half2(__uint_as_float(r[c][j + 0]) - d4.x, __uint_as_float(r[c][j + 1]) - d4.y);
+            const uint32_t e1 = pack_half2(__uint_as_float(r[c][j + 2]) - d4.z, __uint_as_float(r[c][j + 3]) - d4.w);
+            dsp[c * 16 + (j >> 1) + 0] = hmul2_bits(pk[c * 16 + (j >> 1) + 0], e0);
+            dsp[c * 16 + (j >> 1) + 1] = hmul2_bits(pk[c * 16 + (j >> 1) + 1], e1);
           }
         }
       }
@@ -517,7 +537,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
     }
-  } else {
+  } else if (warp < 14) {
     // ===================== dQ write-back ======================================
     // dQ tile: TMEM lane = query row, column = head_dim.  It leaves in 64-column halves.  For each
     // half a thread reads its row's 64 values, writes them as two 32-float slices into the two

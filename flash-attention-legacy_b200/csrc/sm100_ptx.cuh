@@ -349,6 +349,13 @@ __device__ __forceinline__ uint32_t exp2_f16x2(uint32_t x) {
   return y;
 }
 
+// Packed fp16 multiply on half2 bit patterns.
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // Three-input maximum (one instruction on sm_100).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
