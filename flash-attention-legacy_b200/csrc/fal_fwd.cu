@@ -89,7 +89,8 @@ struct FwdSmem {
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kBarOff = kVOff + kStages * kTileBytes;
   // barriers: q_full[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_ready[2] p_ready[2] o_done[2]
-  static constexpr int kNumBars = 2 + 4 * kStages + 6;
+  //           p_half[2]
+  static constexpr int kNumBars = 2 + 4 * kStages + 8;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
   static constexpr int kBytes = kMiscOff + 16;
   static constexpr int kAllocBytes = kBytes + 1024;  // room to align the base to 1024
@@ -173,7 +174,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t bar0 = sbase + L::kBarOff;
   auto bar = [&](int i) { return bar0 + 8u * i; };
   const int iQFull = 0, iKFull = 2, iKEmpty = 2 + NS, iVFull = 2 + 2 * NS, iVEmpty = 2 + 3 * NS,
-            iSReady = 2 + 4 * NS, iPReady = iSReady + 2, iODone = iSReady + 4;
+            iSReady = 2 + 4 * NS, iPReady = iSReady + 2, iODone = iSReady + 4, iPHalf = iSReady + 6;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kMiscOff + 4);
   const WaitCtx wctx{abort_flag, p.status};
@@ -210,6 +211,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int w = 0; w < 2; ++w) {
       mbar_init(bar(iSReady + w), 1);
       mbar_init(bar(iPReady + w), kTileM);
+      mbar_init(bar(iPHalf + w), kTileM);
       mbar_init(bar(iODone + w), 1);
     }
     fence_mbar_init();
@@ -281,10 +283,11 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // O[w] += P[w] V_j : A = P from TMEM (8 columns of packed fp16 per 16 keys), B = V
       // MN-major (head_dim contiguous): 16 keys = 2048 bytes per step, 64-column halves
       // kBoxBytes apart (LBO), 8-key groups 1024 bytes apart (SBO).
-      auto issue_pv = [&](int w, int j) {
+      auto issue_pv = [&](int w, int j, int half) {
         const uint32_t v_lo = smem_desc_lo(sbase + L::kVOff + (j % NS) * L::kTileBytes, L::kBoxBytes);
 #pragma unroll
-        for (int ks = 0; ks < kTileN / 16; ++ks) {
+        for (int kk = 0; kk < kTileN / 32; ++kk) {
+          const int ks = half * (kTileN / 32) + kk;
           umma_ts(tmem_base + 256 + w * D, tmem_base + w * kTileN + ks * 8,
                   smem_desc_join(v_lo + ((ks * 2048) >> 4), kHi), idesc_pv,
                   (j > 0 || ks > 0) ? 1u : 0u);
@@ -307,10 +310,15 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int use = j / NS;
         for (int w = 0; w < 2; ++w) {
           if (j >= ntile[w]) continue;
-          mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w);
+          // P arrives in two halves of 64 keys, so that PV starts while the softmax warps are
+          // still exponentiating the second half.
+          mbar_wait(bar(iPHalf + w), j & 1, wctx, kBarPReady + w);
           mbar_wait(bar(iVFull + s), use & 1, wctx, kBarVFull + s);
           tc_fence_after_sync();
-          issue_pv(w, j);
+          issue_pv(w, j, 0);
+          mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w);
+          tc_fence_after_sync();
+          issue_pv(w, j, 1);
           tc_commit(bar(iODone + w));
           if (w == 1 || j >= ntile[1]) tc_commit(bar(iVEmpty + s));
           if (j + 1 < ntile[w]) {
@@ -430,6 +438,11 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           pk[(i >> 1) + 1] = pack_half2(p2, p3);
         }
         tmem_st_32x32b_x16(tS + c * 16, pk);
+        if (c == 1) {  // the first 64 keys of P are in TMEM: the PV MMA may start on them
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar(iPHalf + wg));
+        }
       }
       const float sum_lo = sum0 + sum1, sum_hi = sum2 + sum3;
       const float sum01 = sum_lo + sum_hi;
