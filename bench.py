@@ -242,6 +242,67 @@ def run_decode_extra(ext, peaks, steps=256, batch=64):
     return res
 
 
+def run_long_context(args, rank, world, local, dist, ext):
+    """Secondary metric: one 131072-token causal sequence, forward + backward, context parallel.
+
+    Rank r holds rows [r*N/G, (r+1)*N/G).  With one rank the kernels run on the whole sequence; with
+    more, K/V shards travel the ring (NCCL point-to-point) while the kernels work on the shard already
+    present.  Contiguous shards under a causal mask are unbalanced: rank r has r+1 shard pairs to do,
+    so the time is set by the last rank.
+    """
+    from flash_attn_legacy import distributed as fd
+    B, Hq, Hkv, N, d = 1, 32, 8, 131072, 128
+    scale = 1.0 / math.sqrt(d)
+    dev = torch.device("cuda", local)
+    lo, hi = fd.shard_range(N, world, rank)
+    n_local = hi - lo
+    gen = torch.Generator(device="cuda").manual_seed(4 + rank)
+    q = torch.randn(B, Hq, n_local, d, device=dev, generator=gen).half()
+    k = torch.randn(B, Hkv, n_local, d, device=dev, generator=gen).half()
+    v = torch.randn(B, Hkv, n_local, d, device=dev, generator=gen).half()
+    do = torch.randn(B, Hq, n_local, d, device=dev, generator=gen).half()
+
+    def step():
+        if world == 1:
+            o, lse = ext.forward(q, k, v, scale, True)
+            return ext.backward(do, q, k, v, o, lse, scale, True)
+        o, lse = fd.ring_attention_forward(q, k, v, scale, True)
+        return fd.ring_attention_backward(do, q, k, v, o, lse, scale, True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    barrier()
+    steps = max(1, min(args.steps, 5))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    flops = 3.5 * 4.0 * B * Hq * N * N * d * 0.5
+    status = ext.device_status()
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": steps, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "long_context_B1_Hq32_Hkv8_N131072_d128_causal_fwd_bwd",
+                       "parallelism": f"contiguous sequence shards over {world} rank(s), ring K/V exchange"},
+            "device_status": status}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -249,6 +310,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and decode extras")
+    ap.add_argument("--workload", default="gqa_fwd_bwd", choices=["gqa_fwd_bwd", "long_context"],
+                    help="long_context: B=1 Hq=32 Hkv=8 N=131072 d=128 causal forward+backward, the sequence "
+                         "sharded contiguously over the ranks with the ring K/V exchange (secondary metric)")
     ap.add_argument("--decode-profile", action="store_true",
                     help="run only a small decode case (batch 16, a few steps): the case profilers capture")
     args = ap.parse_args()
@@ -263,6 +327,10 @@ def main():
     rank, world, local, dist = dist_setup(args.gpus)
     import flash_attn_legacy_cuda as ext
     import flash_attn_legacy as fal
+
+    if args.workload == "long_context":
+        run_long_context(args, rank, world, local, dist, ext)
+        return
 
     if args.decode_profile:
         res = run_decode_extra(ext, measured_peaks(), steps=max(args.steps, 4), batch=16)
