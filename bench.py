@@ -245,10 +245,11 @@ def run_decode_extra(ext, peaks, steps=256, batch=64):
 def run_long_context(args, rank, world, local, dist, ext):
     """Secondary metric: one 131072-token causal sequence, forward + backward, context parallel.
 
-    Rank r holds rows [r*N/G, (r+1)*N/G).  With one rank the kernels run on the whole sequence; with
-    more, K/V shards travel the ring (NCCL point-to-point) while the kernels work on the shard already
-    present.  Contiguous shards under a causal mask are unbalanced: rank r has r+1 shard pairs to do,
-    so the time is set by the last rank.
+    With one rank the kernels run on the whole sequence; with more, K/V shards travel the ring (NCCL
+    point-to-point) while the kernels work on the shard already present.  Layout "zigzag" (default):
+    the sequence is cut into 2G chunks, rank r holds chunks r and 2G-1-r, every rank does the same
+    work in every ring step.  Layout "contiguous": rank r holds rows [r*N/G, (r+1)*N/G) and has r+1
+    shard pairs to do under the causal mask, so the last rank sets the time.
     """
     from flash_attn_legacy import distributed as fd
     B, Hq, Hkv, N, d = 1, 32, 8, 131072, 128
@@ -266,8 +267,8 @@ def run_long_context(args, rank, world, local, dist, ext):
         if world == 1:
             o, lse = ext.forward(q, k, v, scale, True)
             return ext.backward(do, q, k, v, o, lse, scale, True)
-        o, lse = fd.ring_attention_forward(q, k, v, scale, True)
-        return fd.ring_attention_backward(do, q, k, v, o, lse, scale, True)
+        o, lse = fd.ring_attention_forward(q, k, v, scale, True, layout=args.ring_layout)
+        return fd.ring_attention_backward(do, q, k, v, o, lse, scale, True, layout=args.ring_layout)
 
     def barrier():
         if dist is not None:
@@ -297,7 +298,8 @@ def run_long_context(args, rank, world, local, dist, ext):
             "steps": steps, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": "long_context_B1_Hq32_Hkv8_N131072_d128_causal_fwd_bwd",
-                       "parallelism": f"contiguous sequence shards over {world} rank(s), ring K/V exchange"},
+                       "parallelism": f"{args.ring_layout} sequence shards over {world} rank(s), ring K/V exchange"
+                                      if world > 1 else "one rank, whole sequence"},
             "device_status": status}))
     if dist is not None:
         dist.destroy_process_group()
@@ -313,6 +315,8 @@ def main():
     ap.add_argument("--workload", default="gqa_fwd_bwd", choices=["gqa_fwd_bwd", "long_context"],
                     help="long_context: B=1 Hq=32 Hkv=8 N=131072 d=128 causal forward+backward, the sequence "
                          "sharded contiguously over the ranks with the ring K/V exchange (secondary metric)")
+    ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"],
+                    help="long_context with more than one rank: how the sequence rows are dealt to the ranks")
     ap.add_argument("--decode-profile", action="store_true",
                     help="run only a small decode case (batch 16, a few steps): the case profilers capture")
     args = ap.parse_args()

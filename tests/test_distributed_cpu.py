@@ -46,7 +46,7 @@ def _oracle_bwd(d_out, q, k, v, o, lse, scale, causal):
     return dq, dk, dv
 
 
-def _ring_worker(rank, world, port, causal, results):
+def _ring_worker(rank, world, port, causal, results, layout="contiguous"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -58,16 +58,24 @@ def _ring_worker(rank, world, port, causal, results):
         torch.manual_seed(0)
         B, Hq, Hkv, N, d = 1, 4, 2, 24 * world, 16
         q, k, v, g = torch.randn(B, Hq, N, d), torch.randn(B, Hkv, N, d), torch.randn(B, Hkv, N, d), torch.randn(B, Hq, N, d)
-        lo, hi = fd.shard_range(N, world, rank)
-        sl = slice(lo, hi)
-        o, lse = fd.ring_attention_forward(q[:, :, sl], k[:, :, sl], v[:, :, sl], 0.25, causal, None, _oracle_fwd)
+        if layout == "zigzag":
+            def take(x):
+                return fd.zigzag_take(x, world, rank)
+        else:
+            lo, hi = fd.shard_range(N, world, rank)
+
+            def take(x):
+                return x[:, :, lo:hi]
+        # contiguous local tensors, reused by both calls: the exchange must leave them as they are
+        ql, kl, vl, gl = (take(x).contiguous() for x in (q, k, v, g))
+        o, lse = fd.ring_attention_forward(ql, kl, vl, 0.25, causal, None, _oracle_fwd, layout)
         o_ref, lse_ref = orc.attention_fwd(q, k, v, 0.25, causal)
-        dq, dk, dv = fd.ring_attention_backward(g[:, :, sl], q[:, :, sl], k[:, :, sl], v[:, :, sl], o, lse, 0.25,
-                                                causal, None, _oracle_bwd)
+        dq, dk, dv = fd.ring_attention_backward(gl, ql, kl, vl, o, lse, 0.25, causal, None, _oracle_bwd, layout)
+        assert torch.equal(kl, take(k)) and torch.equal(vl, take(v)) and torch.equal(ql, take(q))
         dq_ref, dk_ref, dv_ref = orc.attention_bwd(q, k, v, g, 0.25, causal)
-        errs = [(o - o_ref[:, :, sl]).abs().max().item(), (lse - lse_ref[:, :, sl]).abs().max().item(),
-                (dq - dq_ref[:, :, sl]).abs().max().item(), (dk - dk_ref[:, :, sl]).abs().max().item(),
-                (dv - dv_ref[:, :, sl]).abs().max().item()]
+        errs = [(o - take(o_ref)).abs().max().item(), (lse - take(lse_ref)).abs().max().item(),
+                (dq - take(dq_ref)).abs().max().item(), (dk - take(dk_ref)).abs().max().item(),
+                (dv - take(dv_ref)).abs().max().item()]
         results[rank] = errs
     finally:
         dist.destroy_process_group()
@@ -83,6 +91,31 @@ def test_ring_attention_matches_full_attention(world, causal):
     assert len(results) == world
     for rank, errs in results.items():
         assert max(errs) < 1e-4, (rank, errs)
+
+
+@pytest.mark.parametrize("world,causal", [(2, True), (4, True), (3, False)])
+def test_zigzag_ring_attention_matches_full_attention(world, causal):
+    port = _free_port()
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_ring_worker, args=(world, port, causal, results, "zigzag"), nprocs=world, join=True)
+    assert len(results) == world
+    for rank, errs in results.items():
+        assert max(errs) < 1e-4, (rank, errs)
+
+
+def test_zigzag_rows_cover_the_sequence_once():
+    import flash_attn_legacy.distributed as fd
+    for world in (1, 2, 3, 4, 8):
+        n = 2 * world * 5
+        seen = []
+        for r in range(world):
+            (a0, a1), (b0, b1) = fd.zigzag_rows(n, world, r)
+            assert a1 - a0 == b1 - b0 == 5 and a1 <= b0
+            seen += list(range(a0, a1)) + list(range(b0, b1))
+        assert sorted(seen) == list(range(n))
+    with pytest.raises(ValueError):
+        fd.zigzag_rows(10, 4, 0)
 
 
 def test_shard_helpers():
