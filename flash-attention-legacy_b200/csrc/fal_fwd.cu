@@ -51,6 +51,26 @@ __device__ __forceinline__ float tile_exp2(int i, float x) {
   return (((i + K) & 7) < FAL_EXP_EMU_PER8) ? exp2_fma(x) : fast_exp2(x);
 }
 
+// Packed softmax arithmetic: scale-and-subtract, the row sums and (for a share of the pairs) the
+// exponential itself run as two-float instructions.  FAL_FWD_EMU_PAIRS of every 4 pairs take the
+// polynomial path instead of the special-function unit (0 = none).
+#ifndef FAL_FWD_PACKED
+#define FAL_FWD_PACKED 1
+#endif
+#ifndef FAL_FWD_EMU_PAIRS
+#define FAL_FWD_EMU_PAIRS 0
+#endif
+template <int K>
+__device__ __forceinline__ uint64_t tile_exp2_pair(int i, uint64_t x) {
+  // pair index within its group of four; i is a multiple of 4 under full unrolling
+  const int q = ((i >> 1) + K) & 3;
+  const bool emu = (FAL_FWD_EMU_PAIRS == 1) ? (q == 0)
+                 : (FAL_FWD_EMU_PAIRS == 2) ? ((q & 1) == 0)
+                 : (FAL_FWD_EMU_PAIRS == 3) ? (q != 3)
+                 : (FAL_FWD_EMU_PAIRS >= 4);
+  return emu ? exp2_pair_fma(x) : exp2_pair_mufu(x);
+}
+
 // Register split after launch (setmaxnreg).  The kernel launches with 168 registers for each of
 // its 384 threads = 64512; the two softmax warpgroups and the third warpgroup must not ask for
 // more than that in total, or setmaxnreg.inc would wait forever.
@@ -65,6 +85,26 @@ constexpr int kRegsOther = FAL_FWD_REGS_OTHER;
 static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 168 * 384,
               "setmaxnreg split exceeds the registers the CTA was launched with");
 static_assert(kRegsSoftmax % 8 == 0 && kRegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
+
+// Tuning aid, compiled in only with -DFAL_FWD_TIMING: cycles per role and phase, summed over CTAs.
+#ifdef FAL_FWD_TIMING
+__device__ unsigned long long g_fwd_cycles[32];
+#define FWD_T(slot, stmt)                  \
+  do {                                     \
+    const long long _t0 = clock64();       \
+    stmt;                                  \
+    tacc[slot] += clock64() - _t0;         \
+  } while (0)
+#define FWD_MARK(slot)                     \
+  do {                                     \
+    const long long _t1 = clock64();       \
+    tacc[slot] += _t1 - tmark;             \
+    tmark = _t1;                           \
+  } while (0)
+#else
+#define FWD_T(slot, stmt) stmt
+#define FWD_MARK(slot)
+#endif
 
 // Barrier ids (only used to label a wait that gave up).
 enum FwdBarrier : int {
@@ -276,8 +316,13 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
+#ifdef FAL_FWD_DEBUG_QK_FROM_TMEM  // tuning aid: A operand from TMEM (garbage) to take Q's shared-memory reads away
+          umma_ts(tmem_base + w * kTileN, tmem_base + 256 + w * D + ks * 8,
+                  smem_desc_join(k_lo + off, kHi), idesc_qk, ks > 0 ? 1u : 0u);
+#else
           umma_ss(tmem_base + w * kTileN, smem_desc_join(q_lo[w] + off, kHi),
                   smem_desc_join(k_lo + off, kHi), idesc_qk, ks > 0 ? 1u : 0u);
+#endif
         }
       };
       // O[w] += P[w] V_j : A = P from TMEM (8 columns of packed fp16 per 16 keys), B = V
@@ -294,6 +339,10 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       };
 
+#ifdef FAL_FWD_TIMING
+      long long tacc[8] = {};
+      const long long t_begin = clock64();
+#endif
       if (n_max > 0) {
         mbar_wait(bar(iKFull + 0), 0, wctx, kBarKFull);
         for (int w = 0; w < 2; ++w) {
@@ -312,25 +361,32 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (j >= ntile[w]) continue;
           // P arrives in two halves of 64 keys, so that PV starts while the softmax warps are
           // still exponentiating the second half.
-          mbar_wait(bar(iPHalf + w), j & 1, wctx, kBarPReady + w);
-          mbar_wait(bar(iVFull + s), use & 1, wctx, kBarVFull + s);
+          FWD_T(0, mbar_wait(bar(iPHalf + w), j & 1, wctx, kBarPReady + w));
+          FWD_T(1, mbar_wait(bar(iVFull + s), use & 1, wctx, kBarVFull + s));
           tc_fence_after_sync();
-          issue_pv(w, j, 0);
-          mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w);
+          FWD_T(5, issue_pv(w, j, 0));
+          FWD_T(2, mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w));
           tc_fence_after_sync();
-          issue_pv(w, j, 1);
+          FWD_T(6, issue_pv(w, j, 1));
           tc_commit(bar(iODone + w));
           if (w == 1 || j >= ntile[1]) tc_commit(bar(iVEmpty + s));
           if (j + 1 < ntile[w]) {
             const int s1 = (j + 1) % NS;
-            mbar_wait(bar(iKFull + s1), ((j + 1) / NS) & 1, wctx, kBarKFull + s1);
+            FWD_T(3, mbar_wait(bar(iKFull + s1), ((j + 1) / NS) & 1, wctx, kBarKFull + s1));
             tc_fence_after_sync();
-            issue_qk(w, j + 1);
+            FWD_T(7, issue_qk(w, j + 1));
             tc_commit(bar(iSReady + w));
             if (w == 1 || j + 1 >= ntile[1]) tc_commit(bar(iKEmpty + s1));
           }
         }
       }
+#ifdef FAL_FWD_TIMING
+      for (int i = 0; i < 4; ++i) atomicAdd(&g_fwd_cycles[i], static_cast<unsigned long long>(tacc[i]));
+      for (int i = 5; i < 8; ++i) atomicAdd(&g_fwd_cycles[18 + i], static_cast<unsigned long long>(tacc[i]));
+      atomicAdd(&g_fwd_cycles[4], static_cast<unsigned long long>(clock64() - t_begin));
+      atomicAdd(&g_fwd_cycles[5], static_cast<unsigned long long>(ntile[0] + ntile[1]));
+      atomicAdd(&g_fwd_cycles[6], 1ull);
+#endif
     }
     __syncwarp();
   }
@@ -351,9 +407,22 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     float m_ref = kNegInf;
     float l = 0.f;
 
+#ifdef FAL_FWD_TIMING
+    long long tacc[8] = {};
+    long long tmark = clock64();
+    const long long t_begin = tmark;
+#endif
     for (int j = 0; j < nt; ++j) {
+      FWD_MARK(7);  // loop overhead
       mbar_wait(bar(iSReady + wg), j & 1, wctx, kBarSReady + wg);
       tc_fence_after_sync();
+      FWD_MARK(0);  // wait for S
+#ifdef FAL_FWD_DEBUG_NO_SOFTMAX  // tuning aid: the MMA side alone (results are meaningless)
+      tc_fence_before_sync();
+      mbar_arrive(bar(iPHalf + wg));
+      mbar_arrive(bar(iPReady + wg));
+      continue;
+#endif
       const int kv0 = j * kTileN;
       int limit = wk.seqlen_k - kv0;  // columns c < limit are visible
       if (CAUSAL) limit = min(limit, q_local - kv0 + 1);
@@ -365,6 +434,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tS + c * 32, sr[c]);
       tmem_wait_ld();
+      FWD_MARK(1);  // S into registers
       if (tile_mask) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -393,6 +463,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mx = fmax3(mx, part[6], part[7]);
       }
       const float m_new = fmaxf(m_ref, mx);
+      FWD_MARK(2);  // mask + row max
 
       if (j == 0) {
         m_ref = m_new;
@@ -417,9 +488,45 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       const float moff = (m_ref == kNegInf) ? 0.f : m_ref * c2;
+      FWD_MARK(3);  // rescale decision (and rescale)
 
       // P = exp2(s * c2 - m * c2) from the registers, four independent row-sum chains,
       // fp16 P back into TMEM over the first half of S.
+#if FAL_FWD_PACKED
+      const uint64_t c2p = pack_f32x2(c2, c2);
+      const uint64_t moffp = pack_f32x2(-moff, -moff);
+      uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const uint64_t x01 = ffma2(pack_f32x2(__uint_as_float(sr[c][i + 0]), __uint_as_float(sr[c][i + 1])),
+                                     c2p, moffp);
+          const uint64_t x23 = ffma2(pack_f32x2(__uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3])),
+                                     c2p, moffp);
+          const uint64_t p01 = tile_exp2_pair<0>(i, x01);
+          const uint64_t p23 = tile_exp2_pair<1>(i, x23);
+          sum_a = fadd2(sum_a, p01);
+          sum_b = fadd2(sum_b, p23);
+          float p0, p1, p2, p3;
+          unpack_f32x2(p01, p0, p1);
+          unpack_f32x2(p23, p2, p3);
+          pk[(i >> 1) + 0] = pack_half2(p0, p1);
+          pk[(i >> 1) + 1] = pack_half2(p2, p3);
+        }
+        tmem_st_32x32b_x16(tS + c * 16, pk);
+        if (c == 1) {  // the first 64 keys of P are in TMEM: the PV MMA may start on them
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar(iPHalf + wg));
+          FWD_MARK(4);  // first half of P
+        }
+      }
+      float sum0, sum1, sum2, sum3;
+      unpack_f32x2(sum_a, sum0, sum1);
+      unpack_f32x2(sum_b, sum2, sum3);
+#else
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -444,13 +551,24 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mbar_arrive(bar(iPHalf + wg));
         }
       }
+#endif
       const float sum_lo = sum0 + sum1, sum_hi = sum2 + sum3;
       const float sum01 = sum_lo + sum_hi;
       l += sum01;
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar(iPReady + wg));
+      FWD_MARK(5);  // second half of P
     }
+#ifdef FAL_FWD_TIMING
+    if (lane == 0 && quarter == 0) {
+      for (int i = 0; i < 8; ++i)
+        if (i != 6) atomicAdd(&g_fwd_cycles[8 + i], static_cast<unsigned long long>(tacc[i]));
+      atomicAdd(&g_fwd_cycles[8 + 6], static_cast<unsigned long long>(clock64() - t_begin));
+      atomicAdd(&g_fwd_cycles[16], static_cast<unsigned long long>(nt));
+    }
+    const long long t_epi = clock64();
+#endif
 
     // ---- epilogue: O / l -> fp16, LSE -----------------------------------------
     if (nt > 0) {
@@ -488,6 +606,10 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                                       : kNegInf;
       p.lse[wk.lse_base + static_cast<int64_t>(q_local) * p.lse_strides.row] = lse;
     }
+#ifdef FAL_FWD_TIMING
+    if (lane == 0 && quarter == 0)
+      atomicAdd(&g_fwd_cycles[17], static_cast<unsigned long long>(clock64() - t_epi));
+#endif
   }
 
   // ---- teardown -------------------------------------------------------------
@@ -498,6 +620,21 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tmem_dealloc(tmem_base, 512);
   }
 }
+
+#ifdef FAL_FWD_TIMING
+}  // namespace
+}  // namespace fal
+extern "C" __attribute__((visibility("default"))) int fal_debug_fwd_cycles(unsigned long long* out32, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out32, fal::g_fwd_cycles, sizeof(unsigned long long) * 32);
+  if (e == cudaSuccess && reset) {
+    unsigned long long z[32] = {};
+    e = cudaMemcpyToSymbol(fal::g_fwd_cycles, z, sizeof(z));
+  }
+  return static_cast<int>(e);
+}
+namespace fal {
+namespace {
+#endif
 
 template <int D, bool CAUSAL>
 cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,

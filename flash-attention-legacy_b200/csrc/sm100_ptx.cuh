@@ -342,6 +342,62 @@ __device__ __forceinline__ float exp2_fma(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
+// ---- packed fp32 pairs (one instruction works on two floats held in a 64-bit register) ----
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t r, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(r));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fsub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2_round_down(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// 2^x for a pair, on the special-function unit.
+__device__ __forceinline__ uint64_t exp2_pair_mufu(uint64_t x) {
+  float a, b;
+  unpack_f32x2(x, a, b);
+  return pack_f32x2(fast_exp2(a), fast_exp2(b));
+}
+
+// 2^x for a pair without the special-function unit: exp2_fma's arithmetic with the packed
+// instructions (same polynomial, same clamp).
+__device__ __forceinline__ uint64_t exp2_pair_fma(uint64_t x) {
+  float a, b;
+  unpack_f32x2(x, a, b);
+  x = pack_f32x2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);
+  const uint64_t t = fadd2_round_down(x, magic);  // low mantissa bits = floor(x)
+  const uint64_t fr = fsub2(x, fsub2(t, magic));
+  uint64_t pl = ffma2(pack_f32x2(0.07706618f, 0.07706618f), fr, pack_f32x2(0.22764593f, 0.22764593f));
+  pl = ffma2(pl, fr, pack_f32x2(0.69511657f, 0.69511657f));
+  pl = ffma2(pl, fr, pack_f32x2(1.0f, 1.0f));
+  float p0, p1, t0, t1;
+  unpack_f32x2(pl, p0, p1);
+  unpack_f32x2(t, t0, t1);
+  return pack_f32x2(__int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23)),
+                    __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23)));
+}
+
 // Two exponentials per instruction on packed fp16 (input and result are half2 bit patterns).
 __device__ __forceinline__ uint32_t exp2_f16x2(uint32_t x) {
   uint32_t y;
