@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -149,6 +150,8 @@ BwdWorkspace bwd_workspace_layout(int batch, int heads_q, int rows, int head_dim
 }
 
 constexpr int kDecodeSplitLen = 1024;
+// Shortest (mean) sequence for which the forward runs on CTA pairs by default: off until measured.
+constexpr int64_t kPairForwardMinRows = INT64_MAX;
 
 // ---------------------------------------------------------------------------
 // Optional event timing around the main kernels (off by default).
@@ -205,6 +208,20 @@ int fal_last_cuda_error(void) { return g_last_cuda_error; }
 
 const char* fal_version(void) { return "0.1.0"; }
 
+namespace {
+// Which forward kernel: the CTA-pair kernel (head_dim 128) pays off once a sequence fills its
+// 512-row blocks; FAL_FWD_PAIR=0 / 1 in the environment forces the choice (tuning aid).
+bool use_pair_forward(int head_dim, int64_t rows_per_sequence) {
+  static const int forced = [] {
+    const char* e = std::getenv("FAL_FWD_PAIR");
+    return e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
+  }();
+  if (head_dim != 128) return false;
+  if (forced >= 0) return forced == 1;
+  return rows_per_sequence >= kPairForwardMinRows;
+}
+}  // namespace
+
 int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
             int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
             const fal_strides* q_strides, const fal_strides* k_strides,
@@ -243,15 +260,20 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   p.heads_kv = heads_kv;
   p.seqlen_q = seqlen_q;
   p.seqlen_k = seqlen_k;
-  p.num_qblk = (seqlen_q + 255) / 256;
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
-  const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q;
-  if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool pair = use_pair_forward(head_dim, seqlen_q);
+  CUtensorMap tk_half;
+  if (pair && (rc = make_tensor_map(&tk_half, k, head_dim, seqlen_k, heads_kv, batch, to_rs(k_strides), 64)))
+    return rc;
+  p.num_qblk = pair ? (seqlen_q + 511) / 512 : (seqlen_q + 255) / 256;
+  const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q * (pair ? 2 : 1);
+  if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
-  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  cudaError_t e = pair ? fal::launch_fwd_pair(is_causal != 0, tq, tk_half, tv, p, static_cast<int>(grid), st)
+                       : fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
@@ -299,16 +321,21 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   p.heads_kv = heads_kv;
   p.seqlen_q = 0;
   p.seqlen_k = 0;
-  // Every sequence rounds up to whole 256-row blocks: at most one extra block each.
-  p.num_qblk = total_q / 256 + num_seqs;
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
-  const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q;
-  if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The lengths stay on the device; the mean length decides between the kernels.
+  const bool pair = use_pair_forward(head_dim, total_q / num_seqs);
+  CUtensorMap tk_half;
+  if (pair && (rc = make_tensor_map(&tk_half, k, head_dim, total_k, heads_kv, 1, ks, 64))) return rc;
+  // Every sequence rounds up to whole 256-row (512-row) blocks: at most one extra block each.
+  p.num_qblk = (pair ? total_q / 512 : total_q / 256) + num_seqs;
+  const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q * (pair ? 2 : 1);
+  if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
-  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  cudaError_t e = pair ? fal::launch_fwd_pair(is_causal != 0, tq, tk_half, tv, p, static_cast<int>(grid), st)
+                       : fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
