@@ -475,7 +475,10 @@ def main():
         achieved = bwd_flops / (bwd_kernel_ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": "fal_bwd_kernel<128,causal>", "achieved": achieved,
                     "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "traffic": None,
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
+                    # DRAM read + write bytes of one launch on this workload, from the ncu capture
+                    # summarised in profiles/bwd_kernel_config2.md (not re-measured here).
+                    "traffic": 3.58e9, "traffic_unit": "bytes per launch",
                     "kernel_ms": bwd_kernel_ms, "frac_of_nominal_2250": achieved / 2250.0}
     if fwd_n:
         fwd_kernel_ms = fwd_ms / fwd_n
