@@ -73,8 +73,8 @@ struct BwdSmem {
   static constexpr int kStatBytes = kQStages * 2 * kQTile * 4;
   static constexpr int kBarOff = kStatOff + kStatBytes;
   // k_full v_full q_full[2] q_empty[2] stat_full[2] do_full do_empty
-  // s_ready dp_ready dq_ready dq_free p_ready ds_ready all_done
-  static constexpr int kNumBars = 2 + 6 + 2 + 7;
+  // s_ready dp_ready dq_ready dq_free p_ready ds_ready all_done ds_free
+  static constexpr int kNumBars = 2 + 6 + 2 + 8;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kBytes = kMiscOff + 16;
   // No slack for re-aligning the base: at head_dim 128 the layout fills the 227 KB limit, so the
@@ -94,12 +94,26 @@ struct BwdWork {
   int seqlen_k;
 };
 
+#ifndef FAL_BWD_WAVE_GROUPS
+#define FAL_BWD_WAVE_GROUPS 8
+#endif
+constexpr int kWaveGroups = FAL_BWD_WAVE_GROUPS;
+
 __device__ __forceinline__ bool bwd_decode_work(const BwdParams& p, BwdWork& w) {
   const int idx = blockIdx.x;
   if (p.cu_k == nullptr) {
+    // CTAs are numbered in waves of kWaveGroups (batch, KV head) groups; inside a wave the first key
+    // blocks come first (under a causal mask they see the most queries).  The CTAs that run at the
+    // same time then add into the fp32 dQ accumulators of a few groups only (8 MB per group at
+    // 4 heads x 4096 rows), which stay in L2 between the 32 key tiles that touch them.
     const int bh_count = p.batch * p.heads_kv;
-    w.kvblk = idx / bh_count;  // first key blocks first: under a causal mask they see the most queries
-    const int bh = idx % bh_count;
+    const int nkvblk = (p.seqlen_k + kKvTile - 1) / kKvTile;
+    const int wave = idx / (kWaveGroups * nkvblk);
+    const int first_group = wave * kWaveGroups;
+    const int groups_here = min(kWaveGroups, bh_count - first_group);
+    const int r = idx - wave * kWaveGroups * nkvblk;
+    w.kvblk = r / groups_here;
+    const int bh = first_group + r % groups_here;
     w.batch = bh / p.heads_kv;
     w.kv_head = bh % p.heads_kv;
     w.q_row0 = 0;
@@ -139,6 +153,16 @@ __device__ __forceinline__ float bwd_exp2(int j, float x) {
   // j is a multiple of 4 under full unrolling, so the choice folds at compile time.
   return (((j + K) & 7) < FAL_BWD_EXP_EMU_PER8) ? exp2_fma(x) : fast_exp2(x);
 }
+
+// dQ(i) issued before dK(i) (1): the write-back warps drain dQ out of TMEM -- which the next
+// step's dP^T needs gone -- while dK still runs.  0: dK first.
+#ifndef FAL_BWD_DQ_FIRST
+#define FAL_BWD_DQ_FIRST 1
+#endif
+// One elected lane per compute warp arrives on p_ready / ds_ready (1) or every thread (0).
+#ifndef FAL_BWD_ELECT_ARRIVE
+#define FAL_BWD_ELECT_ARRIVE 1
+#endif
 
 // Tuning aid, compiled in only with -DFAL_BWD_TIMING: cycles each role spends in each wait.
 #ifdef FAL_BWD_TIMING
@@ -190,7 +214,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto bar = [&](int i) { return bar0 + 8u * i; };
   constexpr int iKFull = 0, iVFull = 1, iQFull = 2, iQEmpty = 4, iStatFull = 6, iDoFull = 8, iDoEmpty = 9,
                 iSReady = 10, iDpReady = 11, iDqReady = 12, iDqFree = 13, iPReady = 14, iDsReady = 15,
-                iAllDone = 16;
+                iAllDone = 16, iDsFree = 17;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kMiscOff + 4);
   const WaitCtx wctx{abort_flag, p.status};
@@ -221,9 +245,10 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(bar(iDpReady), 1);
     mbar_init(bar(iDqReady), 1);
     mbar_init(bar(iDqFree), 128);
-    mbar_init(bar(iPReady), 256);
-    mbar_init(bar(iDsReady), 256);
+    mbar_init(bar(iPReady), FAL_BWD_ELECT_ARRIVE ? 8 : 256);
+    mbar_init(bar(iDsReady), FAL_BWD_ELECT_ARRIVE ? 8 : 256);
     mbar_init(bar(iAllDone), 1);
+    mbar_init(bar(iDsFree), 1);
     fence_mbar_init();
   }
   if (warp == 9) {
@@ -361,25 +386,37 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           issue_xyT(kColS, k_lo_k, sbase + L::kQOff + st1 * L::kTileBytes);
           tc_commit(bar(iSReady));
         }
-        // dK += dS^T(i) Q(i)
         BWD_WAIT(5, bar(iDsReady), i & 1, wctx, kBbDsReady);
         tc_fence_after_sync();
+        // dK += dS^T(i) Q(i)
+        auto issue_dk = [&]() {
 #pragma unroll
-        for (int ks = 0; ks < kQTile / 16; ++ks) {
-          const uint32_t a_off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
-          umma_ss(tmem_base + kColDk, smem_desc_join(ds_lo_k + a_off, kHi),
-                  smem_desc_join(q_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dkv,
-                  (i > 0 || ks > 0) ? 1u : 0u);
-        }
-        tc_commit(bar(iQEmpty + st));  // Q(i) has no reader left once dK(i) is done
+          for (int ks = 0; ks < kQTile / 16; ++ks) {
+            const uint32_t a_off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
+            umma_ss(tmem_base + kColDk, smem_desc_join(ds_lo_k + a_off, kHi),
+                    smem_desc_join(q_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dkv,
+                    (i > 0 || ks > 0) ? 1u : 0u);
+          }
+          tc_commit(bar(iQEmpty + st));  // Q(i) has no reader left once dK(i) is done
+        };
         // dQ(i) = dS(i) K: the dS^T buffer read as an M-contiguous A operand; the result (queries on
         // the lanes, head_dim on the columns) goes into the columns of the consumed dP^T(i)
+        auto issue_dq = [&]() {
 #pragma unroll
-        for (int ks = 0; ks < kKvTile / 16; ++ks) {
-          umma_ss(tmem_base + kColDpq, smem_desc_join(ds_lo_mn + ((ks * 2048) >> 4), kHi),
-                  smem_desc_join(k_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dq, ks > 0 ? 1u : 0u);
-        }
-        tc_commit(bar(iDqReady));  // also tells the compute warps that the dS^T buffer is free again
+          for (int ks = 0; ks < kKvTile / 16; ++ks) {
+            umma_ss(tmem_base + kColDpq, smem_desc_join(ds_lo_mn + ((ks * 2048) >> 4), kHi),
+                    smem_desc_join(k_lo_mn + ((ks * 2048) >> 4), kHi), idesc_dq, ks > 0 ? 1u : 0u);
+          }
+          tc_commit(bar(iDqReady));
+        };
+#if FAL_BWD_DQ_FIRST
+        issue_dq();
+        issue_dk();
+#else
+        issue_dk();
+        issue_dq();
+#endif
+        tc_commit(bar(iDsFree));  // both readers of the dS^T buffer are done
         // dP^T(i+1) goes where dQ(i) is: the write-back warps must have read it out first.
         if (i + 1 < n_iter) {
           BWD_WAIT(1, bar(iDoFull), (i + 1) & 1, wctx, kBbDoFull);
@@ -461,7 +498,12 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         BWD_TIMING_ONLY(tacc[18] += clock64() - t_p2;)
       }
       tc_fence_before_sync();
+#if FAL_BWD_ELECT_ARRIVE
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(iPReady));
+#else
       mbar_arrive(bar(iPReady));
+#endif
       BWD_TIMING_ONLY(tacc[22] += clock64() - t_p0;)
 
       // ---- dS^T = P^T o (dP^T - delta) ------------------------------------------
@@ -490,7 +532,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       BWD_TIMING_ONLY(tacc[20] += clock64() - t_s0;)
-      if (i > 0) BWD_WAIT(9, bar(iDqReady), (i - 1) & 1, wctx, kBbDqReady);
+      if (i > 0) BWD_WAIT(9, bar(iDsFree), (i - 1) & 1, wctx, kBbDqReady);
       // dS^T row -> shared memory, 128-byte XOR swizzle (16-byte chunk index ^ row % 8)
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -499,7 +541,12 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
+#if FAL_BWD_ELECT_ARRIVE
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(iDsReady));
+#else
       mbar_arrive(bar(iDsReady));
+#endif
       BWD_TIMING_ONLY(tacc[23] += clock64() - t_s0;)
     }
 
@@ -577,9 +624,19 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 make_uint4(r[c][4 * v + 0], r[c][4 * v + 1], r[c][4 * v + 2], r[c][4 * v + 3]);
         fence_proxy_async_smem();
         named_barrier_sync(1, 128);
+#ifdef FAL_BWD_DEBUG_NO_REDUCE  // tuning aid: dQ is staged but never added (dQ comes out zero)
+        if (false) {
+#else
         if (issuer) {
+#endif
+#ifdef FAL_BWD_DEBUG_LOCAL_REDUCE  // tuning aid: every CTA adds into one small region (wrong dQ)
+          const int dbg_head = blockIdx.x % p.heads_q, dbg_batch = (blockIdx.x / p.heads_q) % p.batch;
+          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff, hf * 64, 0, dbg_head, dbg_batch);
+          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff + L::kBoxBytes, hf * 64 + 32, 0, dbg_head, dbg_batch);
+#else
           tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff, hf * 64, grow, head, wk.batch);
           tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff + L::kBoxBytes, hf * 64 + 32, grow, head, wk.batch);
+#endif
           bulk_commit_group();
         }
       }
