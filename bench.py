@@ -478,7 +478,7 @@ def main():
                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
                     # DRAM read + write bytes of one launch on this workload, from the ncu capture
                     # summarised in profiles/bwd_kernel_config2.md (not re-measured here).
-                    "traffic": 3.58e9, "traffic_unit": "bytes per launch",
+                    "traffic": 1.088e9, "traffic_unit": "bytes per launch",
                     "kernel_ms": bwd_kernel_ms, "frac_of_nominal_2250": achieved / 2250.0}
     if fwd_n:
         fwd_kernel_ms = fwd_ms / fwd_n
