@@ -1,5 +1,6 @@
 """CPU: host-side logic of the Python surface (no kernel launches)."""
 import math
+import os
 
 import pytest
 import torch
@@ -121,3 +122,21 @@ def test_device_info_needs_cuda(fal):
     with pytest.raises(RuntimeError):
         fal.get_device_info()
     assert fal.check_gpu_compatibility(verbose=False) is False
+
+
+def test_build_script_keeps_tuning_builds_away_from_the_product_library():
+    import importlib.util
+    from conftest import PKG
+    spec = importlib.util.spec_from_file_location("fal_b200_build_t", os.path.join(PKG, "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with pytest.raises(RuntimeError):
+        mod.build(defines=("FAL_FWD_TIMING",))  # a define without --out would replace the product library
+    with pytest.raises(RuntimeError):
+        mod.build(defines=("FAL_FWD_TIMING",), out=mod.LIB_PATH)
+
+
+def test_cycle_counters_are_absent_from_the_product_library():
+    import flash_attn_legacy_cuda as ext
+    for which in ("fwd", "fwd_pair", "bwd"):
+        assert ext.debug_cycles(which) is None
