@@ -45,14 +45,29 @@ def _native_head_dim(d: int) -> int:
     )
 
 
+def _kernel_ready(t: torch.Tensor) -> torch.Tensor:
+    """`t` itself when the kernels can address it through strides, else a contiguous copy.
+
+    The library takes (batch, head, row) element strides, so a [B,H,N,d] view of [B,N,H,d] memory
+    (what a QKV projection followed by .transpose(1, 2) gives) needs no copy, where the reference
+    copies every input (flash_attn.py:39).  Needed: head_dim contiguous, 16-byte aligned rows.
+    """
+    if (t.stride(-1) == 1 and t.data_ptr() % 16 == 0
+            and all(s % 8 == 0 for s in t.stride()[:-1])):
+        return t
+    return t.contiguous()
+
+
 class FlashAttentionFunc(Function):
     """q [B,Hq,N,d], k/v [B,Hkv,N,d] fp16 -> o [B,Hq,N,d]; Hq % Hkv == 0 (GQA / MQA).
 
-    Mirrors FlashAttentionFunc of the reference (flash_attn.py:22-56).
+    Mirrors FlashAttentionFunc of the reference (flash_attn.py:22-56).  `out_layout="bnhd"`
+    (not in the reference) makes the result a [B,Hq,N,d] view of [B,N,Hq,d] memory, so that the
+    `.transpose(1, 2)` a transformer block applies next is already contiguous.
     """
 
     @staticmethod
-    def forward(ctx, q, k, v, softmax_scale, is_causal):
+    def forward(ctx, q, k, v, softmax_scale, is_causal, out_layout="bhnd"):
         assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
         assert k.dtype == torch.float16 and v.dtype == torch.float16
         assert q.is_cuda and q.dim() == 4
@@ -61,8 +76,13 @@ class FlashAttentionFunc(Function):
         h_q, h_kv = q.shape[1], k.shape[1]
         assert h_q % h_kv == 0, f"H_q ({h_q}) must be divisible by H_kv ({h_kv})"
 
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o, lse = flash_attn_legacy_cuda.forward(q, k, v, softmax_scale, is_causal)
+        assert out_layout in ("bhnd", "bnhd"), f"out_layout must be 'bhnd' or 'bnhd', got {out_layout}"
+        q, k, v = _kernel_ready(q), _kernel_ready(k), _kernel_ready(v)
+        out = None
+        if out_layout == "bnhd":
+            b, _, n, _ = q.shape
+            out = torch.empty((b, n, h_q, d), dtype=q.dtype, device=q.device).transpose(1, 2)
+        o, lse = flash_attn_legacy_cuda.forward(q, k, v, softmax_scale, is_causal, out=out)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.softmax_scale = softmax_scale
         ctx.is_causal = is_causal
@@ -72,9 +92,9 @@ class FlashAttentionFunc(Function):
     def backward(ctx, grad_output):
         q, k, v, o, lse = ctx.saved_tensors
         dq, dk, dv = flash_attn_legacy_cuda.backward(
-            grad_output.contiguous(), q, k, v, o, lse, ctx.softmax_scale, ctx.is_causal
+            _kernel_ready(grad_output), q, k, v, o, lse, ctx.softmax_scale, ctx.is_causal
         )
-        return dq, dk, dv, None, None
+        return dq, dk, dv, None, None, None
 
 
 def _pad_last(x, d_to):
@@ -87,12 +107,15 @@ def flash_attention(
     v: torch.Tensor,
     softmax_scale: Optional[float] = None,
     is_causal: bool = False,
+    out_layout: str = "bhnd",
 ) -> torch.Tensor:
     """softmax(q k^T * scale [+ causal mask]) v, O(N) memory, fp16 in / fp16 out.
 
     q [B,Hq,N,d]; k, v [B,Hkv,N,d] with Hq divisible by Hkv (MHA, GQA, MQA).
     `softmax_scale` defaults to 1/sqrt(d).  The causal mask hides key j from query i
-    when j > i.  Same contract as the reference's flash_attention (flash_attn.py:59-87).
+    when j > i.  Same contract as the reference's flash_attention (flash_attn.py:59-87);
+    inputs that are strided views with a contiguous head_dim are read in place, and
+    `out_layout="bnhd"` returns the [B,Hq,N,d] result as a view of [B,N,Hq,d] memory.
     """
     assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
     d = q.shape[-1]
@@ -102,9 +125,9 @@ def flash_attention(
     dn = _native_head_dim(d)
     if dn != d:
         out = FlashAttentionFunc.apply(_pad_last(q, dn), _pad_last(k, dn), _pad_last(v, dn),
-                                       softmax_scale, is_causal)
+                                       softmax_scale, is_causal, out_layout)
         return out[..., :d]
-    return FlashAttentionFunc.apply(q, k, v, softmax_scale, is_causal)
+    return FlashAttentionFunc.apply(q, k, v, softmax_scale, is_causal, out_layout)
 
 
 class FlashAttnVarlenFunc(Function):

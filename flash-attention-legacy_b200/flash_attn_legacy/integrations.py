@@ -74,9 +74,12 @@ def flash_attn_legacy_forward(
 
     if q_len == kv_len and d in _KERNEL_HEAD_DIMS and query.is_cuda:
         # Prefill.  As in the reference, attention_mask is not consulted on this branch.
+        # Inputs are read through their strides and the result is written as [B, q_len, Hq, d]
+        # memory, so neither side of the call copies (the reference copies q, k, v and the output:
+        # flash_attn.py:39, integrations.py:101).
         out = flash_attention(to_half(query), to_half(key), to_half(value),
-                              softmax_scale=scaling, is_causal=is_causal)
-        out = out.to(in_dtype).transpose(1, 2).contiguous()
+                              softmax_scale=scaling, is_causal=is_causal, out_layout="bnhd")
+        out = out.to(in_dtype).transpose(1, 2).contiguous()  # no-op for fp16 models
     elif q_len == 1 and attention_mask is None and d in _DECODE_HEAD_DIMS and query.is_cuda:
         # Decode: one new token against the whole cache, no mask.
         out = flash_attn_with_kvcache(

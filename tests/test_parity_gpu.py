@@ -436,6 +436,28 @@ def test_flash_attention_autograd_all_head_dims(fal, d):
     check_grads((qc.grad, kc.grad, vc.grad), orc.attention_bwd(q, k, v, do, scale, True))
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_operator_reads_strided_views_and_writes_bnhd_memory(fal, causal):
+    """The layout a transformer block has: [B,N,H,d] projections viewed as [B,H,N,d], and an output the
+    block transposes back.  Neither side of the operator should need a copy, forward or backward."""
+    gen = torch.Generator().manual_seed(21)
+    b, hq, hkv, n, d = 2, 8, 2, 300, 128
+    q_mem, k_mem, v_mem = rand_half(gen, b, n, hq, d), rand_half(gen, b, n, hkv, d), rand_half(gen, b, n, hkv, d)
+    do_mem = rand_half(gen, b, n, hq, d)
+    q, k, v = (t.cuda().transpose(1, 2).requires_grad_(True) for t in (q_mem, k_mem, v_mem))
+    assert not q.is_contiguous()
+    scale = 1.0 / math.sqrt(d)
+    out = fal.flash_attention(q, k, v, softmax_scale=scale, is_causal=causal, out_layout="bnhd")
+    assert out.shape == (b, hq, n, d) and out.transpose(1, 2).is_contiguous()
+    out.backward(do_mem.cuda().transpose(1, 2))  # a strided gradient, as the block's reshape produces
+    qf, kf, vf, dof = (t.transpose(1, 2).contiguous() for t in (q_mem, k_mem, v_mem, do_mem))
+    o_ref, _ = orc.attention_fwd(qf, kf, vf, scale, causal)
+    assert orc.rel_max_err(out, o_ref) <= orc.TOL_O
+    check_grads((q.grad, k.grad, v.grad), orc.attention_bwd(qf, kf, vf, dof, scale, causal))
+    # default layout unchanged: contiguous [B,H,N,d]
+    assert fal.flash_attention(q.detach(), k.detach(), v.detach(), is_causal=causal).is_contiguous()
+
+
 def test_head_dim_256_is_reported_as_not_built(fal):
     q = torch.zeros(1, 1, 16, 256, dtype=torch.float16, device="cuda")
     with pytest.raises(NotImplementedError):
