@@ -6,10 +6,14 @@ Drop-in for flash_attn_legacy/integrations.py of sirCamp/flash-attention-legacy:
 patches PreTrainedModel._check_and_adjust_attn_implementation exactly where the
 reference does (integrations.py:106-161).
 
-Routing differs from the reference in one place: single-token decode without an
-additive mask goes to the split-K decode kernel instead of eager matmul/softmax.
-Everything the kernels do not cover (an explicit attention_mask, q_len > 1 with a
-longer key sequence, unsupported head_dim) keeps the reference's eager arithmetic.
+Routing differs from the reference in two places.  Single-token decode without a mask
+goes to the split-K decode kernel instead of eager matmul/softmax.  And a padding mask is
+honoured: `register()` also registers transformers' 2-D ("which tokens are real") mask
+format for this name -- without that, transformers hands a custom attention function no
+mask at all, and the reference attends to padding (integrations.py:63-76) -- and a prefill
+with such a mask runs un-padded through the packed kernels.  Everything the kernels do not
+cover (an additive 4-D mask, a padding mask outside prefill, q_len > 1 with a longer key
+sequence, unsupported head_dim) keeps the reference's eager arithmetic.
 """
 import math
 from typing import Optional
@@ -49,6 +53,33 @@ def _eager_attention(query, key, value, attention_mask, scaling, is_causal):
     return torch.matmul(torch.softmax(scores, dim=-1), value)
 
 
+def _padded_prefill(query, key, value, keep, scaling, is_causal):
+    """Prefill of a padded batch through the packed kernels.
+
+    `keep` [B, N] bool marks the real tokens of every row (left or right padding, any pattern).
+    Real tokens are packed in order, attend among themselves (causal order is preserved by the
+    packing), and their outputs go back to their places; padded positions give zeros.
+    Returns [B, N, Hq, d].
+    """
+    from .flash_attn import flash_attn_varlen_func
+
+    bsz, h_q, n, d = query.shape
+    h_kv = key.shape[1]
+    idx = keep.reshape(-1).nonzero(as_tuple=True)[0]  # the un-padding; sizes depend on the data
+    lens = keep.sum(dim=1, dtype=torch.int32)
+    cu = torch.zeros(bsz + 1, dtype=torch.int32, device=query.device)
+    cu[1:] = torch.cumsum(lens, dim=0)
+
+    def pack(t, h):
+        return t.transpose(1, 2).reshape(bsz * n, h, d).index_select(0, idx)
+
+    out_packed = flash_attn_varlen_func(pack(query, h_q), pack(key, h_kv), pack(value, h_kv),
+                                        cu, cu, n, n, softmax_scale=scaling, causal=is_causal)
+    out = torch.zeros(bsz * n, h_q, d, dtype=out_packed.dtype, device=query.device)
+    out.index_copy_(0, idx, out_packed)
+    return out.view(bsz, n, h_q, d)
+
+
 def flash_attn_legacy_forward(
     module: nn.Module,
     query: torch.Tensor,
@@ -66,13 +97,35 @@ def flash_attn_legacy_forward(
     kv_len = key.shape[2]
     if scaling is None:
         scaling = 1.0 / math.sqrt(d)
+    # A 2-D mask says which key positions are real tokens (transformers' format for un-padded
+    # attention, registered for this name by register()); anything else is additive.
+    keep = None
+    if attention_mask is not None and attention_mask.dim() == 2:
+        keep = attention_mask.to(torch.bool)
+        attention_mask = None
+        if keep.shape[-1] != kv_len or bool(keep.all()):
+            keep = None
     is_causal = _resolve_causal(module, attention_mask, q_len, kwargs)
     in_dtype = query.dtype
 
     def to_half(t):
         return t if t.dtype == torch.float16 else t.half()
 
-    if q_len == kv_len and d in _KERNEL_HEAD_DIMS and query.is_cuda:
+    if keep is not None and q_len == kv_len and d in _KERNEL_HEAD_DIMS and query.is_cuda:
+        out = _padded_prefill(to_half(query), to_half(key), to_half(value), keep, scaling,
+                              is_causal).to(in_dtype)
+    elif keep is not None:
+        # Padding outside prefill (e.g. decode of a left-padded batch): eager arithmetic with the
+        # padded keys masked out; causal rows are aligned to the end of the key sequence.
+        additive = torch.zeros(bsz, 1, q_len, kv_len, dtype=query.dtype, device=query.device)
+        additive.masked_fill_(~keep[:, None, None, :], float("-inf"))
+        if is_causal and q_len > 1:
+            qi = torch.arange(q_len, device=query.device)[:, None] + (kv_len - q_len)
+            kj = torch.arange(kv_len, device=query.device)[None, :]
+            additive.masked_fill_((kj > qi)[None, None], float("-inf"))
+        out = _eager_attention(query, key, value, additive, scaling, False)
+        out = torch.nan_to_num(out).transpose(1, 2).contiguous()  # rows that see no key at all
+    elif q_len == kv_len and d in _KERNEL_HEAD_DIMS and query.is_cuda:
         # Prefill.  As in the reference, attention_mask is not consulted on this branch.
         # Inputs are read through their strides and the result is written as [B, q_len, Hq, d]
         # memory, so neither side of the call copies (the reference copies q, k, v and the output:
@@ -105,6 +158,12 @@ def register():
         from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS, PreTrainedModel
 
         ALL_ATTENTION_FUNCTIONS.register("flash_attn_legacy", flash_attn_legacy_forward)
+        try:  # the mask format of un-padded attention: a 2-D "real token" mask, or None
+            from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS, flash_attention_mask
+
+            ALL_MASK_ATTENTION_FUNCTIONS.register("flash_attn_legacy", flash_attention_mask)
+        except (ImportError, AttributeError):
+            pass  # older transformers: no mask interface, the hook gets no mask as before
         stock_check = PreTrainedModel._check_and_adjust_attn_implementation
         if getattr(stock_check, "_flash_attn_legacy_patched", False):
             return True  # idempotent: do not stack wrappers on repeated imports

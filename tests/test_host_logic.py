@@ -140,3 +140,33 @@ def test_cycle_counters_are_absent_from_the_product_library():
     import flash_attn_legacy_cuda as ext
     for which in ("fwd", "fwd_pair", "bwd"):
         assert ext.debug_cycles(which) is None
+
+
+def test_padding_mask_reaches_the_hook_and_is_honoured_on_cpu(fal):
+    """transformers hands a custom attention function no mask unless a mask format is registered for its
+    name; register() does that, and the hook then masks padded keys (here through its eager branch)."""
+    transformers = pytest.importorskip("transformers")
+    assert fal.register()
+    from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS
+    assert "flash_attn_legacy" in ALL_MASK_ATTENTION_FUNCTIONS
+
+    def tiny(attn):
+        cfg = transformers.LlamaConfig(vocab_size=100, hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                                       num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
+        cfg._attn_implementation = attn
+        torch.manual_seed(0)
+        return transformers.LlamaForCausalLM(cfg).eval()
+
+    ref, model = tiny("eager"), tiny("flash_attn_legacy")
+    model.load_state_dict(ref.state_dict())
+    assert model.config._attn_implementation == "flash_attn_legacy"
+    ids = torch.randint(0, 100, (2, 12))
+    mask = torch.ones(2, 12, dtype=torch.long)
+    mask[1, :5] = 0  # left padding in row 1
+    with torch.no_grad():
+        a = model(ids, attention_mask=mask).logits
+        b = ref(ids, attention_mask=mask).logits
+        unmasked = model(ids).logits
+    real = mask.bool()
+    assert torch.allclose(a[real], b[real], atol=1e-4, rtol=1e-4)
+    assert not torch.allclose(a[1, 5:], unmasked[1, 5:], atol=1e-4)  # the mask does change row 1

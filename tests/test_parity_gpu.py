@@ -553,6 +553,47 @@ def test_hf_registration_prefill_and_generate(fal):
     assert launches >= 15 * 2  # every decode step of both layers ran the split-K kernel
 
 
+def test_hf_padded_batch_runs_unpadded_through_the_packed_kernels(fal):
+    from flash_attn_legacy.integrations import _padded_prefill
+    gen = torch.Generator().manual_seed(5)
+    b, hq, hkv, n, d = 3, 8, 2, 200, 128
+    q, k, v = rand_half(gen, b, hq, n, d), rand_half(gen, b, hkv, n, d), rand_half(gen, b, hkv, n, d)
+    keep = torch.ones(b, n, dtype=torch.bool)
+    keep[0, :37] = False          # left padding
+    keep[1, 150:] = False         # right padding
+    scale = 1.0 / math.sqrt(d)
+    out = _padded_prefill(q.cuda(), k.cuda(), v.cuda(), keep.cuda(), scale, True)  # [B, N, Hq, d]
+    assert out.shape == (b, n, hq, d)
+    for row in range(b):
+        sel = keep[row]
+        o_ref, _ = orc.attention_fwd(q[row:row + 1, :, sel], k[row:row + 1, :, sel], v[row:row + 1, :, sel], scale, True)
+        got = out[row, sel.cuda()].transpose(0, 1).unsqueeze(0)
+        assert orc.rel_max_err(got, o_ref) <= orc.TOL_O
+        assert (out[row, (~sel).cuda()] == 0).all()
+
+    # the whole route: a left-padded batch through a tiny LLaMA against eager attention
+    assert fal.register()
+    ref_model = _tiny_llama("eager")
+    model = _tiny_llama("flash_attn_legacy")
+    model.load_state_dict(ref_model.state_dict())
+    ids = torch.randint(0, 1000, (2, 48), device="cuda")
+    mask = torch.ones(2, 48, dtype=torch.long, device="cuda")
+    mask[1, :17] = 0
+    import flash_attn_legacy_cuda as ext
+    with torch.no_grad():
+        a = model(ids, attention_mask=mask).logits.float()
+        r = ref_model(ids, attention_mask=mask).logits.float()
+    real = mask.bool()
+    cos = torch.nn.functional.cosine_similarity(a[real].flatten(), r[real].flatten(), dim=0).item()
+    assert cos > 0.999
+    with torch.no_grad():
+        out = model.generate(ids[:, :24], attention_mask=mask[:, :24], max_new_tokens=8, do_sample=False)
+        out_ref = ref_model.generate(ids[:, :24], attention_mask=mask[:, :24], max_new_tokens=8, do_sample=False)
+    assert out.shape == (2, 32)
+    assert (out == out_ref).float().mean().item() > 0.9  # greedy tokens agree (fp16 ties aside)
+    assert ext.device_status() == 0
+
+
 # ---------------------------------------------------------------------------------------------
 # The CTA-pair forward kernel (opt-in: FAL_FWD_PAIR=1 is read once per process, so a child runs it)
 # ---------------------------------------------------------------------------------------------
