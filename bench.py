@@ -513,7 +513,7 @@ def main():
                     "pipeline": f"{nchunk} batch chunks; copy-in, kernels and copy-out on three streams"},
             "gpu_launches": 4 * args.steps,
             "launches_per_step": {"fal_fwd_kernel": 1, "fal_bwd_prep_kernel": 1, "fal_bwd_kernel": 1,
-                                  "fal_bwd_post_kernel": 1, "cudaMemsetAsync": 1},
+                                  "fal_bwd_post_kernel": 1},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": clocks,
             "device_status": status, "extra": extra,
         }))

@@ -682,7 +682,8 @@ namespace {
 #endif
 
 // ---------------------------------------------------------------------------
-// Pre-pass: delta[row] = sum_d dO*O  (precompute_D_kernel, bwd.cu:76-107 of the reference).
+// Pre-pass: delta[row] = sum_d dO*O  (precompute_D_kernel, bwd.cu:76-107 of the reference) and
+// the zeroing of the fp32 dQ accumulator (dQ_fp32 = zeros at csrc/flash_attn_legacy.cpp:126).
 // ---------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(256) fal_bwd_prep_kernel(const BwdPrepParams p) {
@@ -718,6 +719,15 @@ __global__ void __launch_bounds__(256) fal_bwd_prep_kernel(const BwdPrepParams p
 #pragma unroll
   for (int off = kLanesPerRow / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (ok && sub == 0) p.delta[b * p.delta_batch_stride + h * p.delta_head_stride + r] = acc;
+  // The fp32 dQ accumulator must start at zero (the main kernel only ever adds to it): this thread
+  // clears the 8 columns of the row it has just read from O and dO.  Rows between p.rows and the
+  // padded row count may be added into by partial tiles but are never read, so they stay as they are.
+  if (ok) {
+    float4* acc_row = reinterpret_cast<float4*>(p.dq_accum + b * p.dq_accum_batch_stride +
+                                                h * p.dq_accum_head_stride + static_cast<int64_t>(r) * D + sub * 8);
+    acc_row[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    acc_row[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -766,10 +776,6 @@ cudaError_t launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
 }  // namespace
 
 cudaError_t launch_bwd_prep(const BwdPrepParams& p, cudaStream_t stream) {
-  // The accumulator must start at zero: the main kernel only ever adds to it.
-  const size_t acc_bytes = static_cast<size_t>(p.batch) * p.dq_accum_batch_stride * sizeof(float);
-  cudaError_t e = cudaMemsetAsync(p.dq_accum, 0, acc_bytes, stream);
-  if (e != cudaSuccess) return e;
   const int64_t total = static_cast<int64_t>(p.batch) * p.heads_q * p.rows;
   if (p.head_dim == 128) {
     const int64_t blocks = (total + 15) / 16;
