@@ -102,16 +102,19 @@ constexpr int kWaveGroups = FAL_BWD_WAVE_GROUPS;
 __device__ __forceinline__ bool bwd_decode_work(const BwdParams& p, BwdWork& w) {
   const int idx = blockIdx.x;
   if (p.cu_k == nullptr) {
-    // CTAs are numbered in waves of kWaveGroups (batch, KV head) groups; inside a wave the first key
+    // CTAs are numbered in waves of up to kWaveGroups (batch, KV head) groups; inside a wave the first key
     // blocks come first (under a causal mask they see the most queries).  The CTAs that run at the
     // same time then add into the fp32 dQ accumulators of a few groups only (8 MB per group at
     // 4 heads x 4096 rows), which stay in L2 between the 32 key tiles that touch them.
     const int bh_count = p.batch * p.heads_kv;
     const int nkvblk = (p.seqlen_k + kKvTile - 1) / kKvTile;
-    const int wave = idx / (kWaveGroups * nkvblk);
-    const int first_group = wave * kWaveGroups;
-    const int groups_here = min(kWaveGroups, bh_count - first_group);
-    const int r = idx - wave * kWaveGroups * nkvblk;
+    // equal waves of at most kWaveGroups groups (a short last wave leaves SMs idle at the end)
+    const int num_waves = (bh_count + kWaveGroups - 1) / kWaveGroups;
+    const int wave_groups = (bh_count + num_waves - 1) / num_waves;
+    const int wave = idx / (wave_groups * nkvblk);
+    const int first_group = wave * wave_groups;
+    const int groups_here = min(wave_groups, bh_count - first_group);
+    const int r = idx - wave * wave_groups * nkvblk;
     w.kvblk = r / groups_here;
     const int bh = first_group + r % groups_here;
     w.batch = bh / p.heads_kv;
