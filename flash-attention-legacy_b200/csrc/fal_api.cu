@@ -127,7 +127,11 @@ int check_device() {
   return cached[dev] == 1 ? FAL_OK : FAL_ERR_UNSUPPORTED_DEVICE;
 }
 
+// 64 and 128 everywhere; 256 in the forward and in decode only (its backward is not built).
 bool head_dim_ok(int d) { return d == 64 || d == 128; }
+bool inference_head_dim_ok(int d) { return head_dim_ok(d) || d == 256; }
+// Query rows per forward CTA (one 128-row tile at head_dim 256, two otherwise).
+int forward_cta_rows(int d) { return d == 256 ? 128 : 256; }
 
 int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
@@ -192,7 +196,7 @@ const char* fal_strerror(int code) {
   switch (code) {
     case FAL_OK: return "ok";
     case FAL_ERR_INVALID_ARGUMENT: return "invalid argument (shape, stride, alignment or null pointer)";
-    case FAL_ERR_UNSUPPORTED_HEAD_DIM: return "unsupported head_dim (64 and 128 are supported)";
+    case FAL_ERR_UNSUPPORTED_HEAD_DIM: return "unsupported head_dim (64 and 128; 256 in the forward and decode entries only)";
     case FAL_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
     case FAL_ERR_CUDA: return "CUDA runtime error";
     case FAL_ERR_TENSOR_MAP: return "TMA descriptor could not be built";
@@ -232,7 +236,7 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || seqlen_q <= 0 || seqlen_k < 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
       o_strides->head % 8 != 0 || o_strides->batch % 8 != 0)
     return FAL_ERR_INVALID_ARGUMENT;
@@ -268,7 +272,8 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   CUtensorMap tk_half;
   if (pair && (rc = make_tensor_map(&tk_half, k, head_dim, seqlen_k, heads_kv, batch, to_rs(k_strides), 64)))
     return rc;
-  p.num_qblk = pair ? (seqlen_q + 511) / 512 : (seqlen_q + 255) / 256;
+  const int cta_rows = forward_cta_rows(head_dim);
+  p.num_qblk = pair ? (seqlen_q + 511) / 512 : (seqlen_q + cta_rows - 1) / cta_rows;
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q * (pair ? 2 : 1);
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
@@ -293,7 +298,7 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   if (num_seqs <= 0 || total_q <= 0 || total_k < 0 || heads_q <= 0 || heads_kv <= 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
       o_strides->head % 8 != 0)
     return FAL_ERR_INVALID_ARGUMENT;
@@ -330,7 +335,7 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   CUtensorMap tk_half;
   if (pair && (rc = make_tensor_map(&tk_half, k, head_dim, total_k, heads_kv, 1, ks, 64))) return rc;
   // Every sequence rounds up to whole 256-row (512-row) blocks: at most one extra block each.
-  p.num_qblk = (pair ? total_q / 512 : total_q / 256) + num_seqs;
+  p.num_qblk = (pair ? total_q / 512 : total_q / forward_cta_rows(head_dim)) + num_seqs;
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q * (pair ? 2 : 1);
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
@@ -544,7 +549,7 @@ int fal_decode(const void* q, void* k_cache, void* v_cache, const fal_strides* k
   if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || capacity <= 0) return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o) ||
       !aligned16(k_new) || !aligned16(v_new))
@@ -602,7 +607,7 @@ int fal_decode_static(const void* q, void* k_cache, void* v_cache, const fal_str
   if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || capacity <= 0) return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o) ||
       !aligned16(k_new) || !aligned16(v_new))

@@ -408,6 +408,7 @@ cudaError_t launch_decode_append(const DecodeParams& p, cudaStream_t stream) {
 cudaError_t launch_decode_splitk(const DecodeParams& p, cudaStream_t stream) {
   if (p.head_dim == 128) return launch_splitk_t<128>(p, stream);
   if (p.head_dim == 64) return launch_splitk_t<64>(p, stream);
+  if (p.head_dim == 256) return launch_splitk_t<256>(p, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -35,7 +35,6 @@ namespace {
 constexpr int kFwdThreads = 384;  // three warpgroups: softmax 0, softmax 1, {producer, issuer, 2 idle}
 constexpr int kTileM = 128;   // query rows per softmax warpgroup
 constexpr int kTileN = 128;   // keys per step
-constexpr int kCtaRows = 2 * kTileM;
 constexpr float kNegInf = -INFINITY;
 // Skip the O rescale while the running maximum grows by less than 2^8.
 constexpr float kRescaleThreshold = 8.0f;
@@ -120,12 +119,16 @@ enum FwdBarrier : int {
 
 template <int D>
 struct FwdSmem {
-  static constexpr int kStages = (D == 128) ? 2 : 4;
+  // head_dim 256: one 128-row query tile per CTA (its O accumulator alone takes 256 of the 512 TMEM
+  // columns) and single K and V buffers (a 128 x 256 tile is 64 KB); the second softmax warpgroup idles.
+  static constexpr int kQTiles = (D == 256) ? 1 : 2;
+  static constexpr int kCtaRows = kQTiles * kTileM;
+  static constexpr int kStages = (D == 256) ? 1 : (D == 128) ? 2 : 4;
   static constexpr int kBoxes = D / 64;                 // 64-element (128-byte) column boxes
   static constexpr int kBoxBytes = kTileM * 128;        // one box of a 128-row tile
   static constexpr int kTileBytes = kBoxes * kBoxBytes;  // Q, K and V tiles are all 128 x D
   static constexpr int kQOff = 0;
-  static constexpr int kKOff = 2 * kTileBytes;
+  static constexpr int kKOff = kQTiles * kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kBarOff = kVOff + kStages * kTileBytes;
   // barriers: q_full[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_ready[2] p_ready[2] o_done[2]
@@ -151,7 +154,7 @@ struct FwdWork {
 
 // Maps blockIdx.x to a unit of work.  Returns false when the block has none
 // (packed mode launches an upper bound of blocks).
-__device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, FwdWork& w) {
+__device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, int cta_rows, FwdWork& w) {
   const int idx = blockIdx.x;
   if (p.cu_q == nullptr) {
     const int bh_count = p.batch * p.heads_q;
@@ -176,7 +179,7 @@ __device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, FwdWork& w) 
     for (int s = 0; s < p.num_seqs; ++s) {
       const int a = __ldg(p.cu_q + s);
       const int e = __ldg(p.cu_q + s + 1);
-      const int nblk = (e - a + kCtaRows - 1) / kCtaRows;
+      const int nblk = (e - a + cta_rows - 1) / cta_rows;
       if (slot < first + nblk) {
         seq = s;
         q_start = a;
@@ -205,7 +208,8 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   constexpr int NS = L::kStages;
 
   FwdWork wk;
-  if (!fwd_decode_work(p, wk)) return;
+  constexpr int kCtaRows = L::kCtaRows;
+  if (!fwd_decode_work(p, kCtaRows, wk)) return;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -229,7 +233,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   for (int w = 0; w < 2; ++w) {
     const int row0 = wk.qblk * kCtaRows + w * kTileM;
     int n = 0;
-    if (row0 < wk.seqlen_q) {
+    if (w < L::kQTiles && row0 < wk.seqlen_q) {
       n = nk_tiles;
       if (CAUSAL) n = min(n, row0 / kTileN + 1);
     }
@@ -576,7 +580,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_after_sync();
     }
     const float inv = (l > 0.f) ? 1.f / l : 0.f;
-    const bool row_ok = q_local < wk.seqlen_q;
+    const bool row_ok = wg < L::kQTiles && q_local < wk.seqlen_q;  // an unused second tile owns no rows
     __half* o_row = static_cast<__half*>(p.o) + wk.o_base +
                     static_cast<int64_t>(q_local) * p.o_strides.row;
 #pragma unroll
@@ -661,6 +665,10 @@ cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const C
   if (head_dim == 64) {
     return causal ? launch_fwd_t<64, true>(tq, tk, tv, p, grid, stream)
                   : launch_fwd_t<64, false>(tq, tk, tv, p, grid, stream);
+  }
+  if (head_dim == 256) {
+    return causal ? launch_fwd_t<256, true>(tq, tk, tv, p, grid, stream)
+                  : launch_fwd_t<256, false>(tq, tk, tv, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

@@ -27,7 +27,8 @@ except ImportError as e:  # same failure mode as the reference: no extension, no
     )
 
 SUPPORTED_HEAD_DIMS = (32, 64, 96, 128, 256)
-_NATIVE_HEAD_DIMS = (64, 128)
+_NATIVE_HEAD_DIMS = (64, 128, 256)   # what the forward and decode kernels run at
+_BACKWARD_HEAD_DIMS = (64, 128)      # head_dim 256 has no backward kernel: inference only
 
 
 def _native_head_dim(d: int) -> int:
@@ -39,9 +40,13 @@ def _native_head_dim(d: int) -> int:
         return 64
     if d == 96:
         return 128
+    raise NotImplementedError(f"head_dim={d} is not built (32, 64, 96, 128 and 256 are)")
+
+
+def _no_backward(d: int):
     raise NotImplementedError(
-        f"head_dim={d} is accepted by the reference but not built for B200 yet (64 and 128 are "
-        "native; 32 and 96 run zero-padded)"
+        f"head_dim={d}: the B200 build has forward and decode kernels for it but no backward kernel "
+        "(the reference's backward accepts it); run under torch.no_grad() or use head_dim <= 128"
     )
 
 
@@ -72,7 +77,7 @@ class FlashAttentionFunc(Function):
         assert k.dtype == torch.float16 and v.dtype == torch.float16
         assert q.is_cuda and q.dim() == 4
         d = q.shape[-1]
-        assert d in _NATIVE_HEAD_DIMS, f"native head_dim must be 64 or 128, got {d}"
+        assert d in _NATIVE_HEAD_DIMS, f"native head_dim must be 64, 128 or 256, got {d}"
         h_q, h_kv = q.shape[1], k.shape[1]
         assert h_q % h_kv == 0, f"H_q ({h_q}) must be divisible by H_kv ({h_kv})"
 
@@ -91,6 +96,8 @@ class FlashAttentionFunc(Function):
     @staticmethod
     def backward(ctx, grad_output):
         q, k, v, o, lse = ctx.saved_tensors
+        if q.shape[-1] not in _BACKWARD_HEAD_DIMS:
+            _no_backward(q.shape[-1])
         dq, dk, dv = flash_attn_legacy_cuda.backward(
             _kernel_ready(grad_output), q, k, v, o, lse, ctx.softmax_scale, ctx.is_causal
         )
@@ -143,7 +150,7 @@ class FlashAttnVarlenFunc(Function):
         assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
         assert q.is_cuda and q.dim() == 3
         d = q.shape[-1]
-        assert d in _NATIVE_HEAD_DIMS, f"native head_dim must be 64 or 128, got {d}"
+        assert d in _NATIVE_HEAD_DIMS, f"native head_dim must be 64, 128 or 256, got {d}"
 
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         cu_seqlens_q = cu_seqlens_q.contiguous().to(torch.int32)
@@ -161,6 +168,8 @@ class FlashAttnVarlenFunc(Function):
     @staticmethod
     def backward(ctx, grad_output):
         q, k, v, o, lse, cu_q, cu_k = ctx.saved_tensors
+        if q.shape[-1] not in _BACKWARD_HEAD_DIMS:
+            _no_backward(q.shape[-1])
         dq, dk, dv = flash_attn_legacy_cuda.backward_varlen(
             grad_output.contiguous(), q, k, v, o, lse, cu_q, cu_k,
             ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.softmax_scale, ctx.is_causal,
@@ -226,7 +235,7 @@ def flash_attn_with_kvcache(
     assert q.dim() == 4 and q.shape[1] == 1, "q must be [B, 1, H_q, d]"
     assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
     b, _, hq, d = q.shape
-    assert d in _NATIVE_HEAD_DIMS, f"decode supports head_dim 64 and 128, got {d}"
+    assert d in _NATIVE_HEAD_DIMS, f"decode supports head_dim 64, 128 and 256, got {d}"
     seq_axis = 1 if cache_layout == "bshd" else 2
     if cache_seqlens is None:
         cache_seqlens = torch.full((b,), k_cache.shape[seq_axis], dtype=torch.int32, device=q.device)

@@ -21,8 +21,8 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-_KERNEL_HEAD_DIMS = (32, 64, 96, 128)
-_DECODE_HEAD_DIMS = (64, 128)
+_KERNEL_HEAD_DIMS = (32, 64, 96, 128, 256)   # 256: forward only, so only without autograd
+_DECODE_HEAD_DIMS = (64, 128, 256)
 
 
 def _resolve_causal(module, attention_mask, q_len, kwargs):
@@ -111,7 +111,9 @@ def flash_attn_legacy_forward(
     def to_half(t):
         return t if t.dtype == torch.float16 else t.half()
 
-    if keep is not None and q_len == kv_len and d in _KERNEL_HEAD_DIMS and query.is_cuda:
+    kernel_ok = d in _KERNEL_HEAD_DIMS and query.is_cuda and not (
+        d == 256 and torch.is_grad_enabled() and query.requires_grad)
+    if keep is not None and q_len == kv_len and kernel_ok:
         out = _padded_prefill(to_half(query), to_half(key), to_half(value), keep, scaling,
                               is_causal).to(in_dtype)
     elif keep is not None:
@@ -125,7 +127,7 @@ def flash_attn_legacy_forward(
             additive.masked_fill_((kj > qi)[None, None], float("-inf"))
         out = _eager_attention(query, key, value, additive, scaling, False)
         out = torch.nan_to_num(out).transpose(1, 2).contiguous()  # rows that see no key at all
-    elif q_len == kv_len and d in _KERNEL_HEAD_DIMS and query.is_cuda:
+    elif q_len == kv_len and kernel_ok:
         # Prefill.  As in the reference, attention_mask is not consulted on this branch.
         # Inputs are read through their strides and the result is written as [B, q_len, Hq, d]
         # memory, so neither side of the call copies (the reference copies q, k, v and the output:

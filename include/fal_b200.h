@@ -18,7 +18,7 @@
  *     internal wait ran out (a bug indicator); read it after synchronising.
  *
  * All tensor data is fp16, statistics are fp32, index data int32.
- * Supported head_dim: 64 and 128.
+ * Supported head_dim: 64 and 128; 256 in the forward (fal_fwd, fal_fwd_varlen) and in decode only.
  */
 #ifndef FAL_B200_H_
 #define FAL_B200_H_

@@ -30,9 +30,9 @@ def test_binding_exposes_the_reference_extension_functions():
 
 def test_native_head_dim_mapping():
     from flash_attn_legacy.flash_attn import _native_head_dim
-    assert [_native_head_dim(d) for d in (32, 64, 96, 128)] == [64, 64, 128, 128]
+    assert [_native_head_dim(d) for d in (32, 64, 96, 128, 256)] == [64, 64, 128, 128, 256]
     with pytest.raises(NotImplementedError):
-        _native_head_dim(256)
+        _native_head_dim(80)
 
 
 def test_operator_asserts_fire_before_any_launch(fal):

@@ -458,10 +458,52 @@ def test_operator_reads_strided_views_and_writes_bnhd_memory(fal, causal):
     assert fal.flash_attention(q.detach(), k.detach(), v.detach(), is_causal=causal).is_contiguous()
 
 
-def test_head_dim_256_is_reported_as_not_built(fal):
-    q = torch.zeros(1, 1, 16, 256, dtype=torch.float16, device="cuda")
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("n", [1, 200, 1000])
+def test_head_dim_256_forward(ext, causal, n):
+    """head_dim 256 has forward and decode kernels only (one 128-row query tile per CTA)."""
+    gen = torch.Generator().manual_seed(n)
+    b, hq, hkv, d = 2, 4, 2, 256
+    q, k, v = rand_half(gen, b, hq, n, d), rand_half(gen, b, hkv, n, d), rand_half(gen, b, hkv, n, d)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = ext.forward(q.cuda(), k.cuda(), v.cuda(), scale, causal)
+    o_ref, lse_ref = orc.attention_fwd(q, k, v, scale, causal)
+    if n == 1:
+        assert torch.equal(o.cpu(), v.repeat_interleave(hq // hkv, 1))
+    else:
+        check_fwd(o, lse, o_ref, lse_ref)
+    assert ext.device_status() == 0
+
+
+def test_head_dim_256_varlen_forward_and_decode(ext):
+    gen = torch.Generator().manual_seed(8)
+    lens = [300, 17, 520]
+    total, hq, hkv, d = sum(lens), 4, 2, 256
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    q, k, v = rand_half(gen, total, hq, d), rand_half(gen, total, hkv, d), rand_half(gen, total, hkv, d)
+    o, lse = ext.forward_varlen(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens), 0.07, True)
+    o_ref, lse_ref = orc.varlen_fwd(q, k, v, cu, cu, 0.07, True)
+    check_fwd(o, lse, o_ref, lse_ref)
+
+    b, cap = 3, 2048
+    kc, vc = rand_half(gen, b, cap, hkv, d), rand_half(gen, b, cap, hkv, d)
+    qd = rand_half(gen, b, hq, d)
+    seqlens = torch.tensor([1, 1500, 2048], dtype=torch.int32)
+    out = ext.decode(qd.cuda(), kc.cuda(), vc.cuda(), seqlens.cuda(), 0.07)
+    out = out[0] if isinstance(out, (list, tuple)) else out
+    ref = orc.decode_fwd(qd, kc, vc, seqlens, 0.07)
+    ref = ref[0] if isinstance(ref, (list, tuple)) else ref
+    assert orc.rel_max_err(out, ref) <= orc.TOL_O
+    assert ext.device_status() == 0
+
+
+def test_head_dim_256_has_no_backward(fal):
+    q = torch.randn(1, 2, 64, 256, dtype=torch.float16, device="cuda", requires_grad=True)
+    out = fal.flash_attention(q, q.detach(), q.detach(), is_causal=True)
     with pytest.raises(NotImplementedError):
-        fal.flash_attention(q, q, q)
+        out.sum().backward()
+    with torch.no_grad():
+        assert fal.flash_attention(q, q, q).shape == q.shape
 
 
 def test_varlen_func_autograd(fal):
