@@ -306,8 +306,10 @@ class FlashMultiHeadAttention(nn.Module):
         in_dtype = q.dtype
         if in_dtype != torch.float16:
             q, k, v = q.half(), k.half(), v.half()
-        out = flash_attention(q, k, v, self.scale, self.causal)
+        # q, k, v are [B,H,N,d] views of the projections' [B,N,H,d] memory and the result is written
+        # as [B,N,H,d] memory: no copy on either side of the kernel (the reference copies all four).
+        out = flash_attention(q, k, v, self.scale, self.causal, out_layout="bnhd")
         if in_dtype != torch.float16:
             out = out.to(in_dtype)
-        out = out.transpose(1, 2).contiguous().view(bsz, n, self.embed_dim)
+        out = out.transpose(1, 2).contiguous().view(bsz, n, self.embed_dim)  # already contiguous
         return self.dropout(self.out_proj(out))
