@@ -242,7 +242,30 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int n_max = max(ntile[0], ntile[1]);
 
   // ---- one-time setup -------------------------------------------------------
-  if (threadIdx.x == 0) {
+  // The producer lane initialises the barriers and sends the first loads (Q, K_0, V_0) on their way
+  // before the CTA-wide sync, so that their latency overlaps the TMEM allocation and the sync.
+  auto load_q = [&](int w) {
+    mbar_arrive_expect_tx(bar(iQFull + w), L::kTileBytes);
+    const int row = wk.q_row0 + wk.qblk * kCtaRows + w * kTileM;
+    for (int bx = 0; bx < L::kBoxes; ++bx)
+      tma_load_4d(sbase + L::kQOff + w * L::kTileBytes + bx * L::kBoxBytes, &tm_q, bar(iQFull + w),
+                  bx * 64, row, wk.head, wk.batch);
+  };
+  auto load_k = [&](int j) {
+    const int s = j % NS;
+    mbar_arrive_expect_tx(bar(iKFull + s), L::kTileBytes);
+    for (int bx = 0; bx < L::kBoxes; ++bx)
+      tma_load_4d(sbase + L::kKOff + s * L::kTileBytes + bx * L::kBoxBytes, &tm_k, bar(iKFull + s),
+                  bx * 64, wk.k_row0 + j * kTileN, wk.kv_head, wk.batch);
+  };
+  auto load_v = [&](int j) {
+    const int s = j % NS;
+    mbar_arrive_expect_tx(bar(iVFull + s), L::kTileBytes);
+    for (int bx = 0; bx < L::kBoxes; ++bx)
+      tma_load_4d(sbase + L::kVOff + s * L::kTileBytes + bx * L::kBoxBytes, &tm_v, bar(iVFull + s),
+                  bx * 64, wk.k_row0 + j * kTileN, wk.kv_head, wk.batch);
+  };
+  if (threadIdx.x == 8 * 32) {
     *abort_flag = 0;
     mbar_init(bar(iQFull + 0), 1);
     mbar_init(bar(iQFull + 1), 1);
@@ -259,6 +282,15 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(bar(iODone + w), 1);
     }
     fence_mbar_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    for (int w = 0; w < 2; ++w)
+      if (ntile[w] > 0) load_q(w);
+    if (n_max > 0) {
+      load_k(0);
+      load_v(0);
+    }
   }
   if (warp == 9) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -276,31 +308,13 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (warp == 8) {
     // ===================== TMA producer =====================================
     if (lane == 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      for (int w = 0; w < 2; ++w) {
-        if (ntile[w] == 0) continue;
-        mbar_arrive_expect_tx(bar(iQFull + w), L::kTileBytes);
-        const int row = wk.q_row0 + wk.qblk * kCtaRows + w * kTileM;
-        for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_load_4d(sbase + L::kQOff + w * L::kTileBytes + bx * L::kBoxBytes, &tm_q,
-                      bar(iQFull + w), bx * 64, row, wk.head, wk.batch);
-      }
-      for (int j = 0; j < n_max; ++j) {
+      for (int j = 1; j < n_max; ++j) {  // tile 0 went out during setup
         const int s = j % NS;
         const int use = j / NS;
-        const int row = wk.k_row0 + j * kTileN;
         if (use > 0) mbar_wait(bar(iKEmpty + s), (use - 1) & 1, wctx, kBarKEmpty + s);
-        mbar_arrive_expect_tx(bar(iKFull + s), L::kTileBytes);
-        for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_load_4d(sbase + L::kKOff + s * L::kTileBytes + bx * L::kBoxBytes, &tm_k,
-                      bar(iKFull + s), bx * 64, row, wk.kv_head, wk.batch);
+        load_k(j);
         if (use > 0) mbar_wait(bar(iVEmpty + s), (use - 1) & 1, wctx, kBarVEmpty + s);
-        mbar_arrive_expect_tx(bar(iVFull + s), L::kTileBytes);
-        for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_load_4d(sbase + L::kVOff + s * L::kTileBytes + bx * L::kBoxBytes, &tm_v,
-                      bar(iVFull + s), bx * 64, row, wk.kv_head, wk.batch);
+        load_v(j);
       }
     }
     __syncwarp();
