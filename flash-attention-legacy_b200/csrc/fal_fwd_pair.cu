@@ -26,7 +26,8 @@
 // (leader's TMA transaction + the peer's forwarder); P-ready barriers live in the leader and
 // count one elected arrival per softmax warp of both CTAs; everything the MMAs signal (S ready,
 // O done, stage empty) is committed to the same barrier of BOTH CTAs.  A stage holds the K and
-// the V half of one key tile.
+// the V half of one key tile and has one "empty" barrier per pair tile (each tile's issuer
+// commits its own); a token barrier per tile keeps the two issuers strictly alternating.
 // TMEM columns per CTA: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P (fp16) overwrites
 // the first 64 columns of its S tile and feeds the P V MMA straight from TMEM.
 #define FAL_WAIT_SLOW_PATH_INLINE  // this kernel uses setmaxnreg, which rules out calls
