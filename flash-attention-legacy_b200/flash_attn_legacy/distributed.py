@@ -215,28 +215,36 @@ def ring_attention_backward(d_out, q, k, v, o, lse, softmax_scale: float, causal
                         torch.zeros(v.shape, dtype=torch.float32, device=v.device)], group, rank, world)
     dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     lse_late = None
+    grads_in_flight = None
     for step in range(world):
-        # K/V of the next step can move while this step computes; the gradient accumulators
-        # can only move once this step has added its share.
+        # K/V of the next step move while this step computes.  The gradient accumulators of the
+        # shard held now were sent by the previous rank after ITS previous step: that transfer is
+        # left in flight during this step's kernels and only waited for when their result is added.
         kv_reqs = kv.start() if step + 1 < world else []
         plan = _shard_plan(zigzag, causal, rank, (rank - step) % world, rows)
+        partial = None
         if plan is not None:
             qs, ks, masked = plan
             k_cur, v_cur = kv.cur
-            dk_cur, dv_cur = grads.cur
             if qs.stop - qs.start == rows:
                 lse_rows = lse
             else:
                 if lse_late is None:
                     lse_late = lse[:, :, qs].contiguous()
                 lse_rows = lse_late
-            dq_p, dk_p, dv_p = local_bwd(d_out[:, :, qs], q[:, :, qs], k_cur[:, :, ks], v_cur[:, :, ks],
-                                         o[:, :, qs], lse_rows, softmax_scale, masked)
+            partial = local_bwd(d_out[:, :, qs], q[:, :, qs], k_cur[:, :, ks], v_cur[:, :, ks],
+                                o[:, :, qs], lse_rows, softmax_scale, masked)
+        if grads_in_flight is not None:
+            grads.finish(grads_in_flight)
+        if partial is not None:
+            dq_p, dk_p, dv_p = partial
+            dk_cur, dv_cur = grads.cur
             dq[:, :, qs] += dq_p
             dk_cur[:, :, ks] += dk_p
             dv_cur[:, :, ks] += dv_p
         kv.finish(kv_reqs)
-        grads.finish(grads.start())
+        grads_in_flight = grads.start()
+    grads.finish(grads_in_flight)
     # After `world` hops every accumulator is back at its owner.
     dk_own, dv_own = grads.cur
     return dq.to(q.dtype), dk_own.to(k.dtype), dv_own.to(v.dtype)
