@@ -127,9 +127,9 @@ int check_device() {
   return cached[dev] == 1 ? FAL_OK : FAL_ERR_UNSUPPORTED_DEVICE;
 }
 
-// 64 and 128 everywhere; 256 in the forward and in decode only (its backward is not built).
-bool head_dim_ok(int d) { return d == 64 || d == 128; }
-bool inference_head_dim_ok(int d) { return head_dim_ok(d) || d == 256; }
+// 64, 128 and 256 in every entry point (the head_dim-256 backward runs on column halves).
+bool head_dim_ok(int d) { return d == 64 || d == 128 || d == 256; }
+bool inference_head_dim_ok(int d) { return head_dim_ok(d); }
 // Query rows per forward CTA (one 128-row tile at head_dim 256, two otherwise).
 int forward_cta_rows(int d) { return d == 256 ? 128 : 256; }
 
@@ -196,7 +196,7 @@ const char* fal_strerror(int code) {
   switch (code) {
     case FAL_OK: return "ok";
     case FAL_ERR_INVALID_ARGUMENT: return "invalid argument (shape, stride, alignment or null pointer)";
-    case FAL_ERR_UNSUPPORTED_HEAD_DIM: return "unsupported head_dim (64 and 128; 256 in the forward and decode entries only)";
+    case FAL_ERR_UNSUPPORTED_HEAD_DIM: return "unsupported head_dim (64, 128 and 256 are built)";
     case FAL_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
     case FAL_ERR_CUDA: return "CUDA runtime error";
     case FAL_ERR_TENSOR_MAP: return "TMA descriptor could not be built";
@@ -236,6 +236,9 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || seqlen_q <= 0 || seqlen_k < 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
+  // The bottom-right-aligned mask is defined here for a query block that ends where the keys end.
+  if (is_causal < 0 || is_causal > FAL_CAUSAL_BOTTOM_RIGHT) return FAL_ERR_INVALID_ARGUMENT;
+  if (is_causal == FAL_CAUSAL_BOTTOM_RIGHT && seqlen_k < seqlen_q) return FAL_ERR_INVALID_ARGUMENT;
   if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
       o_strides->head % 8 != 0 || o_strides->batch % 8 != 0)
@@ -264,11 +267,13 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   p.heads_kv = heads_kv;
   p.seqlen_q = seqlen_q;
   p.seqlen_k = seqlen_k;
+  p.causal_shift = is_causal == FAL_CAUSAL_BOTTOM_RIGHT ? seqlen_k - seqlen_q : 0;
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const bool pair = use_pair_forward(head_dim, seqlen_q);
+  // (the CTA-pair kernel knows the top-left mask only)
+  const bool pair = p.causal_shift == 0 && use_pair_forward(head_dim, seqlen_q);
   CUtensorMap tk_half;
   if (pair && (rc = make_tensor_map(&tk_half, k, head_dim, seqlen_k, heads_kv, batch, to_rs(k_strides), 64)))
     return rc;

@@ -36,6 +36,14 @@
 // TMEM columns: S^T/P^T [0,128), dP^T/dQ [128,256) (the dQ tile of a step reuses the columns of
 //               that step's consumed dP^T), dV [256,256+D), dK [256+D,256+2D).
 // Shared memory at head_dim 128: K 32K, V 32K, Q 2 x 32K, dO 32K, dS^T 32K, dQ staging 2 x 16K.
+//
+// head_dim 256 (SPLIT = true) runs the head_dim-128 layout on column halves: two CTAs share a key
+// tile, each owning 128 of the 256 columns of dV, dK and dQ.  The two score GEMMs contract over all
+// 256 columns, so every step first loads the OTHER half of K, Q, V and dO into the (single) tile
+// buffers and starts S^T and dP^T on it, then loads its own half over them and accumulates; from
+// there the step is the head_dim-128 step.  K and V are therefore reloaded every step (they come
+// from L2) and a step's loads and GEMMs run one after the other: it is the reference's head_dim
+// 256 backward made available, not a tuned kernel.
 #include "fal_common.h"
 #include "fal_launch.h"
 #include "sm100_ptx.cuh"
@@ -52,7 +60,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 enum BwdBarrier : int {
   kBbKFull = 100, kBbVFull = 101, kBbQFull = 110, kBbDoFull = 120, kBbStatFull = 130,
   kBbQEmpty = 140, kBbDoEmpty = 145, kBbSReady = 150, kBbDpReady = 160, kBbPReady = 161,
-  kBbDsReady = 162, kBbDqReady = 164, kBbDqFree = 165, kBbAllDone = 166,
+  kBbDsReady = 162, kBbDqReady = 164, kBbDqFree = 165, kBbAllDone = 166, kBbAFull = 170, kBbADone = 171,
 };
 
 template <int D>
@@ -73,8 +81,8 @@ struct BwdSmem {
   static constexpr int kStatBytes = kQStages * 2 * kQTile * 4;
   static constexpr int kBarOff = kStatOff + kStatBytes;
   // k_full v_full q_full[2] q_empty[2] stat_full[2] do_full do_empty
-  // s_ready dp_ready dq_ready dq_free p_ready ds_ready all_done ds_free
-  static constexpr int kNumBars = 2 + 6 + 2 + 8;
+  // s_ready dp_ready dq_ready dq_free p_ready ds_ready all_done ds_free a_full a_done
+  static constexpr int kNumBars = 2 + 6 + 2 + 8 + 2;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kBytes = kMiscOff + 16;
   // No slack for re-aligning the base: at head_dim 128 the layout fills the 227 KB limit, so the
@@ -99,8 +107,7 @@ struct BwdWork {
 #endif
 constexpr int kWaveGroups = FAL_BWD_WAVE_GROUPS;
 
-__device__ __forceinline__ bool bwd_decode_work(const BwdParams& p, BwdWork& w) {
-  const int idx = blockIdx.x;
+__device__ __forceinline__ bool bwd_decode_work(const BwdParams& p, int idx, BwdWork& w) {
   if (p.cu_k == nullptr) {
     // CTAs are numbered in waves of up to kWaveGroups (batch, KV head) groups; inside a wave the first key
     // blocks come first (under a causal mask they see the most queries).  The CTAs that run at the
@@ -195,16 +202,19 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool SPLIT>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
   using L = BwdSmem<D>;
-  constexpr int NS = L::kQStages;
+  constexpr int NS = SPLIT ? 1 : L::kQStages;
+  // SPLIT: head_dim is 2 * D; CTAs 2n and 2n+1 share key tile n and own columns [0, D) and [D, 2D).
+  const int col_own = SPLIT ? static_cast<int>(blockIdx.x & 1) * D : 0;
+  const int col_other = SPLIT ? D - col_own : 0;
 
   BwdWork wk;
-  if (!bwd_decode_work(p, wk)) return;
+  if (!bwd_decode_work(p, SPLIT ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x), wk)) return;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t sbase = smem_u32(smem_raw);
@@ -217,7 +227,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto bar = [&](int i) { return bar0 + 8u * i; };
   constexpr int iKFull = 0, iVFull = 1, iQFull = 2, iQEmpty = 4, iStatFull = 6, iDoFull = 8, iDoEmpty = 9,
                 iSReady = 10, iDpReady = 11, iDqReady = 12, iDqFree = 13, iPReady = 14, iDsReady = 15,
-                iAllDone = 16, iDsFree = 17;
+                iAllDone = 16, iDsFree = 17, iAFull = 18, iADone = 19;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kMiscOff + 4);
   const WaitCtx wctx{abort_flag, p.status};
@@ -252,6 +262,8 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(bar(iDsReady), FAL_BWD_ELECT_ARRIVE ? 8 : 256);
     mbar_init(bar(iAllDone), 1);
     mbar_init(bar(iDsFree), 1);
+    mbar_init(bar(iAFull), 1);
+    mbar_init(bar(iADone), 1);
     fence_mbar_init();
   }
   if (warp == 9) {
@@ -265,7 +277,48 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   constexpr uint32_t kColS = 0, kColDpq = 128, kColDv = 256, kColDk = 256 + D;
 
   if (warp == 8) {
-    // ===================== producer: TMA + per-row statistics =================
+    // ===================== producer: TMA ======================================
+    if constexpr (SPLIT) {
+      if (lane == 0 && n_iter > 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        tma_prefetch_desc(&tm_do);
+        tma_prefetch_desc(&tm_dq);
+        const uint32_t k_s = sbase + L::kKOff, v_s = sbase + L::kVOff, q_s = sbase + L::kQOff,
+                       do_s = sbase + L::kDoOff;
+        for (int i = 0; i < n_iter; ++i) {
+          const int head = wk.kv_head * group + i / nq;
+          const int row = wk.q_row0 + (qt0 + i % nq) * kQTile;
+          const int krow = wk.k_row0 + kv0;
+          // every GEMM of the previous step has completed: all four tile buffers are free
+          if (i >= 1) mbar_wait(bar(iQEmpty), (i - 1) & 1, wctx, kBbQEmpty);
+          mbar_arrive_expect_tx(bar(iAFull), 4 * L::kTileBytes);
+          for (int bx = 0; bx < L::kBoxes; ++bx) {
+            const int x = col_other + bx * 64;
+            tma_load_4d(k_s + bx * L::kBoxBytes, &tm_k, bar(iAFull), x, krow, wk.kv_head, wk.batch);
+            tma_load_4d(q_s + bx * L::kBoxBytes, &tm_q, bar(iAFull), x, row, head, wk.batch);
+            tma_load_4d(v_s + bx * L::kBoxBytes, &tm_v, bar(iAFull), x, krow, wk.kv_head, wk.batch);
+            tma_load_4d(do_s + bx * L::kBoxBytes, &tm_do, bar(iAFull), x, row, head, wk.batch);
+          }
+          // the partial S^T and dP^T have read them: this CTA's own columns go over them
+          mbar_wait(bar(iADone), i & 1, wctx, kBbADone);
+          mbar_arrive_expect_tx(bar(iQFull), 2 * L::kTileBytes);
+          for (int bx = 0; bx < L::kBoxes; ++bx) {
+            const int x = col_own + bx * 64;
+            tma_load_4d(k_s + bx * L::kBoxBytes, &tm_k, bar(iQFull), x, krow, wk.kv_head, wk.batch);
+            tma_load_4d(q_s + bx * L::kBoxBytes, &tm_q, bar(iQFull), x, row, head, wk.batch);
+          }
+          mbar_arrive_expect_tx(bar(iDoFull), 2 * L::kTileBytes);
+          for (int bx = 0; bx < L::kBoxes; ++bx) {
+            const int x = col_own + bx * 64;
+            tma_load_4d(v_s + bx * L::kBoxBytes, &tm_v, bar(iDoFull), x, krow, wk.kv_head, wk.batch);
+            tma_load_4d(do_s + bx * L::kBoxBytes, &tm_do, bar(iDoFull), x, row, head, wk.batch);
+          }
+        }
+      }
+      __syncwarp();
+    } else {
     if (lane == 0 && n_iter > 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
@@ -303,6 +356,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       __syncwarp();
     }
+    }  // !SPLIT
   } else if (warp == 14) {
     // ===================== per-row statistics: lse * log2(e) and delta ========
     for (int i = 0; i < n_iter; ++i) {
@@ -345,16 +399,17 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const uint32_t ds_lo_mn = smem_desc_lo(ds_s, L::kBoxBytes);   // dS^T, MN-major B of dQ^T
 
       // acc[128 keys x 128 queries] = X[keys x D] * Y[queries x D]^T, both head_dim-contiguous
-      auto issue_xyT = [&](uint32_t d_col, uint32_t x_lo, uint32_t y_s) {
+      auto issue_xyT = [&](uint32_t d_col, uint32_t x_lo, uint32_t y_s, bool accumulate = false) {
         const uint32_t y_lo = smem_desc_lo(y_s, 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
           umma_ss(tmem_base + d_col, smem_desc_join(x_lo + off, kHi), smem_desc_join(y_lo + off, kHi),
-                  idesc_st, ks > 0 ? 1u : 0u);
+                  idesc_st, (accumulate || ks > 0) ? 1u : 0u);
         }
       };
 
+      if constexpr (!SPLIT) {
       mbar_wait(bar(iKFull), 0, wctx, kBbKFull);
       mbar_wait(bar(iQFull + 0), 0, wctx, kBbQFull);
       tc_fence_after_sync();
@@ -365,12 +420,36 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_after_sync();
       issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff);
       tc_commit(bar(iDpReady));
+      }  // !SPLIT
       const uint32_t do_lo_mn = smem_desc_lo(sbase + L::kDoOff, L::kBoxBytes);
 
       for (int i = 0; i < n_iter; ++i) {
         const int st = i % NS;
         const int st1 = (i + 1) % NS;
         const uint32_t q_lo_mn = smem_desc_lo(sbase + L::kQOff + st * L::kTileBytes, L::kBoxBytes);
+        if constexpr (SPLIT) {
+          // S^T(i) and dP^T(i) in two parts: the other column half first, then this CTA's own, which
+          // stays in the tile buffers for dV, dK and dQ.  S^T goes over P^T(i-1), which dV(i-1)
+          // -- issued before -- has read; dP^T goes over dQ(i-1), which the write-back warps must
+          // have read out.
+          mbar_wait(bar(iAFull), i & 1, wctx, kBbAFull);
+          tc_fence_after_sync();
+          issue_xyT(kColS, k_lo_k, sbase + L::kQOff);
+          if (i >= 1) {
+            mbar_wait(bar(iDqFree), (i - 1) & 1, wctx, kBbDqFree);
+            tc_fence_after_sync();
+          }
+          issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff);
+          tc_commit(bar(iADone));
+          mbar_wait(bar(iQFull), i & 1, wctx, kBbQFull);
+          tc_fence_after_sync();
+          issue_xyT(kColS, k_lo_k, sbase + L::kQOff, true);
+          tc_commit(bar(iSReady));
+          mbar_wait(bar(iDoFull), i & 1, wctx, kBbDoFull);
+          tc_fence_after_sync();
+          issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff, true);
+          tc_commit(bar(iDpReady));
+        }
         // dV += P^T(i) dO(i): P^T as packed fp16 in TMEM; query columns [0,64) at +0, [64,128) at +64
         BWD_WAIT(2, bar(iPReady), i & 1, wctx, kBbPReady);
         tc_fence_after_sync();
@@ -383,7 +462,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         tc_commit(bar(iDoEmpty));  // dO(i) has no reader left once dV(i) is done
         // S^T(i+1) overwrites P^T(i): issued after dV(i), which reads it.
-        if (i + 1 < n_iter) {
+        if (!SPLIT && i + 1 < n_iter) {
           BWD_WAIT(3, bar(iQFull + st1), ((i + 1) / NS) & 1, wctx, kBbQFull + st1);
           tc_fence_after_sync();
           issue_xyT(kColS, k_lo_k, sbase + L::kQOff + st1 * L::kTileBytes);
@@ -421,7 +500,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #endif
         tc_commit(bar(iDsFree));  // both readers of the dS^T buffer are done
         // dP^T(i+1) goes where dQ(i) is: the write-back warps must have read it out first.
-        if (i + 1 < n_iter) {
+        if (!SPLIT && i + 1 < n_iter) {
           BWD_WAIT(1, bar(iDoFull), (i + 1) & 1, wctx, kBbDoFull);
           BWD_WAIT(4, bar(iDqFree), i & 1, wctx, kBbDqFree);
           tc_fence_after_sync();
@@ -562,7 +641,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const RowStrides& st_o = is_dk ? p.dk_strides : p.dv_strides;
     __half* out_row = static_cast<__half*>(is_dk ? p.dk : p.dv) + wk.batch * st_o.batch +
                       wk.kv_head * st_o.head +
-                      (static_cast<int64_t>(wk.k_row0) + kv_local) * st_o.row;
+                      (static_cast<int64_t>(wk.k_row0) + kv_local) * st_o.row + col_own;
     const float mul = is_dk ? p.scale : 1.f;
     const uint32_t t_acc = tmem_base + lane_addr + (is_dk ? kColDk : kColDv);
 #pragma unroll
@@ -637,8 +716,9 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff, hf * 64, 0, dbg_head, dbg_batch);
           tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff + L::kBoxBytes, hf * 64 + 32, 0, dbg_head, dbg_batch);
 #else
-          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff, hf * 64, grow, head, wk.batch);
-          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff + L::kBoxBytes, hf * 64 + 32, grow, head, wk.batch);
+          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff, col_own + hf * 64, grow, head, wk.batch);
+          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff + L::kBoxBytes, col_own + hf * 64 + 32, grow, head,
+                            wk.batch);
 #endif
           bulk_commit_group();
         }
@@ -761,18 +841,19 @@ __global__ void __launch_bounds__(256) fal_bwd_post_kernel(const BwdPostParams p
   *reinterpret_cast<uint4*>(dst) = out;
 }
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool SPLIT = false>
 cudaError_t launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const CUtensorMap& tdo, const CUtensorMap& tdq, const BwdParams& p, int grid,
                          cudaStream_t stream) {
-  auto kern = fal_bwd_kernel<D, CAUSAL>;
+  auto kern = fal_bwd_kernel<D, CAUSAL, SPLIT>;
   static DeviceOnce configured;
   cudaError_t e = configured.run([&] {
     return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 BwdSmem<D>::kAllocBytes);
   });
   if (e != cudaSuccess) return e;
-  kern<<<grid, kBwdThreads, BwdSmem<D>::kAllocBytes, stream>>>(tq, tk, tv, tdo, tdq, p);
+  if (SPLIT && grid > 0x3fffffff) return cudaErrorInvalidValue;
+  kern<<<SPLIT ? 2 * grid : grid, kBwdThreads, BwdSmem<D>::kAllocBytes, stream>>>(tq, tk, tv, tdo, tdq, p);
   return cudaGetLastError();
 }
 
@@ -780,7 +861,10 @@ cudaError_t launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
 
 cudaError_t launch_bwd_prep(const BwdPrepParams& p, cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(p.batch) * p.heads_q * p.rows;
-  if (p.head_dim == 128) {
+  if (p.head_dim == 256) {
+    const int64_t blocks = (total + 7) / 8;
+    fal_bwd_prep_kernel<256><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+  } else if (p.head_dim == 128) {
     const int64_t blocks = (total + 15) / 16;
     fal_bwd_prep_kernel<128><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
   } else if (p.head_dim == 64) {
@@ -802,6 +886,10 @@ cudaError_t launch_bwd(int head_dim, bool causal, const CUtensorMap& tq, const C
   if (head_dim == 64) {
     return causal ? launch_bwd_t<64, true>(tq, tk, tv, tdo, tdq, p, grid, stream)
                   : launch_bwd_t<64, false>(tq, tk, tv, tdo, tdq, p, grid, stream);
+  }
+  if (head_dim == 256) {  // two CTAs per key tile, 128 output columns each
+    return causal ? launch_bwd_t<128, true, true>(tq, tk, tv, tdo, tdq, p, grid, stream)
+                  : launch_bwd_t<128, false, true>(tq, tk, tv, tdo, tdq, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

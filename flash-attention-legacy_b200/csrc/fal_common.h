@@ -33,6 +33,7 @@ struct FwdParams {
   int seqlen_q;   // batched mode only
   int seqlen_k;   // batched mode only
   int num_qblk;   // batched: ceil(seqlen_q / 256); packed: bound on all sequences' blocks
+  int causal_shift;  // causal kernels: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
   float scale;       // softmax scale
   float scale_log2;  // softmax scale * log2(e)
   int* status;       // device status word, may be nullptr

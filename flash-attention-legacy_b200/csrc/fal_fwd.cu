@@ -200,7 +200,9 @@ __device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, int cta_rows
   return true;
 }
 
-template <int D, bool CAUSAL>
+// SHIFTED (causal only): the mask's diagonal is moved by p.causal_shift keys (bottom-right
+// alignment); the kernels of the reference's own top-left mask are compiled without it.
+template <int D, bool CAUSAL, bool SHIFTED>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -235,7 +237,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     int n = 0;
     if (w < L::kQTiles && row0 < wk.seqlen_q) {
       n = nk_tiles;
-      if (CAUSAL) n = min(n, row0 / kTileN + 1);
+      if (CAUSAL) n = min(n, SHIFTED ? (row0 + kTileM - 1 + p.causal_shift) / kTileN + 1 : row0 / kTileN + 1);
     }
     ntile[w] = n;
   }
@@ -443,9 +445,10 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #endif
       const int kv0 = j * kTileN;
       int limit = wk.seqlen_k - kv0;  // columns c < limit are visible
-      if (CAUSAL) limit = min(limit, q_local - kv0 + 1);
+      const int cshift = SHIFTED ? p.causal_shift : 0;
+      if (CAUSAL) limit = min(limit, q_local + cshift - kv0 + 1);
       const bool tile_mask =
-          (kv0 + kTileN > wk.seqlen_k) || (CAUSAL && (kv0 + kTileN - 1 > q_tile0));
+          (kv0 + kTileN > wk.seqlen_k) || (CAUSAL && (kv0 + kTileN - 1 > q_tile0 + cshift));
 
       // All 128 scores of this thread's row, one TMEM round trip.
       uint32_t sr[4][32];
@@ -654,10 +657,10 @@ namespace fal {
 namespace {
 #endif
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool SHIFTED = false>
 cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const FwdParams& p, int grid, cudaStream_t stream) {
-  auto kern = fal_fwd_kernel<D, CAUSAL>;
+  auto kern = fal_fwd_kernel<D, CAUSAL, SHIFTED>;
   static DeviceOnce configured;  // one per template instance
   cudaError_t e = configured.run([&] {
     return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -672,6 +675,12 @@ cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
 
 cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream) {
+  if (causal && p.causal_shift != 0) {
+    if (head_dim == 128) return launch_fwd_t<128, true, true>(tq, tk, tv, p, grid, stream);
+    if (head_dim == 64) return launch_fwd_t<64, true, true>(tq, tk, tv, p, grid, stream);
+    if (head_dim == 256) return launch_fwd_t<256, true, true>(tq, tk, tv, p, grid, stream);
+    return cudaErrorInvalidValue;
+  }
   if (head_dim == 128) {
     return causal ? launch_fwd_t<128, true>(tq, tk, tv, p, grid, stream)
                   : launch_fwd_t<128, false>(tq, tk, tv, p, grid, stream);

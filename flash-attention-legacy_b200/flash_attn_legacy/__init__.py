@@ -5,7 +5,8 @@ Same import surface as sirCamp/flash-attention-legacy (flash_attn_legacy/__init_
     from flash_attn_legacy import flash_attention, flash_attn_varlen_func
     out = flash_attention(q, k, v, is_causal=True)          # q [B,Hq,N,d], k/v [B,Hkv,N,d] fp16
 
-plus `flash_attn_with_kvcache` for single-token decode.  Importing the package registers
+plus `flash_attn_with_kvcache` for single-token decode and `flash_attention_chunk` for a chunk
+of new tokens against a longer cache.  Importing the package registers
 the "flash_attn_legacy" attention implementation with HuggingFace transformers when it
 is installed.
 """
@@ -16,6 +17,7 @@ from .flash_attn import (
     FlashAttention,
     FlashMultiHeadAttention,
     flash_attention,
+    flash_attention_chunk,
     flash_attn_varlen_func,
     flash_attn_with_kvcache,
 )
@@ -26,6 +28,7 @@ __all__ = [
     "flash_attention",
     "flash_attn_varlen_func",
     "flash_attn_with_kvcache",
+    "flash_attention_chunk",
     "FlashAttention",
     "FlashMultiHeadAttention",
     "check_gpu_compatibility",

@@ -27,8 +27,7 @@ except ImportError as e:  # same failure mode as the reference: no extension, no
     )
 
 SUPPORTED_HEAD_DIMS = (32, 64, 96, 128, 256)
-_NATIVE_HEAD_DIMS = (64, 128, 256)   # what the forward and decode kernels run at
-_BACKWARD_HEAD_DIMS = (64, 128)      # head_dim 256 has no backward kernel: inference only
+_NATIVE_HEAD_DIMS = (64, 128, 256)   # what the kernels run at (forward, backward and decode)
 
 
 def _native_head_dim(d: int) -> int:
@@ -43,11 +42,6 @@ def _native_head_dim(d: int) -> int:
     raise NotImplementedError(f"head_dim={d} is not built (32, 64, 96, 128 and 256 are)")
 
 
-def _no_backward(d: int):
-    raise NotImplementedError(
-        f"head_dim={d}: the B200 build has forward and decode kernels for it but no backward kernel "
-        "(the reference's backward accepts it); run under torch.no_grad() or use head_dim <= 128"
-    )
 
 
 def _kernel_ready(t: torch.Tensor) -> torch.Tensor:
@@ -96,8 +90,6 @@ class FlashAttentionFunc(Function):
     @staticmethod
     def backward(ctx, grad_output):
         q, k, v, o, lse = ctx.saved_tensors
-        if q.shape[-1] not in _BACKWARD_HEAD_DIMS:
-            _no_backward(q.shape[-1])
         dq, dk, dv = flash_attn_legacy_cuda.backward(
             _kernel_ready(grad_output), q, k, v, o, lse, ctx.softmax_scale, ctx.is_causal
         )
@@ -137,6 +129,41 @@ def flash_attention(
     return FlashAttentionFunc.apply(q, k, v, softmax_scale, is_causal, out_layout)
 
 
+def flash_attention_chunk(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: Optional[float] = None,
+    out_layout: str = "bhnd",
+) -> torch.Tensor:
+    """Causal attention of a prompt chunk against a longer key sequence (inference only).
+
+    q [B,Hq,Nq,d] holds the LAST Nq positions of the sequence whose keys and values are
+    k, v [B,Hkv,Nk,d] with Nk >= Nq: query i sees keys j <= i + (Nk - Nq) (the causal mask is
+    aligned to the bottom-right corner).  This is the step between prefill and single-token
+    decode -- prefill in chunks, or a few new tokens after a cached prefix -- which the reference
+    sends to its eager fallback with its usual top-left mask (integrations.py:63, :77-98).
+    Not in the reference's API; there is no backward for it.  Head dims 64, 128, 256.
+    """
+    assert q.dtype == torch.float16 and k.dtype == torch.float16 and v.dtype == torch.float16
+    assert q.is_cuda and q.dim() == 4
+    d = q.shape[-1]
+    assert d in _NATIVE_HEAD_DIMS, f"head_dim must be 64, 128 or 256 here, got {d}"
+    assert q.shape[1] % k.shape[1] == 0, "H_q must be divisible by H_kv"
+    assert k.shape[2] >= q.shape[2], "the key sequence must be at least as long as the query chunk"
+    assert out_layout in ("bhnd", "bnhd"), f"out_layout must be 'bhnd' or 'bnhd', got {out_layout}"
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(d)
+    out = None
+    if out_layout == "bnhd":
+        b, h_q, n, _ = q.shape
+        out = torch.empty((b, n, h_q, d), dtype=q.dtype, device=q.device).transpose(1, 2)
+    with torch.no_grad():
+        o, _ = flash_attn_legacy_cuda.forward_rect(_kernel_ready(q), _kernel_ready(k), _kernel_ready(v),
+                                                   softmax_scale, True, bottom_right=True, out=out)
+    return o
+
+
 class FlashAttnVarlenFunc(Function):
     """Packed-sequence attention; forward AND backward are single native calls.
 
@@ -168,8 +195,6 @@ class FlashAttnVarlenFunc(Function):
     @staticmethod
     def backward(ctx, grad_output):
         q, k, v, o, lse, cu_q, cu_k = ctx.saved_tensors
-        if q.shape[-1] not in _BACKWARD_HEAD_DIMS:
-            _no_backward(q.shape[-1])
         dq, dk, dv = flash_attn_legacy_cuda.backward_varlen(
             grad_output.contiguous(), q, k, v, o, lse, cu_q, cu_k,
             ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.softmax_scale, ctx.is_causal,

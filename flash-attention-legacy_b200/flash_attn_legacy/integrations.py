@@ -12,8 +12,13 @@ honoured: `register()` also registers transformers' 2-D ("which tokens are real"
 format for this name -- without that, transformers hands a custom attention function no
 mask at all, and the reference attends to padding (integrations.py:63-76) -- and a prefill
 with such a mask runs un-padded through the packed kernels.  Everything the kernels do not
-cover (an additive 4-D mask, a padding mask outside prefill, q_len > 1 with a longer key
-sequence, unsupported head_dim) keeps the reference's eager arithmetic.
+cover (an additive 4-D mask, a padding mask outside prefill, unsupported head_dim) keeps the
+reference's eager arithmetic.  A third difference: several new tokens against a longer cache
+(q_len > 1, kv_len > q_len, causal, no mask, no autograd) run through the forward kernel with
+the causal mask aligned to the END of the key sequence -- the new tokens are its last q_len
+positions -- where the reference's fallback applies its top-left mask (integrations.py:91-96),
+which hides the cached prefix from the first new tokens.  The eager fallback here aligns its
+mask the same way, so the result does not depend on which path a call takes.
 """
 import math
 from typing import Optional
@@ -21,7 +26,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-_KERNEL_HEAD_DIMS = (32, 64, 96, 128, 256)   # 256: forward only, so only without autograd
+_KERNEL_HEAD_DIMS = (32, 64, 96, 128, 256)
 _DECODE_HEAD_DIMS = (64, 128, 256)
 
 
@@ -36,7 +41,8 @@ def _resolve_causal(module, attention_mask, q_len, kwargs):
 
 
 def _eager_attention(query, key, value, attention_mask, scaling, is_causal):
-    """The reference's fallback arithmetic (integrations.py:80-98), in the model dtype."""
+    """The reference's fallback arithmetic (integrations.py:80-98), in the model dtype, with the
+    causal mask aligned to the end of the key sequence."""
     h_q, h_kv = query.shape[1], key.shape[1]
     if h_kv != h_q:
         key = key.repeat_interleave(h_q // h_kv, dim=1)
@@ -46,9 +52,12 @@ def _eager_attention(query, key, value, attention_mask, scaling, is_causal):
         scores = scores + attention_mask
     q_len, kv_len = query.shape[2], key.shape[2]
     if is_causal and q_len > 1:
+        # The queries are the last q_len positions of the key sequence.  (The reference's triu has
+        # diagonal=1 here, integrations.py:91-96: the same thing for q_len == kv_len, but behind a
+        # cached prefix it hides the prefix from the first new tokens.)
         scores = scores + torch.triu(
             torch.full((q_len, kv_len), float("-inf"), device=query.device, dtype=query.dtype),
-            diagonal=1,
+            diagonal=1 + kv_len - q_len,
         )
     return torch.matmul(torch.softmax(scores, dim=-1), value)
 
@@ -91,7 +100,7 @@ def flash_attn_legacy_forward(
     **kwargs,
 ):
     """query [B,Hq,q_len,d], key/value [B,Hkv,kv_len,d] -> (attn_output [B,q_len,Hq,d], None)."""
-    from .flash_attn import flash_attention, flash_attn_with_kvcache
+    from .flash_attn import flash_attention, flash_attention_chunk, flash_attn_with_kvcache
 
     bsz, h_q, q_len, d = query.shape
     kv_len = key.shape[2]
@@ -111,8 +120,7 @@ def flash_attn_legacy_forward(
     def to_half(t):
         return t if t.dtype == torch.float16 else t.half()
 
-    kernel_ok = d in _KERNEL_HEAD_DIMS and query.is_cuda and not (
-        d == 256 and torch.is_grad_enabled() and query.requires_grad)
+    kernel_ok = d in _KERNEL_HEAD_DIMS and query.is_cuda
     if keep is not None and q_len == kv_len and kernel_ok:
         out = _padded_prefill(to_half(query), to_half(key), to_half(value), keep, scaling,
                               is_causal).to(in_dtype)
@@ -134,6 +142,12 @@ def flash_attn_legacy_forward(
         # flash_attn.py:39, integrations.py:101).
         out = flash_attention(to_half(query), to_half(key), to_half(value),
                               softmax_scale=scaling, is_causal=is_causal, out_layout="bnhd")
+        out = out.to(in_dtype).transpose(1, 2).contiguous()  # no-op for fp16 models
+    elif (1 < q_len < kv_len and attention_mask is None and is_causal and query.is_cuda
+          and d in _DECODE_HEAD_DIMS and not (torch.is_grad_enabled() and query.requires_grad)):
+        # A chunk of new tokens against a cache that holds earlier ones.
+        out = flash_attention_chunk(to_half(query), to_half(key), to_half(value),
+                                    softmax_scale=scaling, out_layout="bnhd")
         out = out.to(in_dtype).transpose(1, 2).contiguous()  # no-op for fp16 models
     elif q_len == 1 and attention_mask is None and d in _DECODE_HEAD_DIMS and query.is_cuda:
         # Decode: one new token against the whole cache, no mask.

@@ -206,20 +206,33 @@ def forward(Q, K, V, softmax_scale, is_causal=False, out=None, lse=None):
     return [O, L]
 
 
-def forward_rect(Q, K, V, softmax_scale, is_causal=False):
-    """Forward with seqlen_k != seqlen_q allowed (top-left-aligned causal mask)."""
+def forward_rect(Q, K, V, softmax_scale, is_causal=False, bottom_right=False, out=None):
+    """Forward with seqlen_k != seqlen_q allowed.
+
+    The causal mask is top-left aligned (key j visible to query i iff j <= i, the reference's
+    convention) unless `bottom_right` is set: then, with Nk >= Nq, the queries are the last Nq
+    positions of the key sequence and query i sees keys j <= i + Nk - Nq (a prompt chunk attending
+    to a cache that already holds the earlier chunks).  `out`: optional fp16 [B,Hq,Nq,d] tensor
+    (any strides with a contiguous head_dim) to write into.
+    """
     _require_cuda_half("Q", Q, 4)
     _require_cuda_half("K", K, 4)
     _require_cuda_half("V", V, 4)
     _same_device(Q, K, V)
     B, Hq, Nq, d = Q.shape
     Hkv, Nk = K.shape[1], K.shape[2]
-    O = torch.empty((B, Hq, Nq, d), dtype=torch.float16, device=Q.device)
+    if bottom_right and Nk < Nq:
+        raise RuntimeError("bottom-right causal alignment needs seqlen_k >= seqlen_q")
+    if out is not None:
+        _require_cuda_half("out", out, 4)
+        if tuple(out.shape) != (B, Hq, Nq, d):
+            raise RuntimeError("out must be [B, H_q, N_q, d]")
+    O = out if out is not None else torch.empty((B, Hq, Nq, d), dtype=torch.float16, device=Q.device)
     L = torch.empty((B, Hq, Nq), dtype=torch.float32, device=Q.device)
     _check(_lib.fal_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), L.data_ptr(),
                         B, Hq, Hkv, Nq, Nk, d,
                         _bhn_strides(Q), _bhn_strides(K), _bhn_strides(V), _bhn_strides(O),
-                        float(softmax_scale), int(bool(is_causal)),
+                        float(softmax_scale), (2 if bottom_right else 1) if is_causal else 0,
                         _status_word(Q.device).data_ptr(), _stream(Q)))
     return [O, L]
 

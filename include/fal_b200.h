@@ -18,7 +18,7 @@
  *     internal wait ran out (a bug indicator); read it after synchronising.
  *
  * All tensor data is fp16, statistics are fp32, index data int32.
- * Supported head_dim: 64 and 128; 256 in the forward (fal_fwd, fal_fwd_varlen) and in decode only.
+ * Supported head_dim: 64, 128 and 256 in every entry point.
  */
 #ifndef FAL_B200_H_
 #define FAL_B200_H_
@@ -57,6 +57,17 @@ FAL_API int fal_last_cuda_error(void);
 /* Library version, "major.minor.patch". */
 FAL_API const char* fal_version(void);
 
+/* Values of fal_fwd's `is_causal`.  0 and 1 are the reference's flag (no mask / its top-left-aligned
+ * mask).  2 aligns the mask to the bottom-right corner instead: with Nk >= Nq, query i sees keys
+ * j <= i + (Nk - Nq), i.e. the queries are the LAST Nq positions of the key sequence -- a prompt
+ * chunk attending to a cache that already holds earlier chunks, which the reference leaves to its
+ * eager fallback (flash_attn_legacy/integrations.py:63, :77-98).  Forward only. */
+enum fal_causal {
+  FAL_CAUSAL_NONE = 0,
+  FAL_CAUSAL_TOP_LEFT = 1,
+  FAL_CAUSAL_BOTTOM_RIGHT = 2
+};
+
 /* Element strides of a tensor addressed as [batch, head, row, head_dim]. */
 typedef struct fal_strides {
   int64_t batch;
@@ -68,7 +79,8 @@ typedef struct fal_strides {
  * Batched forward.  Stands in for flash_attn_forward
  * (csrc/flash_attn_legacy.cpp:42-98; bound as `forward` at :295-298).
  *   q [B,Hq,Nq,d], k/v [B,Hkv,Nk,d], o [B,Hq,Nq,d] fp16; lse [B,Hq,Nq] fp32 contiguous.
- *   Causal masking is top-left aligned: key j is visible to query i iff j <= i.
+ *   Causal masking (is_causal = 1) is top-left aligned: key j is visible to query i iff j <= i;
+ *   is_causal = 2 (FAL_CAUSAL_BOTTOM_RIGHT, needs Nk >= Nq) shifts the diagonal by Nk - Nq.
  *   lse = natural-log sum-exp of the scaled, masked scores.
  */
 FAL_API int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse,

@@ -40,21 +40,28 @@ def _expand_kv(x, reps):
     return x if reps == 1 else x.repeat_interleave(reps, dim=1)
 
 
-def _scores(q, k, scale, causal):
-    """fp32 scaled scores [B,H,Nq,Nk] with the top-left-aligned causal mask applied."""
+def _scores(q, k, scale, causal, causal_shift=0):
+    """fp32 scaled scores [B,H,Nq,Nk] with the causal mask applied: key j is hidden from query i
+    when j > i + causal_shift (0 = the reference's top-left-aligned mask)."""
     s = torch.matmul(q.float(), k.float().transpose(-2, -1)) * scale
     if causal:
         nq, nk = s.shape[-2], s.shape[-1]
-        mask = torch.triu(torch.ones(nq, nk, dtype=torch.bool), diagonal=1)
+        mask = torch.triu(torch.ones(nq, nk, dtype=torch.bool), diagonal=1 + causal_shift)
         s.masked_fill_(mask, float("-inf"))
     return s
 
 
-def attention_fwd(q, k, v, scale, causal=False):
-    """q [B,Hq,Nq,d], k/v [B,Hkv,Nk,d] (any float dtype) -> (O fp32 [B,Hq,Nq,d], LSE fp32 [B,Hq,Nq])."""
+def attention_fwd(q, k, v, scale, causal=False, causal_shift=0):
+    """q [B,Hq,Nq,d], k/v [B,Hkv,Nk,d] (any float dtype) -> (O fp32 [B,Hq,Nq,d], LSE fp32 [B,Hq,Nq]).
+
+    `causal_shift = Nk - Nq` gives the bottom-right-aligned mask of a chunk of new tokens behind a
+    cached prefix: the same ref_attention arithmetic with the diagonal of its triu mask
+    (tests/test_flash_attn.py:27-30) moved, so that the chunk's rows equal the last Nq rows of the
+    square causal problem over all Nk positions (tests/test_oracle.py checks exactly that).
+    """
     reps = q.shape[1] // k.shape[1]
     kf, vf = _expand_kv(k, reps), _expand_kv(v, reps)
-    s = _scores(q, kf, scale, causal)
+    s = _scores(q, kf, scale, causal, causal_shift)
     lse = torch.logsumexp(s, dim=-1)
     p = torch.softmax(s, dim=-1)
     return torch.matmul(p, vf.float()), lse

@@ -82,6 +82,9 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.fal_fwd(fake, fake, fake, fake, fake, 1, 2, 2, 128, 128, 80, st, st, st, st, 0.125, 0, None, None) == -2
     # non-positive scale
     assert lib.fal_fwd(fake, fake, fake, fake, fake, 1, 2, 2, 128, 128, 64, st, st, st, st, 0.0, 0, None, None) == -1
+    # causal mode outside {0, 1, 2}; bottom-right alignment with fewer keys than queries
+    assert lib.fal_fwd(fake, fake, fake, fake, fake, 1, 2, 2, 128, 128, 64, st, st, st, st, 0.125, 3, None, None) == -1
+    assert lib.fal_fwd(fake, fake, fake, fake, fake, 1, 2, 2, 128, 64, 64, st, st, st, st, 0.125, 2, None, None) == -1
     # misaligned output pointer
     assert lib.fal_fwd(fake, fake, fake, fake + 2, fake, 1, 2, 2, 128, 128, 64, st, st, st, st, 0.125, 0, None, None) == -1
 

@@ -78,13 +78,14 @@ def test_hook_fallback_branch_matches_the_oracle_on_cpu():
     assert weights is None and out.shape == (2, 1, 8, 32)
     ref, _ = orc.decode_fwd(q[:, :, 0], k.transpose(1, 2), v.transpose(1, 2), torch.tensor([37, 37]), 0.2)
     assert torch.allclose(out[:, 0], ref, atol=1e-5)
-    # additive mask and causal chunk: same arithmetic as the reference's fallback
+    # additive mask and causal chunk: the reference's fallback arithmetic, with the four queries
+    # taken as the LAST four of the 37 positions (the reference's triu keeps diagonal=1 there)
     mask = torch.zeros(2, 1, 4, 37)
     mask[..., 1] = float("-inf")
     q4 = torch.randn(2, 8, 4, 32, generator=g)
     out2, _ = flash_attn_legacy_forward(torch.nn.Module(), q4, k, v, mask, scaling=0.2, is_causal=True)
     kk, vv = k.repeat_interleave(4, 1), v.repeat_interleave(4, 1)
-    s = q4 @ kk.transpose(-1, -2) * 0.2 + mask + torch.triu(torch.full((4, 37), float("-inf")), 1)
+    s = q4 @ kk.transpose(-1, -2) * 0.2 + mask + torch.triu(torch.full((4, 37), float("-inf")), 1 + 37 - 4)
     assert torch.allclose(out2, (torch.softmax(s, -1) @ vv).transpose(1, 2), atol=1e-5)
 
 

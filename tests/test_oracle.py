@@ -122,6 +122,20 @@ def test_backward_matches_autograd():
         assert torch.allclose(a, b, atol=1e-5)
 
 
+def test_shifted_causal_mask_is_the_tail_of_the_square_problem():
+    """A chunk of the last Nq queries with causal_shift = Nk - Nq sees what those rows see in the
+    reference's square causal attention over all Nk positions."""
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(2, 4, 300, 32, generator=g).half()
+    k = torch.randn(2, 2, 300, 32, generator=g).half()
+    v = torch.randn(2, 2, 300, 32, generator=g).half()
+    o_full, lse_full = orc.attention_fwd(q, k, v, 0.2, True)
+    for nq in (1, 77, 300):
+        o, lse = orc.attention_fwd(q[:, :, -nq:], k, v, 0.2, True, causal_shift=300 - nq)
+        assert torch.allclose(o, o_full[:, :, -nq:], atol=1e-6)
+        assert torch.allclose(lse, lse_full[:, :, -nq:], atol=1e-6)
+
+
 def test_decode_empty_and_full_cache():
     kc, vc, q = torch.randn(2, 8, 1, 16), torch.randn(2, 8, 1, 16), torch.randn(2, 2, 16)
     o, lse = orc.decode_fwd(q, kc, vc, torch.tensor([0, 8]), 0.25)

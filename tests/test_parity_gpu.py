@@ -461,7 +461,7 @@ def test_operator_reads_strided_views_and_writes_bnhd_memory(fal, causal):
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("n", [1, 200, 1000])
 def test_head_dim_256_forward(ext, causal, n):
-    """head_dim 256 has forward and decode kernels only (one 128-row query tile per CTA)."""
+    """head_dim 256 forward: one 128-row query tile per CTA."""
     gen = torch.Generator().manual_seed(n)
     b, hq, hkv, d = 2, 4, 2, 256
     q, k, v = rand_half(gen, b, hq, n, d), rand_half(gen, b, hkv, n, d), rand_half(gen, b, hkv, n, d)
@@ -497,13 +497,78 @@ def test_head_dim_256_varlen_forward_and_decode(ext):
     assert ext.device_status() == 0
 
 
-def test_head_dim_256_has_no_backward(fal):
-    q = torch.randn(1, 2, 64, 256, dtype=torch.float16, device="cuda", requires_grad=True)
-    out = fal.flash_attention(q, q.detach(), q.detach(), is_causal=True)
-    with pytest.raises(NotImplementedError):
-        out.sum().backward()
-    with torch.no_grad():
-        assert fal.flash_attention(q, q, q).shape == q.shape
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("n", [1, 64, 200, 513])
+def test_head_dim_256_backward(ext, causal, n):
+    """head_dim 256 backward: two CTAs per key tile, 128 columns of dQ, dK and dV each, GQA 2:1."""
+    gen = torch.Generator().manual_seed(256 + n)
+    b, hq, hkv, d = 2, 4, 2, 256
+    q, k, v, do = (rand_half(gen, b, hq, n, d), rand_half(gen, b, hkv, n, d), rand_half(gen, b, hkv, n, d),
+                   rand_half(gen, b, hq, n, d))
+    scale = 1.0 / math.sqrt(d)
+    o, lse, grads = run_fwd_bwd(ext, q, k, v, do, scale, causal)
+    assert ext.device_status() == 0
+    ref = orc.attention_bwd(q, k, v, do, scale, causal)
+    if n == 1:
+        assert grads[0].abs().max().item() < 1e-3 and grads[1].abs().max().item() < 1e-3
+        assert orc.rel_max_err(grads[2], ref[2]) <= orc.TOL_GRAD
+    else:
+        check_grads(grads, ref)
+
+
+def test_head_dim_256_varlen_backward_and_autograd(ext, fal):
+    gen = torch.Generator().manual_seed(77)
+    lens = [300, 17, 0, 140]
+    q, k, v, do, cu = packed_inputs(gen, lens, 4, 2, 256)
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = fal.flash_attn_varlen_func(qc, kc, vc, cu.cuda(), cu.cuda(), 300, 300, causal=True)
+    out.backward(do.cuda())
+    check_grads((qc.grad, kc.grad, vc.grad), orc.varlen_bwd(q, k, v, do, cu, cu, 1 / 16, True))
+    # the batched operator through autograd, strided [B,N,H,d] inputs
+    xq, xk, xv = (torch.randn(1, 150, 2, 256, generator=gen).half() for _ in range(3))
+    g = torch.randn(1, 2, 150, 256, generator=gen).half()
+    tq, tk, tv = (t.cuda().requires_grad_(True) for t in (xq, xk, xv))
+    y = fal.flash_attention(tq.transpose(1, 2), tk.transpose(1, 2), tv.transpose(1, 2), is_causal=True)
+    y.backward(g.cuda())
+    ref = orc.attention_bwd(xq.transpose(1, 2), xk.transpose(1, 2), xv.transpose(1, 2), g, 1 / 16, True)
+    check_grads((tq.grad.transpose(1, 2), tk.grad.transpose(1, 2), tv.grad.transpose(1, 2)), ref)
+    assert ext.device_status() == 0
+
+
+@pytest.mark.parametrize("d", [64, 128, 256])
+@pytest.mark.parametrize("nq,nk", [(1, 300), (100, 100), (128, 512), (200, 777), (257, 1000), (513, 514)])
+def test_forward_with_the_causal_mask_aligned_to_the_end_of_the_keys(ext, d, nq, nk):
+    """A chunk of new tokens behind a cached prefix: query i sees keys j <= i + nk - nq."""
+    gen = torch.Generator().manual_seed(nq * 3 + nk + d)
+    b, hq, hkv = 2, 4, 2
+    q, k, v = rand_half(gen, b, hq, nq, d), rand_half(gen, b, hkv, nk, d), rand_half(gen, b, hkv, nk, d)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = ext.forward_rect(q.cuda(), k.cuda(), v.cuda(), scale, True, bottom_right=True)
+    o_ref, lse_ref = orc.attention_fwd(q, k, v, scale, True, causal_shift=nk - nq)
+    check_fwd(o, lse, o_ref, lse_ref)
+    assert ext.device_status() == 0
+    if nk > nq:  # more queries than keys: the alignment is not defined, the call is refused
+        with pytest.raises(RuntimeError):
+            ext.forward_rect(k.cuda(), q[:, :hkv].cuda(), q[:, :hkv].cuda(), scale, True, bottom_right=True)
+
+
+def test_chunked_prefill_equals_one_prefill(fal):
+    """Prefill in three chunks through flash_attention_chunk == one causal flash_attention call."""
+    gen = torch.Generator().manual_seed(99)
+    b, hq, hkv, n, d = 1, 8, 2, 700, 128
+    q, k, v = (rand_half(gen, b, hq, n, d).cuda(), rand_half(gen, b, hkv, n, d).cuda(),
+               rand_half(gen, b, hkv, n, d).cuda())
+    whole = fal.flash_attention(q, k, v, is_causal=True)
+    parts, start = [], 0
+    for size in (256, 300, 144):
+        end = start + size
+        parts.append(fal.flash_attention_chunk(q[:, :, start:end], k[:, :, :end], v[:, :, :end]))
+        start = end
+    chunked = torch.cat(parts, dim=2)
+    assert orc.rel_max_err(chunked, whole.float().cpu()) <= orc.TOL_O
+    out = fal.flash_attention_chunk(q[:, :, -50:], k, v, out_layout="bnhd")
+    assert out.transpose(1, 2).is_contiguous()
+    assert orc.rel_max_err(out, whole[:, :, -50:].float().cpu()) <= orc.TOL_O
 
 
 def test_varlen_func_autograd(fal):
@@ -593,6 +658,66 @@ def test_hf_registration_prefill_and_generate(fal):
     ext.profile_enable(False)
     assert out.shape == (2, 24)
     assert launches >= 15 * 2  # every decode step of both layers ran the split-K kernel
+
+
+def test_hf_chunk_of_new_tokens_against_a_cache(fal):
+    """24 new tokens after a cached prefix of 40: the hook runs the forward kernel with the causal
+    mask aligned to the end of the cache, and agrees with eager attention (which gets transformers'
+    explicit mask for this case)."""
+    assert fal.register()
+    ref_model = _tiny_llama("eager")
+    model = _tiny_llama("flash_attn_legacy")
+    model.load_state_dict(ref_model.state_dict())
+    ids = torch.randint(0, 1000, (2, 64), device="cuda")
+    import flash_attn_legacy_cuda as ext
+    with torch.no_grad():
+        pre = model(ids[:, :40], use_cache=True)
+        pre_ref = ref_model(ids[:, :40], use_cache=True)
+        ext.profile_enable(True)
+        ext.profile_read(ext.KERNEL_FWD)
+        chunk = model(ids[:, 40:], past_key_values=pre.past_key_values, use_cache=True).logits.float()
+        _, launches = ext.profile_read(ext.KERNEL_FWD)
+        ext.profile_enable(False)
+        chunk_ref = ref_model(ids[:, 40:], past_key_values=pre_ref.past_key_values, use_cache=True).logits.float()
+        whole = ref_model(ids).logits.float()[:, 40:]
+    assert launches == 2  # one forward-kernel launch per layer, no eager fallback
+    cos = torch.nn.functional.cosine_similarity(chunk.flatten(), chunk_ref.flatten(), dim=0).item()
+    assert cos > 0.999
+    cos = torch.nn.functional.cosine_similarity(chunk.flatten(), whole.flatten(), dim=0).item()
+    assert cos > 0.999
+
+
+def test_llama_patch_route(fal):
+    """The reference's second integration route (examples/hf_llama_patch.py: replace every
+    LlamaAttention.forward) on a tiny random LLaMA, as its tests/test_transformers.py does."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "flash-attention-legacy_b200",
+                        "examples", "hf_llama_patch.py")
+    spec = importlib.util.spec_from_file_location("hf_llama_patch", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    ref_model = _tiny_llama("eager")
+    model = _tiny_llama("eager")
+    model.load_state_dict(ref_model.state_dict())
+    assert mod.patch_llama_attention(model) is model
+    ids = torch.randint(0, 1000, (2, 64), device="cuda")
+    import flash_attn_legacy_cuda as ext
+    ext.profile_enable(True)
+    ext.profile_read(ext.KERNEL_FWD)
+    with torch.no_grad():
+        a = model(ids).logits.float()
+        b = ref_model(ids).logits.float()
+    _, launches = ext.profile_read(ext.KERNEL_FWD)
+    ext.profile_enable(False)
+    assert launches == 2
+    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+    assert cos > 0.999
+    with torch.no_grad():
+        out = model.generate(ids[:, :8], max_new_tokens=12, do_sample=False)
+        out_ref = ref_model.generate(ids[:, :8], max_new_tokens=12, do_sample=False)
+    assert out.shape == (2, 20)
+    assert (out == out_ref).float().mean().item() > 0.8  # greedy tokens of random weights: near-ties may flip
 
 
 def test_hf_padded_batch_runs_unpadded_through_the_packed_kernels(fal):
