@@ -201,10 +201,10 @@ def run_reference(args):
     }))
 
 
-def run_decode_extra(ext, peaks, steps=256, batch=64):
+def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3):
     """Secondary metric: KV-cache split-K decode with appends, B=64 Hq=32 Hkv=8 d=128, cache 32768."""
     B, Hq, Hkv, S, d = batch, 32, 8, 32768, 128
-    g = torch.Generator(device="cuda").manual_seed(3)
+    g = torch.Generator(device="cuda").manual_seed(seed)
     kc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
     vc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
     lens0 = torch.randint(1024, S - steps + 1, (B,), device="cuda", generator=g).to(torch.int32)
@@ -231,7 +231,7 @@ def run_decode_extra(ext, peaks, steps=256, batch=64):
     mean_len = lens0.float().mean().item() + (steps + 1) / 2.0
     kv_bytes = mean_len * B * Hkv * d * 2 * 2  # K and V, fp16, read once per KV head
     res = {"workload": f"decode_B{B}_Hq32_Hkv8_d128_cache32768_{steps}steps_with_append",
-           "ms_per_step": ms, "kv_gbs": kv_bytes / ms / 1e6,
+           "ms_per_step": ms, "kv_bytes_per_step": kv_bytes, "kv_gbs": kv_bytes / ms / 1e6,
            "frac_of_hbm_peak": kv_bytes / ms / 1e6 / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
            "launches_per_step": 3}
     if k_n:
@@ -240,6 +240,95 @@ def run_decode_extra(ext, peaks, steps=256, batch=64):
     del kc, vc
     torch.cuda.empty_cache()
     return res
+
+
+def _max_over_ranks(dist, dev, x):
+    if dist is None:
+        return x
+    t = torch.tensor([x], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def run_varlen(args, rank, world, local, dist, ext):
+    """Secondary metric: 16 packed causal sequences of 64..4096 tokens (seeded), H=16, d=128, forward +
+    backward.  The 16 heads are dealt to the ranks (every rank sees the same length mix); no collective."""
+    H, d, num_seqs = 16, 128, 16
+    if H % world != 0:
+        raise SystemExit("the varlen workload shards 16 heads: use 1, 2, 4, 8 or 16 ranks")
+    h_local = H // world
+    dev = torch.device("cuda", local)
+    lens = torch.randint(64, 4097, (num_seqs,), generator=torch.Generator().manual_seed(2))
+    cu = torch.zeros(num_seqs + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    total, max_len = int(cu[-1]), int(lens.max())
+    cu = cu.to(dev)
+    gen = torch.Generator(device="cuda").manual_seed(20 + rank)
+    q, k, v, do = (torch.randn(total, h_local, d, device=dev, generator=gen).half() for _ in range(4))
+    scale = 1.0 / math.sqrt(d)
+
+    def step():
+        o, lse = ext.forward_varlen(q, k, v, cu, cu, max_len, max_len, scale, True)
+        return ext.backward_varlen(do, q, k, v, o, lse, cu, cu, max_len, max_len, scale, True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = _max_over_ranks(dist, dev, e0.elapsed_time(e1) / args.steps)
+    flops = 3.5 * 2.0 * H * d * float((lens.double() ** 2).sum())  # causal half counted once
+    status = ext.device_status()
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"varlen_16seqs_64to4096_{total}tokens_H16_d128_causal_fwd_bwd",
+                       "parallelism": f"{h_local} of 16 heads per rank, no collective"},
+            "device_status": status}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_decode(args, rank, world, local, dist, ext):
+    """Secondary metric: the KV-cache decode of run_decode_extra with its 64 batch entries dealt to
+    the ranks (each rank holds its entries' caches); no collective.  Metric: KV bytes streamed per second."""
+    if 64 % world != 0:
+        raise SystemExit("the decode workload shards 64 batch entries: use a power-of-two rank count")
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+    if dist is not None:
+        dist.barrier()
+    res = run_decode_extra(ext, peaks, steps=256, batch=64 // world, seed=3 + rank)
+    ms = _max_over_ranks(dist, dev, res["ms_per_step"])
+    total_bytes = res["kv_bytes_per_step"]
+    if dist is not None:
+        t = torch.tensor([total_bytes], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        total_bytes = t.item()
+    status = ext.device_status()
+    if rank == 0:
+        gbs = total_bytes / ms / 1e6
+        print(json.dumps({
+            "metric": "decode_kv_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": 256,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "dtype": "f16",
+            "data": "synthetic",
+            "config": {"workload": "decode_B64_Hq32_Hkv8_d128_cache32768_256steps_with_append",
+                       "parallelism": f"{64 // world} of 64 batch entries per rank, no collective"},
+            "frac_of_hbm_peak_per_gpu": gbs / world / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
+            "device_status": status}))
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 def run_long_context(args, rank, world, local, dist, ext):
@@ -312,9 +401,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and decode extras")
-    ap.add_argument("--workload", default="gqa_fwd_bwd", choices=["gqa_fwd_bwd", "long_context"],
-                    help="long_context: B=1 Hq=32 Hkv=8 N=131072 d=128 causal forward+backward, the sequence "
-                         "sharded contiguously over the ranks with the ring K/V exchange (secondary metric)")
+    ap.add_argument("--workload", default="gqa_fwd_bwd", choices=["gqa_fwd_bwd", "long_context", "varlen", "decode"],
+                    help="secondary metrics.  long_context: B=1 Hq=32 Hkv=8 N=131072 d=128 causal forward+backward, "
+                         "the sequence sharded over the ranks with the ring K/V exchange; varlen: 16 packed "
+                         "sequences of 64..4096 tokens, H=16 d=128, heads dealt to the ranks; decode: batch 64 "
+                         "split-K decode over a 32768-token cache, batch entries dealt to the ranks")
     ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"],
                     help="long_context with more than one rank: how the sequence rows are dealt to the ranks")
     ap.add_argument("--decode-profile", action="store_true",
@@ -334,6 +425,12 @@ def main():
 
     if args.workload == "long_context":
         run_long_context(args, rank, world, local, dist, ext)
+        return
+    if args.workload == "varlen":
+        run_varlen(args, rank, world, local, dist, ext)
+        return
+    if args.workload == "decode":
+        run_decode(args, rank, world, local, dist, ext)
         return
 
     if args.decode_profile:

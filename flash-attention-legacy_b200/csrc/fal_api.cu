@@ -58,8 +58,12 @@ int make_tensor_map(CUtensorMap* map, const void* base, int head_dim, int64_t ro
                               static_cast<cuuint64_t>(rows > 0 ? rows : 1),
                               static_cast<cuuint64_t>(heads > 0 ? heads : 1),
                               static_cast<cuuint64_t>(batch > 0 ? batch : 1)};
+  // A dimension of extent <= 1 is never stepped along: any valid stride will do.  A longer one needs
+  // a positive stride (a broadcast view, stride 0, cannot be described to the TMA unit).
+  if ((rows > 1 && st.row <= 0) || (heads > 1 && st.head <= 0) || (batch > 1 && st.batch <= 0))
+    return FAL_ERR_INVALID_ARGUMENT;
   auto fix = [&](int64_t s) -> cuuint64_t {
-    if (s <= 0) s = head_dim;  // unused dimension (extent 1): any valid stride will do
+    if (s <= 0) s = head_dim;
     return static_cast<cuuint64_t>(s) * 2u;
   };
   const cuuint64_t strides[3] = {fix(st.row), fix(st.head), fix(st.batch)};

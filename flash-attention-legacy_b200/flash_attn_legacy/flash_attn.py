@@ -49,10 +49,12 @@ def _kernel_ready(t: torch.Tensor) -> torch.Tensor:
 
     The library takes (batch, head, row) element strides, so a [B,H,N,d] view of [B,N,H,d] memory
     (what a QKV projection followed by .transpose(1, 2) gives) needs no copy, where the reference
-    copies every input (flash_attn.py:39).  Needed: head_dim contiguous, 16-byte aligned rows.
+    copies every input (flash_attn.py:39).  Needed: head_dim contiguous, 16-byte aligned rows, and
+    a real (positive) stride on every dimension longer than one -- an `expand`ed tensor (stride 0:
+    K/V broadcast over heads, or the gradient of a `sum`) is copied.
     """
     if (t.stride(-1) == 1 and t.data_ptr() % 16 == 0
-            and all(s % 8 == 0 for s in t.stride()[:-1])):
+            and all(s % 8 == 0 and (s > 0 or n == 1) for s, n in zip(t.stride()[:-1], t.shape[:-1]))):
         return t
     return t.contiguous()
 

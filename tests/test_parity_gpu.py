@@ -571,6 +571,27 @@ def test_chunked_prefill_equals_one_prefill(fal):
     assert orc.rel_max_err(out, whole[:, :, -50:].float().cpu()) <= orc.TOL_O
 
 
+def test_broadcast_views_are_copied_not_misread(ext, fal):
+    """K/V expanded over the heads (stride 0) and the expanded gradient of a reduction: the operator
+    copies them, the binding refuses them (tests/test_flash_attn.py:177-193 of the reference)."""
+    gen = torch.Generator().manual_seed(12)
+    b, hq, n, d = 2, 8, 128, 64
+    q, k, v = (rand_half(gen, b, hq, n, d).cuda(), rand_half(gen, b, 1, n, d).cuda(),
+               rand_half(gen, b, 1, n, d).cuda())
+    mqa = fal.flash_attention(q, k, v)
+    mha = fal.flash_attention(q, k.expand(b, hq, n, d), v.expand(b, hq, n, d))
+    assert torch.equal(mqa, mha)
+    with pytest.raises(RuntimeError):
+        ext.forward(q, k.expand(b, hq, n, d), v.expand(b, hq, n, d), 0.125, False)
+    # gradient of out.sum(dim=2): every row gets the same [B,H,1,d] slice, expanded along the rows
+    qg = q.clone().requires_grad_(True)
+    w = rand_half(gen, b, hq, d).cuda()
+    (fal.flash_attention(qg, k, v, is_causal=True).sum(dim=2) * w).sum().backward()
+    do = w[:, :, None, :].expand(b, hq, n, d).contiguous()
+    ref = orc.attention_bwd(q.cpu(), k.cpu(), v.cpu(), do.cpu(), 0.125, True)
+    assert orc.rel_max_err(qg.grad, ref[0]) <= orc.TOL_GRAD
+
+
 def test_varlen_func_autograd(fal):
     g = torch.Generator().manual_seed(31)
     lens = [70, 130, 9]
