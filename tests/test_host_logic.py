@@ -35,6 +35,20 @@ def test_native_head_dim_mapping():
         _native_head_dim(80)
 
 
+def test_strided_views_pass_through_and_broadcast_views_are_copied():
+    from flash_attn_legacy.flash_attn import _kernel_ready
+    x = torch.zeros(2, 50, 4, 64, dtype=torch.float16)
+    view = x.transpose(1, 2)                       # [B,H,N,d] view of [B,N,H,d] memory
+    assert _kernel_ready(view) is view
+    kv = torch.zeros(2, 1, 50, 64, dtype=torch.float16)
+    assert _kernel_ready(kv) is kv                 # extent-1 dimensions may have any stride
+    wide = kv.expand(2, 4, 50, 64)                 # stride 0 over the heads
+    assert wide.stride(1) == 0 and _kernel_ready(wide).stride(1) > 0
+    rows = torch.zeros(2, 4, 1, 64, dtype=torch.float16).expand(2, 4, 50, 64)
+    assert _kernel_ready(rows).is_contiguous()     # the gradient of a sum over the rows
+    assert _kernel_ready(x[..., ::2]).is_contiguous()   # head_dim itself strided
+
+
 def test_operator_asserts_fire_before_any_launch(fal):
     q = torch.zeros(1, 2, 8, 64)
     with pytest.raises(AssertionError):
