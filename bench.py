@@ -201,8 +201,13 @@ def run_reference(args):
     }))
 
 
-def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3):
-    """Secondary metric: KV-cache split-K decode with appends, B=64 Hq=32 Hkv=8 d=128, cache 32768."""
+def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False):
+    """Secondary metric: KV-cache split-K decode with appends, B=64 Hq=32 Hkv=8 d=128, cache 32768.
+
+    graph=True captures one step (append + split-K + combine + the length increment) in a CUDA graph
+    and replays it `steps` times: a small per-GPU batch is otherwise bound by the host's launch path,
+    not by the kernels.  Every replay appends the same new token (at a new position) and uses the same
+    query; the kernels and the bytes they move are those of the eager loop."""
     B, Hq, Hkv, S, d = batch, 32, 8, 32768, 128
     g = torch.Generator(device="cuda").manual_seed(seed)
     kc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
@@ -220,11 +225,23 @@ def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3):
     lens = lens0.clone()
     ext.profile_read(ext.KERNEL_DECODE_SPLITK)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        ext.decode(q[i], kc, vc, lens, scale, kn[i], vn[i], out=out)
-        lens += 1
-    e1.record()
+    if graph:
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            ext.decode(q[0], kc, vc, lens, scale, kn[0], vn[0], out=out)
+            lens += 1
+        lens.copy_(lens0)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(steps):
+            cg.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(steps):
+            ext.decode(q[i], kc, vc, lens, scale, kn[i], vn[i], out=out)
+            lens += 1
+        e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
     k_ms, k_n = ext.profile_read(ext.KERNEL_DECODE_SPLITK)
@@ -233,7 +250,7 @@ def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3):
     res = {"workload": f"decode_B{B}_Hq32_Hkv8_d128_cache32768_{steps}steps_with_append",
            "ms_per_step": ms, "kv_bytes_per_step": kv_bytes, "kv_gbs": kv_bytes / ms / 1e6,
            "frac_of_hbm_peak": kv_bytes / ms / 1e6 / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
-           "launches_per_step": 3}
+           "launches_per_step": 3, "launch_path": "cuda graph replay" if graph else "eager"}
     if k_n:
         res["splitk_kernel_ms"] = k_ms / k_n
         res["splitk_kernel_gbs"] = kv_bytes / (k_ms / k_n) / 1e6
@@ -309,7 +326,8 @@ def run_decode(args, rank, world, local, dist, ext):
     peaks = measured_peaks()
     if dist is not None:
         dist.barrier()
-    res = run_decode_extra(ext, peaks, steps=256, batch=64 // world, seed=3 + rank)
+    shard = args.decode_batch if (world == 1 and args.decode_batch > 0) else 64 // world
+    res = run_decode_extra(ext, peaks, steps=256, batch=shard, seed=3 + rank, graph=args.decode_graph)
     ms = _max_over_ranks(dist, dev, res["ms_per_step"])
     total_bytes = res["kv_bytes_per_step"]
     if dist is not None:
@@ -324,7 +342,8 @@ def run_decode(args, rank, world, local, dist, ext):
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "dtype": "f16",
             "data": "synthetic",
             "config": {"workload": "decode_B64_Hq32_Hkv8_d128_cache32768_256steps_with_append",
-                       "parallelism": f"{64 // world} of 64 batch entries per rank, no collective"},
+                       "parallelism": f"{shard} of 64 batch entries per rank, no collective",
+                       "launch_path": res["launch_path"]},
             "frac_of_hbm_peak_per_gpu": gbs / world / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
             "device_status": status}))
     if dist is not None:
@@ -408,6 +427,11 @@ def main():
                          "split-K decode over a 32768-token cache, batch entries dealt to the ranks")
     ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"],
                     help="long_context with more than one rank: how the sequence rows are dealt to the ranks")
+    ap.add_argument("--decode-graph", action="store_true",
+                    help="decode workload: replay one captured step as a CUDA graph instead of launching eagerly")
+    ap.add_argument("--decode-batch", type=int, default=0,
+                    help="decode workload on one rank: run this many of the 64 batch entries (what one of "
+                         "64/N ranks holds), to see a shard's step without the other GPUs")
     ap.add_argument("--decode-profile", action="store_true",
                     help="run only a small decode case (batch 16, a few steps): the case profilers capture")
     args = ap.parse_args()

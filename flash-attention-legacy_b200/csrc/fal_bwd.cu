@@ -319,44 +319,44 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       __syncwarp();
     } else {
-    if (lane == 0 && n_iter > 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      tma_prefetch_desc(&tm_do);
-      tma_prefetch_desc(&tm_dq);
-      mbar_arrive_expect_tx(bar(iKFull), L::kTileBytes);
-      for (int bx = 0; bx < L::kBoxes; ++bx)
-        tma_load_4d(sbase + L::kKOff + bx * L::kBoxBytes, &tm_k, bar(iKFull), bx * 64,
-                    wk.k_row0 + kv0, wk.kv_head, wk.batch);
-      mbar_arrive_expect_tx(bar(iVFull), L::kTileBytes);
-      for (int bx = 0; bx < L::kBoxes; ++bx)
-        tma_load_4d(sbase + L::kVOff + bx * L::kBoxBytes, &tm_v, bar(iVFull), bx * 64,
-                    wk.k_row0 + kv0, wk.kv_head, wk.batch);
-    }
-    for (int i = 0; i < n_iter; ++i) {
-      const int st = i % NS;
-      const int head = wk.kv_head * group + i / nq;
-      const int qt = qt0 + i % nq;
-      const int row = wk.q_row0 + qt * kQTile;
-      if (i >= NS) BWD_WAIT(0, bar(iQEmpty + st), ((i / NS) - 1) & 1, wctx, kBbQEmpty + st);
-      if (lane == 0) {
-        mbar_arrive_expect_tx(bar(iQFull + st), L::kTileBytes);
+      if (lane == 0 && n_iter > 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        tma_prefetch_desc(&tm_do);
+        tma_prefetch_desc(&tm_dq);
+        mbar_arrive_expect_tx(bar(iKFull), L::kTileBytes);
         for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_load_4d(sbase + L::kQOff + st * L::kTileBytes + bx * L::kBoxBytes, &tm_q,
-                      bar(iQFull + st), bx * 64, row, head, wk.batch);
-      }
-      // dO has a single buffer: it is reloaded as soon as dV of the previous step has read it.
-      if (lane == 0) {
-        if (i >= 1) BWD_WAIT(21, bar(iDoEmpty), (i - 1) & 1, wctx, kBbDoEmpty);
-        mbar_arrive_expect_tx(bar(iDoFull), L::kTileBytes);
+          tma_load_4d(sbase + L::kKOff + bx * L::kBoxBytes, &tm_k, bar(iKFull), bx * 64,
+                      wk.k_row0 + kv0, wk.kv_head, wk.batch);
+        mbar_arrive_expect_tx(bar(iVFull), L::kTileBytes);
         for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_load_4d(sbase + L::kDoOff + bx * L::kBoxBytes, &tm_do, bar(iDoFull), bx * 64, row, head,
-                      wk.batch);
+          tma_load_4d(sbase + L::kVOff + bx * L::kBoxBytes, &tm_v, bar(iVFull), bx * 64,
+                      wk.k_row0 + kv0, wk.kv_head, wk.batch);
       }
-      __syncwarp();
+      for (int i = 0; i < n_iter; ++i) {
+        const int st = i % NS;
+        const int head = wk.kv_head * group + i / nq;
+        const int qt = qt0 + i % nq;
+        const int row = wk.q_row0 + qt * kQTile;
+        if (i >= NS) BWD_WAIT(0, bar(iQEmpty + st), ((i / NS) - 1) & 1, wctx, kBbQEmpty + st);
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar(iQFull + st), L::kTileBytes);
+          for (int bx = 0; bx < L::kBoxes; ++bx)
+            tma_load_4d(sbase + L::kQOff + st * L::kTileBytes + bx * L::kBoxBytes, &tm_q,
+                        bar(iQFull + st), bx * 64, row, head, wk.batch);
+        }
+        // dO has a single buffer: it is reloaded as soon as dV of the previous step has read it.
+        if (lane == 0) {
+          if (i >= 1) BWD_WAIT(21, bar(iDoEmpty), (i - 1) & 1, wctx, kBbDoEmpty);
+          mbar_arrive_expect_tx(bar(iDoFull), L::kTileBytes);
+          for (int bx = 0; bx < L::kBoxes; ++bx)
+            tma_load_4d(sbase + L::kDoOff + bx * L::kBoxBytes, &tm_do, bar(iDoFull), bx * 64, row, head,
+                        wk.batch);
+        }
+        __syncwarp();
+      }
     }
-    }  // !SPLIT
   } else if (warp == 14) {
     // ===================== per-row statistics: lse * log2(e) and delta ========
     for (int i = 0; i < n_iter; ++i) {
@@ -410,17 +410,17 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       };
 
       if constexpr (!SPLIT) {
-      mbar_wait(bar(iKFull), 0, wctx, kBbKFull);
-      mbar_wait(bar(iQFull + 0), 0, wctx, kBbQFull);
-      tc_fence_after_sync();
-      issue_xyT(kColS, k_lo_k, sbase + L::kQOff);
-      tc_commit(bar(iSReady));
-      mbar_wait(bar(iVFull), 0, wctx, kBbVFull);
-      mbar_wait(bar(iDoFull), 0, wctx, kBbDoFull);
-      tc_fence_after_sync();
-      issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff);
-      tc_commit(bar(iDpReady));
-      }  // !SPLIT
+        mbar_wait(bar(iKFull), 0, wctx, kBbKFull);
+        mbar_wait(bar(iQFull + 0), 0, wctx, kBbQFull);
+        tc_fence_after_sync();
+        issue_xyT(kColS, k_lo_k, sbase + L::kQOff);
+        tc_commit(bar(iSReady));
+        mbar_wait(bar(iVFull), 0, wctx, kBbVFull);
+        mbar_wait(bar(iDoFull), 0, wctx, kBbDoFull);
+        tc_fence_after_sync();
+        issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff);
+        tc_commit(bar(iDpReady));
+      }
       const uint32_t do_lo_mn = smem_desc_lo(sbase + L::kDoOff, L::kBoxBytes);
 
       for (int i = 0; i < n_iter; ++i) {
