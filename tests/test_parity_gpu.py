@@ -349,6 +349,43 @@ def test_decode_hf_cache_layout(ext):
     assert orc.rel_max_err(o, o_ref) <= orc.TOL_O
 
 
+def test_decode_step_replayed_as_a_cuda_graph(ext):
+    """One decode step (append, split-K, combine, length increment) captured once and replayed: every
+    replay must give what the oracle gives for the cache as it then stands.  (A small per-GPU batch is
+    bound by the launch path; replaying a graph removes it.)"""
+    g = torch.Generator().manual_seed(44)
+    B, S, hkv, hq, d = 3, 2048, 2, 8, 128
+    kc, vc = rand_half(g, B, S, hkv, d), rand_half(g, B, S, hkv, d)
+    q, kn, vn = rand_half(g, B, hq, d), rand_half(g, B, hkv, d), rand_half(g, B, hkv, d)
+    lens0 = torch.tensor([0, 1023, 2040], dtype=torch.int32)
+    kc_d, vc_d, q_d, kn_d, vn_d = (t.cuda() for t in (kc, vc, q, kn, vn))
+    lens = lens0.cuda()
+    out = torch.empty(B, hq, d, dtype=torch.float16, device="cuda")
+    scale = 1 / math.sqrt(d)
+    scratch_k, scratch_v = kc_d.clone(), vc_d.clone()
+    ext.decode(q_d, scratch_k, scratch_v, lens.clone(), scale, kn_d, vn_d, out=out)  # first call: one-time set-up
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ext.decode(q_d, kc_d, vc_d, lens, scale, kn_d, vn_d, out=out)
+        lens += 1
+    lens.copy_(lens0.cuda())            # capture does not run the kernels; the caches are still untouched
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    for step in range(3):
+        q_d.copy_(rand_half(g, B, hq, d))          # new inputs go into the captured buffers
+        kn_d.copy_(rand_half(g, B, hkv, d))
+        vn_d.copy_(rand_half(g, B, hkv, d))
+        graph.replay()
+        cur = lens0 + step
+        for b in range(B):
+            kc_ref[b, cur[b]] = kn_d[b].cpu()
+            vc_ref[b, cur[b]] = vn_d[b].cpu()
+        o_ref, _ = orc.decode_fwd(q_d.cpu(), kc_ref, vc_ref, cur + 1, scale)
+        assert orc.rel_max_err(out, o_ref) <= orc.TOL_O, step
+    assert lens.cpu().tolist() == (lens0 + 3).tolist()
+    assert ext.device_status() == 0
+
+
 def test_config4_decode_256_steps_with_appends(ext):
     """batch 64, Hq=32, Hkv=8, d=128, caches [64,32768,8,128], lengths uniform in [1024, 32768-256]
     (clamped so that 256 appended tokens fit), 256 decode steps with appends.  The oracle checks
