@@ -548,11 +548,13 @@ size_t fal_decode_workspace_bytes(int batch, int heads_q, int capacity, int head
   return static_cast<size_t>(rows) * (head_dim + 2) * sizeof(float);
 }
 
-int fal_decode(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,
-               const fal_strides* v_strides, const int32_t* cache_seqlens, const void* k_new,
-               const void* v_new, void* o, float* lse, int batch, int heads_q, int heads_kv,
-               int capacity, int head_dim, float softmax_scale, void* workspace,
-               size_t workspace_bytes, int* status, void* stream) {
+namespace {
+int decode_with_workspace(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,
+                          const fal_strides* v_strides, const int32_t* cache_starts,
+                          const int32_t* cache_seqlens, const void* k_new, const void* v_new, void* o,
+                          float* lse, int batch, int heads_q, int heads_kv, int capacity, int head_dim,
+                          float softmax_scale, void* workspace, size_t workspace_bytes, int* status,
+                          void* stream) {
   if (!q || !k_cache || !v_cache || !k_strides || !v_strides || !cache_seqlens || !o || !workspace)
     return FAL_ERR_INVALID_ARGUMENT;
   if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
@@ -580,6 +582,7 @@ int fal_decode(const void* q, void* k_cache, void* v_cache, const fal_strides* k
   p.k_new = k_new;
   p.v_new = v_new;
   p.cache_seqlens = cache_seqlens;
+  p.cache_starts = cache_starts;
   p.o = o;
   p.lse = lse;
   p.batch = batch;
@@ -605,6 +608,29 @@ int fal_decode(const void* q, void* k_cache, void* v_cache, const fal_strides* k
   if (e != cudaSuccess) return cuda_fail(e);
   e = fal::launch_decode_combine(p, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+}  // namespace
+
+int fal_decode(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,
+               const fal_strides* v_strides, const int32_t* cache_seqlens, const void* k_new,
+               const void* v_new, void* o, float* lse, int batch, int heads_q, int heads_kv,
+               int capacity, int head_dim, float softmax_scale, void* workspace,
+               size_t workspace_bytes, int* status, void* stream) {
+  return decode_with_workspace(q, k_cache, v_cache, k_strides, v_strides, nullptr, cache_seqlens, k_new,
+                               v_new, o, lse, batch, heads_q, heads_kv, capacity, head_dim, softmax_scale,
+                               workspace, workspace_bytes, status, stream);
+}
+
+int fal_decode_ranged(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,
+                      const fal_strides* v_strides, const int32_t* cache_starts,
+                      const int32_t* cache_seqlens, const void* k_new, const void* v_new, void* o,
+                      float* lse, int batch, int heads_q, int heads_kv, int capacity, int head_dim,
+                      float softmax_scale, void* workspace, size_t workspace_bytes, int* status,
+                      void* stream) {
+  if (!cache_starts) return FAL_ERR_INVALID_ARGUMENT;
+  return decode_with_workspace(q, k_cache, v_cache, k_strides, v_strides, cache_starts, cache_seqlens,
+                               k_new, v_new, o, lse, batch, heads_q, heads_kv, capacity, head_dim,
+                               softmax_scale, workspace, workspace_bytes, status, stream);
 }
 
 int fal_decode_static(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,

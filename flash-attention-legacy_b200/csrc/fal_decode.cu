@@ -127,6 +127,10 @@ fal_decode_splitk_kernel(const DecodeParams p) {
   int len = __ldg(p.cache_seqlens + b);
   if (p.k_new != nullptr) len += 1;
   len = min(max(len, 0), p.capacity);
+  // With a first attended position the entry's keys are [start, len): positions below are counted
+  // from `start` (the row pointers are moved there).
+  const int start = p.cache_starts ? min(max(__ldg(p.cache_starts + b), 0), len) : 0;
+  len -= start;
   const int pos0 = split * p.split_len;
   if (pos0 >= len) return;  // this split lies beyond the sequence
   const int pos_end = min(pos0 + p.split_len, len);
@@ -155,9 +159,9 @@ fal_decode_splitk_kernel(const DecodeParams p) {
   }
 
   const __half* kbase = static_cast<const __half*>(p.k_cache) + b * p.k_strides.batch +
-                        kv_head * p.k_strides.head;
+                        kv_head * p.k_strides.head + static_cast<int64_t>(start) * p.k_strides.row;
   const __half* vbase = static_cast<const __half*>(p.v_cache) + b * p.v_strides.batch +
-                        kv_head * p.v_strides.head;
+                        kv_head * p.v_strides.head + static_cast<int64_t>(start) * p.v_strides.row;
   const uint32_t wbase = smem_u32(dec_smem) + warp * L::kWarpBytes;
 
   // Issues the loads of this warp's i-th slice (keys pos0 + (i*4 + warp)*16 ...).
@@ -333,6 +337,7 @@ __global__ void fal_decode_combine_kernel(const DecodeParams p) {
   int len = __ldg(p.cache_seqlens + b);
   if (p.k_new != nullptr) len += 1;
   len = min(max(len, 0), p.capacity);
+  if (p.cache_starts) len -= min(max(__ldg(p.cache_starts + b), 0), len);
   const int n = (len + p.split_len - 1) / p.split_len;
   const float* ml = p.part_ml + static_cast<int64_t>(bh) * p.splits * 2;
   const float* po = p.part_o + static_cast<int64_t>(bh) * p.splits * D;

@@ -95,6 +95,7 @@ struct DecodeParams {
   const void* k_new;    // optional [batch, heads_kv, head_dim] fp16 to append, else nullptr
   const void* v_new;
   const int32_t* cache_seqlens;  // [batch] valid positions before the append
+  const int32_t* cache_starts;   // optional [batch]: first position attended to (left padding), else nullptr
   void* o;              // [batch, heads_q, head_dim] fp16
   float* lse;           // optional [batch, heads_q]
   float* part_o;        // workspace [batch, heads_q, splits, head_dim] fp32

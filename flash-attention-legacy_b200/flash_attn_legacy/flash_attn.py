@@ -250,8 +250,10 @@ def flash_attn_with_kvcache(
     cache_seqlens: Optional[torch.Tensor] = None,
     softmax_scale: Optional[float] = None,
     cache_layout: str = "bshd",
+    cache_starts: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """One decode step: q [B,1,Hq,d] attends to the first cache_seqlens[b] cache positions.
+    """One decode step: q [B,1,Hq,d] attends to the first cache_seqlens[b] cache positions
+    (from position cache_starts[b] on, if given: the positions before it are left padding).
 
     Caches are [B,S,Hkv,d] (`cache_layout="bshd"`) or [B,Hkv,S,d] ("bhsd", HuggingFace).
     If k, v ([B,1,Hkv,d]) are given they are written into the caches at position
@@ -273,6 +275,7 @@ def flash_attn_with_kvcache(
     out = flash_attn_legacy_cuda.decode(
         q.reshape(b, hq, d).contiguous(), k_cache, v_cache, cache_seqlens.to(torch.int32),
         softmax_scale, k_new, v_new, cache_layout=cache_layout,
+        cache_starts=cache_starts.to(torch.int32).contiguous() if cache_starts is not None else None,
     )
     return out.view(b, 1, hq, d)
 

@@ -7,7 +7,8 @@ patches PreTrainedModel._check_and_adjust_attn_implementation exactly where the
 reference does (integrations.py:106-161).
 
 Routing differs from the reference in two places.  Single-token decode without a mask
-goes to the split-K decode kernel instead of eager matmul/softmax.  And a padding mask is
+(or with the padding mask of a left-padded batch) goes to the split-K decode kernel instead of
+eager matmul/softmax.  And a padding mask is
 honoured: `register()` also registers transformers' 2-D ("which tokens are real") mask
 format for this name -- without that, transformers hands a custom attention function no
 mask at all, and the reference attends to padding (integrations.py:63-76) -- and a prefill
@@ -60,6 +61,16 @@ def _eager_attention(query, key, value, attention_mask, scaling, is_causal):
             diagonal=1 + kv_len - q_len,
         )
     return torch.matmul(torch.softmax(scores, dim=-1), value)
+
+
+def _left_padding_starts(keep):
+    """First real position of every row of `keep` [B, N] bool, as int32 [B], if the padding of every
+    row is a prefix (what generation with a decoder-only model uses); None for any other pattern.
+    Reads one flag back from the device."""
+    n = keep.shape[1]
+    starts = (n - keep.sum(dim=1)).to(torch.int32)
+    prefix = torch.arange(n, device=keep.device)[None, :] >= starts[:, None]
+    return starts if bool((keep == prefix).all()) else None
 
 
 def _padded_prefill(query, key, value, keep, scaling, is_causal):
@@ -124,8 +135,15 @@ def flash_attn_legacy_forward(
     if keep is not None and q_len == kv_len and kernel_ok:
         out = _padded_prefill(to_half(query), to_half(key), to_half(value), keep, scaling,
                               is_causal).to(in_dtype)
+    elif (keep is not None and q_len == 1 and d in _DECODE_HEAD_DIMS and query.is_cuda
+          and (starts := _left_padding_starts(keep)) is not None):
+        # Decode of a left-padded batch: every entry skips its padded prefix of the cache.
+        out = flash_attn_with_kvcache(
+            to_half(query).transpose(1, 2), to_half(key), to_half(value),
+            softmax_scale=scaling, cache_layout="bhsd", cache_starts=starts,
+        ).to(in_dtype)
     elif keep is not None:
-        # Padding outside prefill (e.g. decode of a left-padded batch): eager arithmetic with the
+        # Other padding outside prefill: eager arithmetic with the
         # padded keys masked out; causal rows are aligned to the end of the key sequence.
         additive = torch.zeros(bsz, 1, q_len, kv_len, dtype=query.dtype, device=query.device)
         additive.masked_fill_(~keep[:, None, None, :], float("-inf"))

@@ -63,6 +63,10 @@ _lib.fal_decode.restype = _i
 _lib.fal_decode.argtypes = [_vp, _vp, _vp, _sp, _sp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
                             _vp, ctypes.c_size_t, _vp, _vp]
 
+_lib.fal_decode_ranged.restype = _i
+_lib.fal_decode_ranged.argtypes = [_vp, _vp, _vp, _sp, _sp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
+                                   _vp, ctypes.c_size_t, _vp, _vp]
+
 _lib.fal_decode_static.restype = _i
 _lib.fal_decode_static.argtypes = [_vp, _vp, _vp, _sp, _sp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
                                    _vp, _vp]
@@ -345,20 +349,25 @@ _decode_ws = {}
 
 
 def decode(q, k_cache, v_cache, cache_seqlens, softmax_scale, k_new=None, v_new=None,
-           cache_layout="bshd", return_lse=False, out=None):
+           cache_layout="bshd", return_lse=False, out=None, cache_starts=None):
     """Single-token decode.  q [B,Hq,d]; caches [B,S,Hkv,d] ("bshd") or [B,Hkv,S,d] ("bhsd").
 
     If k_new / v_new ([B,Hkv,d]) are given they are written into the caches at position
-    cache_seqlens[b] first.  Returns O [B,Hq,d] fp16 (and LSE [B,Hq] fp32 if asked).
+    cache_seqlens[b] first.  `cache_starts` (int32 [B], optional) is the first position each
+    entry attends to -- the positions before it are padding (a left-padded batch).
+    Returns O [B,Hq,d] fp16 (and LSE [B,Hq] fp32 if asked).
     """
     _require_cuda_half("q", q, 3)
     _require_cuda_half("k_cache", k_cache, 4)
     _require_cuda_half("v_cache", v_cache, 4)
-    _same_device(q, k_cache, v_cache, cache_seqlens, k_new, v_new)
+    _same_device(q, k_cache, v_cache, cache_seqlens, k_new, v_new, cache_starts)
     if not q.is_contiguous():
         raise RuntimeError("q must be contiguous [B, H_q, d]")
     if cache_seqlens.dtype != torch.int32:
         raise RuntimeError("cache_seqlens must be int32")
+    if cache_starts is not None and (cache_starts.dtype != torch.int32 or cache_starts.numel() != q.shape[0]
+                                     or not cache_starts.is_contiguous()):
+        raise RuntimeError("cache_starts must be a contiguous int32 [B] tensor")
     B, Hq, d = q.shape
     if cache_layout == "bshd":
         S, Hkv = k_cache.shape[1], k_cache.shape[2]
@@ -385,13 +394,17 @@ def decode(q, k_cache, v_cache, cache_seqlens, softmax_scale, k_new=None, v_new=
         ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
         _decode_ws.clear()
         _decode_ws[key] = ws
-    _check(_lib.fal_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ks, vs,
-                           cache_seqlens.data_ptr(),
-                           k_new.data_ptr() if k_new is not None else None,
-                           v_new.data_ptr() if v_new is not None else None,
-                           o.data_ptr(), lse.data_ptr() if lse is not None else None,
-                           B, Hq, Hkv, S, d, float(softmax_scale), ws.data_ptr(), nbytes,
-                           _status_word(q.device).data_ptr(), _stream(q)))
+    tail = (k_new.data_ptr() if k_new is not None else None,
+            v_new.data_ptr() if v_new is not None else None,
+            o.data_ptr(), lse.data_ptr() if lse is not None else None,
+            B, Hq, Hkv, S, d, float(softmax_scale), ws.data_ptr(), nbytes,
+            _status_word(q.device).data_ptr(), _stream(q))
+    if cache_starts is None:
+        _check(_lib.fal_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ks, vs,
+                               cache_seqlens.data_ptr(), *tail))
+    else:
+        _check(_lib.fal_decode_ranged(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ks, vs,
+                                      cache_starts.data_ptr(), cache_seqlens.data_ptr(), *tail))
     return (o, lse) if return_lse else o
 
 

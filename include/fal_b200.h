@@ -168,6 +168,22 @@ FAL_API int fal_decode(const void* q, void* k_cache, void* v_cache,
                int* status, void* stream);
 
 /*
+ * fal_decode for a left-padded batch: entry b attends to cache positions
+ * [cache_starts[b], cache_seqlens[b]) only (device int32 [B]; plus the appended position).
+ * Stands in for the same eager branch of the reference's hook when the batch carries padding
+ * (flash_attn_legacy/integrations.py:77-98 with its additive mask at :88-89): decoder-only models
+ * are padded on the left for generation, so the padded keys of an entry are a prefix of its cache.
+ * Same workspace and arguments as fal_decode otherwise.
+ */
+FAL_API int fal_decode_ranged(const void* q, void* k_cache, void* v_cache,
+               const fal_strides* k_strides, const fal_strides* v_strides,
+               const int32_t* cache_starts, const int32_t* cache_seqlens,
+               const void* k_new, const void* v_new, void* o, float* lse,
+               int batch, int heads_q, int heads_kv, int capacity, int head_dim,
+               float softmax_scale, void* workspace, size_t workspace_bytes,
+               int* status, void* stream);
+
+/*
  * Decode for callers that must not allocate device memory (no counterpart in the
  * reference).  Some hosts of this library cannot call cudaMalloc at the point where
  * they decode: a serving loop that was handed a fixed memory budget at start-up, a

@@ -121,8 +121,10 @@ def varlen_bwd(q, k, v, d_out, cu_q, cu_k, scale, causal=False):
     return dq, dk, dv
 
 
-def decode_fwd(q, k_cache, v_cache, cache_seqlens, scale):
-    """q [B,Hq,d]; caches [B,S,Hkv,d]; attends to the first cache_seqlens[b] positions.
+def decode_fwd(q, k_cache, v_cache, cache_seqlens, scale, cache_starts=None):
+    """q [B,Hq,d]; caches [B,S,Hkv,d]; attends to the first cache_seqlens[b] positions, from
+    position cache_starts[b] on when given (the hook's additive padding mask, integrations.py:88-89,
+    for a left-padded batch: the keys it sets to -inf are a prefix of the cache).
 
     -> (O fp32 [B,Hq,d], LSE fp32 [B,Hq]).
     """
@@ -133,10 +135,11 @@ def decode_fwd(q, k_cache, v_cache, cache_seqlens, scale):
     lse = torch.full((bsz, hq), float("-inf"), dtype=torch.float32)
     for b in range(bsz):
         n = int(cache_seqlens[b])
-        if n == 0:
+        s0 = min(int(cache_starts[b]), n) if cache_starts is not None else 0
+        if n - s0 == 0:
             continue
-        kb = _expand_kv(k_cache[b, :n].permute(1, 0, 2).unsqueeze(0), reps).float()  # [1,Hq,n,d]
-        vb = _expand_kv(v_cache[b, :n].permute(1, 0, 2).unsqueeze(0), reps).float()
+        kb = _expand_kv(k_cache[b, s0:n].permute(1, 0, 2).unsqueeze(0), reps).float()  # [1,Hq,n-s0,d]
+        vb = _expand_kv(v_cache[b, s0:n].permute(1, 0, 2).unsqueeze(0), reps).float()
         qb = q[b].float().view(1, hq, 1, d)
         s = torch.matmul(qb, kb.transpose(-2, -1)) * scale
         lse[b] = torch.logsumexp(s, dim=-1).view(hq)

@@ -49,6 +49,19 @@ def test_strided_views_pass_through_and_broadcast_views_are_copied():
     assert _kernel_ready(x[..., ::2]).is_contiguous()   # head_dim itself strided
 
 
+def test_left_padding_is_recognised_and_nothing_else():
+    from flash_attn_legacy.integrations import _left_padding_starts
+    keep = torch.ones(3, 6, dtype=torch.bool)
+    keep[1, :2] = False
+    keep[2, :5] = False
+    assert _left_padding_starts(keep).tolist() == [0, 2, 5]
+    keep[0, 3] = False                      # a hole
+    assert _left_padding_starts(keep) is None
+    right = torch.ones(2, 6, dtype=torch.bool)
+    right[1, 4:] = False                    # right padding
+    assert _left_padding_starts(right) is None
+
+
 def test_operator_asserts_fire_before_any_launch(fal):
     q = torch.zeros(1, 2, 8, 64)
     with pytest.raises(AssertionError):

@@ -136,6 +136,24 @@ def test_shifted_causal_mask_is_the_tail_of_the_square_problem():
         assert torch.allclose(lse, lse_full[:, :, -nq:], atol=1e-6)
 
 
+def test_decode_with_a_first_position_equals_the_hook_with_a_padding_mask():
+    """decode_fwd(cache_starts=...) against the eager branch of the hook given the additive mask that
+    hides each entry's left padding (flash_attn_legacy/integrations.py:80-98)."""
+    from flash_attn_legacy.integrations import _eager_attention
+    g = torch.Generator().manual_seed(9)
+    b, hq, hkv, n, d = 3, 4, 2, 40, 16
+    q = torch.randn(b, hq, 1, d, generator=g)
+    k, v = torch.randn(b, hkv, n, d, generator=g), torch.randn(b, hkv, n, d, generator=g)
+    starts = torch.tensor([0, 13, 39])
+    mask = torch.zeros(b, 1, 1, n)
+    for i in range(b):
+        mask[i, ..., :starts[i]] = float("-inf")
+    ref = _eager_attention(q, k, v, mask, 0.3, False)[:, :, 0]
+    o, _ = orc.decode_fwd(q[:, :, 0], k.transpose(1, 2), v.transpose(1, 2), torch.full((b,), n), 0.3,
+                          cache_starts=starts)
+    assert torch.allclose(o, ref, atol=1e-5)
+
+
 def test_decode_empty_and_full_cache():
     kc, vc, q = torch.randn(2, 8, 1, 16), torch.randn(2, 8, 1, 16), torch.randn(2, 2, 16)
     o, lse = orc.decode_fwd(q, kc, vc, torch.tensor([0, 8]), 0.25)

@@ -349,6 +349,31 @@ def test_decode_hf_cache_layout(ext):
     assert orc.rel_max_err(o, o_ref) <= orc.TOL_O
 
 
+@pytest.mark.parametrize("layout", ["bshd", "bhsd"])
+def test_decode_skips_a_left_padded_prefix(ext, layout):
+    """cache_starts: entry b attends to positions [start_b, len_b) (+ the appended one)."""
+    g = torch.Generator().manual_seed(61)
+    B, S, hkv, hq, d = 5, 2300, 2, 8, 128
+    kc, vc, q = rand_half(g, B, S, hkv, d), rand_half(g, B, S, hkv, d), rand_half(g, B, hq, d)
+    kn, vn = rand_half(g, B, hkv, d), rand_half(g, B, hkv, d)
+    lens = torch.tensor([2299, 1500, 1024, 7, 2000], dtype=torch.int32)
+    starts = torch.tensor([0, 1499, 1000, 7, 1025], dtype=torch.int32)   # entry 3: nothing but the new token
+    kcc, vcc = kc.cuda(), vc.cuda()
+    if layout == "bhsd":
+        kcc, vcc = kcc.transpose(1, 2).contiguous(), vcc.transpose(1, 2).contiguous()
+    o, lse = ext.decode(q.cuda(), kcc, vcc, lens.cuda(), 0.09, kn.cuda(), vn.cuda(), cache_layout=layout,
+                        return_lse=True, cache_starts=starts.cuda())
+    for b in range(B):
+        kc[b, lens[b]] = kn[b]
+        vc[b, lens[b]] = vn[b]
+    check_fwd(o, lse, *orc.decode_fwd(q, kc, vc, lens + 1, 0.09, cache_starts=starts))
+    # without an append, and an entry whose range is empty: zeros
+    o2 = ext.decode(q.cuda(), kcc, vcc, lens.cuda(), 0.09, cache_layout=layout, cache_starts=starts.cuda())
+    o2_ref, _ = orc.decode_fwd(q, kc, vc, lens, 0.09, cache_starts=starts)
+    assert orc.rel_max_err(o2, o2_ref) <= orc.TOL_O and (o2[3] == 0).all()
+    assert ext.device_status() == 0
+
+
 def test_decode_step_replayed_as_a_cuda_graph(ext):
     """One decode step (append, split-K, combine, length increment) captured once and replayed: every
     replay must give what the oracle gives for the cache as it then stands.  (A small per-GPU batch is
@@ -811,9 +836,14 @@ def test_hf_padded_batch_runs_unpadded_through_the_packed_kernels(fal):
     real = mask.bool()
     cos = torch.nn.functional.cosine_similarity(a[real].flatten(), r[real].flatten(), dim=0).item()
     assert cos > 0.999
+    ext.profile_enable(True)
+    ext.profile_read(ext.KERNEL_DECODE_SPLITK)
     with torch.no_grad():
         out = model.generate(ids[:, :24], attention_mask=mask[:, :24], max_new_tokens=8, do_sample=False)
         out_ref = ref_model.generate(ids[:, :24], attention_mask=mask[:, :24], max_new_tokens=8, do_sample=False)
+    _, decode_launches = ext.profile_read(ext.KERNEL_DECODE_SPLITK)
+    ext.profile_enable(False)
+    assert decode_launches >= 7 * 2  # the decode steps of the left-padded batch ran the split-K kernel
     assert out.shape == (2, 32)
     assert (out == out_ref).float().mean().item() > 0.9  # greedy tokens agree (fp16 ties aside)
     assert ext.device_status() == 0
