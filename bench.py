@@ -317,6 +317,58 @@ def run_varlen(args, rank, world, local, dist, ext):
         dist.destroy_process_group()
 
 
+def run_shapes(args, ext):
+    """Kernel timing on stated shapes, one JSON line each (one GPU).  A shape is
+    `pass:B,Hq,Hkv,Nq,Nk,d[:noncausal]` with pass = fwd, bwd (backward incl. its pre- and post-pass; Nq = Nk)
+    or chunk (forward of the last Nq positions against Nk keys, causal mask aligned to the end of the keys).
+    FLOPs: 4*B*Hq*d per visible (query, key) pair forward, 2.5x that backward."""
+    for spec in args.shape:
+        parts = spec.split(":")
+        kind = parts[0]
+        B, Hq, Hkv, Nq, Nk, d = (int(x) for x in parts[1].split(","))
+        causal = not (len(parts) > 2 and parts[2] == "noncausal")
+        gen = torch.Generator(device="cuda").manual_seed(7)
+        q = torch.randn(B, Hq, Nq, d, device="cuda", generator=gen).half()
+        k = torch.randn(B, Hkv, Nk, d, device="cuda", generator=gen).half()
+        v = torch.randn(B, Hkv, Nk, d, device="cuda", generator=gen).half()
+        do = torch.randn(B, Hq, Nq, d, device="cuda", generator=gen).half()
+        scale = 1.0 / math.sqrt(d)
+        if kind == "chunk":
+            pairs = Nq * (Nk - Nq) + Nq * (Nq + 1) / 2.0
+            fn = lambda: ext.forward_rect(q, k, v, scale, True, bottom_right=True)
+            mult = 1.0
+        else:
+            if Nq != Nk:
+                raise SystemExit("fwd / bwd shapes need Nq == Nk")
+            pairs = Nq * (Nq + 1) / 2.0 if causal else float(Nq) * Nk
+            if kind == "fwd":
+                fn = lambda: ext.forward(q, k, v, scale, causal)
+                mult = 1.0
+            elif kind == "bwd":
+                o, lse = ext.forward(q, k, v, scale, causal)
+                fn = lambda: ext.backward(do, q, k, v, o, lse, scale, causal)
+                mult = 2.5
+            else:
+                raise SystemExit(f"unknown pass {kind!r}: fwd, bwd or chunk")
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        flops = mult * 4.0 * B * Hq * d * pairs
+        print(json.dumps({"metric": "attn_kernel_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT,
+                          "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                          "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": spec, "pass": kind, "causal": causal,
+                                     "l2_policy": "back-to-back launches on the same tensors"},
+                          "device_status": ext.device_status()}))
+
+
 def run_decode(args, rank, world, local, dist, ext):
     """Secondary metric: the KV-cache decode of run_decode_extra with its 64 batch entries dealt to
     the ranks (each rank holds its entries' caches); no collective.  Metric: KV bytes streamed per second."""
@@ -420,13 +472,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and decode extras")
-    ap.add_argument("--workload", default="gqa_fwd_bwd", choices=["gqa_fwd_bwd", "long_context", "varlen", "decode"],
+    ap.add_argument("--workload", default="gqa_fwd_bwd", choices=["gqa_fwd_bwd", "long_context", "varlen", "decode", "shape"],
                     help="secondary metrics.  long_context: B=1 Hq=32 Hkv=8 N=131072 d=128 causal forward+backward, "
                          "the sequence sharded over the ranks with the ring K/V exchange; varlen: 16 packed "
                          "sequences of 64..4096 tokens, H=16 d=128, heads dealt to the ranks; decode: batch 64 "
                          "split-K decode over a 32768-token cache, batch entries dealt to the ranks")
     ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"],
                     help="long_context with more than one rank: how the sequence rows are dealt to the ranks")
+    ap.add_argument("--shape", action="append", default=[],
+                    help="--workload shape: pass:B,Hq,Hkv,Nq,Nk,d[:noncausal] with pass = fwd | bwd | chunk; repeatable")
     ap.add_argument("--decode-graph", action="store_true",
                     help="decode workload: replay one captured step as a CUDA graph instead of launching eagerly")
     ap.add_argument("--decode-batch", type=int, default=0,
@@ -455,6 +509,9 @@ def main():
         return
     if args.workload == "decode":
         run_decode(args, rank, world, local, dist, ext)
+        return
+    if args.workload == "shape":
+        run_shapes(args, ext)
         return
 
     if args.decode_profile:
