@@ -20,6 +20,8 @@
 //     free for the loads;
 //   - each split writes an unnormalised fp32 partial (O, max, sum); the combine
 //     kernel merges the splits that the sequence length actually reaches.
+// An optional first position per batch entry (cache_starts) skips a padded prefix
+// of the cache: the entry's row pointers start there and its length shrinks.
 #include "fal_common.h"
 #include "fal_launch.h"
 #include "sm100_ptx.cuh"

@@ -6,7 +6,10 @@
 // (csrc/kernels/flash_attn_fwd_volta.cu:170-345, :350-523 of the reference):
 // same math -- s = (q.k) * scale, top-left-aligned causal mask (kv > q masked,
 // local indices), fp32 online softmax with P rounded to fp16 before PV,
-// O = acc / l, L = m + ln(l) -- on a different machine model.
+// O = acc / l, L = m + ln(l) -- on a different machine model.  A second causal
+// instance (SHIFTED) moves the mask's diagonal by seqlen_k - seqlen_q keys for a
+// chunk of new tokens behind a cached prefix, which the reference computes
+// eagerly (flash_attn_legacy/integrations.py:77-98).
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles, each
 // with its own softmax warpgroup, S/P tile and O accumulator in TMEM.  The
