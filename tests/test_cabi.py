@@ -24,7 +24,7 @@ def declared_functions():
 
 def test_header_declares_the_expected_entry_points():
     names = declared_functions()
-    for must in ("fal_fwd", "fal_fwd_varlen", "fal_bwd", "fal_bwd_varlen", "fal_decode",
+    for must in ("fal_fwd", "fal_fwd_varlen", "fal_bwd", "fal_bwd_varlen", "fal_decode", "fal_decode_ranged",
                  "fal_bwd_workspace_bytes", "fal_decode_workspace_bytes", "fal_strerror"):
         assert must in names
 
@@ -96,6 +96,14 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     # workspace too small
     assert lib.fal_decode(fake, fake, fake, st, st, fake, None, None, fake, None, 1, 8, 2, 128, 64, 0.125,
                           fake, 16, None, None) == -3
+    # the ranged form without its first-position array
+    lib.fal_decode_ranged.restype = i
+    lib.fal_decode_ranged.argtypes = [vp, vp, vp, sp, sp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp,
+                                      ctypes.c_size_t, vp, vp]
+    assert lib.fal_decode_ranged(fake, fake, fake, st, st, None, fake, None, None, fake, None, 1, 8, 2, 128, 64,
+                                 0.125, fake, 1 << 20, None, None) == -1
+    assert lib.fal_decode_ranged(fake, fake, fake, st, st, fake, fake, None, None, fake, None, 1, 8, 2, 128, 64,
+                                 0.125, fake, 16, None, None) == -3
 
 
 def test_profile_api_is_inert_without_launches(lib):
