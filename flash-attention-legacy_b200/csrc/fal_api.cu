@@ -6,7 +6,6 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -133,7 +132,6 @@ int check_device() {
 
 // 64, 128 and 256 in every entry point (the head_dim-256 backward runs on column halves).
 bool head_dim_ok(int d) { return d == 64 || d == 128 || d == 256; }
-bool inference_head_dim_ok(int d) { return head_dim_ok(d); }
 // Query rows per forward CTA (one 128-row tile at head_dim 256, two otherwise).
 int forward_cta_rows(int d) { return d == 256 ? 128 : 256; }
 
@@ -158,8 +156,6 @@ BwdWorkspace bwd_workspace_layout(int batch, int heads_q, int rows, int head_dim
 }
 
 constexpr int kDecodeSplitLen = 1024;
-// Shortest (mean) sequence for which the forward runs on CTA pairs by default: off until measured.
-constexpr int64_t kPairForwardMinRows = INT64_MAX;
 
 // ---------------------------------------------------------------------------
 // Optional event timing around the main kernels (off by default).
@@ -216,20 +212,6 @@ int fal_last_cuda_error(void) { return g_last_cuda_error; }
 
 const char* fal_version(void) { return "0.1.0"; }
 
-namespace {
-// Which forward kernel: the CTA-pair kernel (head_dim 128) pays off once a sequence fills its
-// 512-row blocks; FAL_FWD_PAIR=0 / 1 in the environment forces the choice (tuning aid).
-bool use_pair_forward(int head_dim, int64_t rows_per_sequence) {
-  static const int forced = [] {
-    const char* e = std::getenv("FAL_FWD_PAIR");
-    return e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
-  }();
-  if (head_dim != 128) return false;
-  if (forced >= 0) return forced == 1;
-  return rows_per_sequence >= kPairForwardMinRows;
-}
-}  // namespace
-
 int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
             int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
             const fal_strides* q_strides, const fal_strides* k_strides,
@@ -243,7 +225,7 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   // The bottom-right-aligned mask is defined here for a query block that ends where the keys end.
   if (is_causal < 0 || is_causal > FAL_CAUSAL_BOTTOM_RIGHT) return FAL_ERR_INVALID_ARGUMENT;
   if (is_causal == FAL_CAUSAL_BOTTOM_RIGHT && seqlen_k < seqlen_q) return FAL_ERR_INVALID_ARGUMENT;
-  if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
       o_strides->head % 8 != 0 || o_strides->batch % 8 != 0)
     return FAL_ERR_INVALID_ARGUMENT;
@@ -276,18 +258,12 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // (the CTA-pair kernel knows the top-left mask only)
-  const bool pair = p.causal_shift == 0 && use_pair_forward(head_dim, seqlen_q);
-  CUtensorMap tk_half;
-  if (pair && (rc = make_tensor_map(&tk_half, k, head_dim, seqlen_k, heads_kv, batch, to_rs(k_strides), 64)))
-    return rc;
   const int cta_rows = forward_cta_rows(head_dim);
-  p.num_qblk = pair ? (seqlen_q + 511) / 512 : (seqlen_q + cta_rows - 1) / cta_rows;
-  const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q * (pair ? 2 : 1);
+  p.num_qblk = (seqlen_q + cta_rows - 1) / cta_rows;
+  const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
-  cudaError_t e = pair ? fal::launch_fwd_pair(is_causal != 0, tq, tk_half, tv, p, static_cast<int>(grid), st)
-                       : fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
@@ -307,7 +283,7 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   if (num_seqs <= 0 || total_q <= 0 || total_k < 0 || heads_q <= 0 || heads_kv <= 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
       o_strides->head % 8 != 0)
     return FAL_ERR_INVALID_ARGUMENT;
@@ -339,17 +315,13 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // The lengths stay on the device; the mean length decides between the kernels.
-  const bool pair = use_pair_forward(head_dim, total_q / num_seqs);
-  CUtensorMap tk_half;
-  if (pair && (rc = make_tensor_map(&tk_half, k, head_dim, total_k, heads_kv, 1, ks, 64))) return rc;
-  // Every sequence rounds up to whole 256-row (512-row) blocks: at most one extra block each.
-  p.num_qblk = (pair ? total_q / 512 : total_q / forward_cta_rows(head_dim)) + num_seqs;
-  const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q * (pair ? 2 : 1);
+  // The lengths stay on the device.  Every sequence rounds up to whole query blocks: at most one
+  // extra block each.
+  p.num_qblk = total_q / forward_cta_rows(head_dim) + num_seqs;
+  const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
-  cudaError_t e = pair ? fal::launch_fwd_pair(is_causal != 0, tq, tk_half, tv, p, static_cast<int>(grid), st)
-                       : fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
@@ -560,7 +532,7 @@ int decode_with_workspace(const void* q, void* k_cache, void* v_cache, const fal
   if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || capacity <= 0) return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o) ||
       !aligned16(k_new) || !aligned16(v_new))
@@ -642,7 +614,7 @@ int fal_decode_static(const void* q, void* k_cache, void* v_cache, const fal_str
   if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || capacity <= 0) return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  if (!inference_head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
+  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o) ||
       !aligned16(k_new) || !aligned16(v_new))

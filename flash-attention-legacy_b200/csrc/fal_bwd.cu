@@ -174,21 +174,6 @@ __device__ __forceinline__ float bwd_exp2(int j, float x) {
 #define FAL_BWD_ELECT_ARRIVE 1
 #endif
 
-// Tuning aid, compiled in only with -DFAL_BWD_TIMING: cycles each role spends in each wait.
-#ifdef FAL_BWD_TIMING
-__device__ unsigned long long g_bwd_wait_cycles[32];
-#define BWD_WAIT(slot, ...)                           \
-  do {                                                \
-    const long long _t0 = clock64();                  \
-    mbar_wait(__VA_ARGS__);                           \
-    tacc[slot] += clock64() - _t0;                    \
-  } while (0)
-#define BWD_TIMING_ONLY(x) x
-#else
-#define BWD_WAIT(slot, ...) mbar_wait(__VA_ARGS__)
-#define BWD_TIMING_ONLY(x)
-#endif
-
 // fp32 add-reduction of one swizzled shared-memory box into a 4-D tensor (TMA).
 __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1,
                                                   int c2, int c3) {
@@ -234,7 +219,6 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  BWD_TIMING_ONLY(long long tacc[24] = {}; const long long t_cta0 = clock64();)
 
   const int group = p.heads_q / p.heads_kv;
   const int kv0 = wk.kvblk * kKvTile;                       // local index of the tile's first key
@@ -339,7 +323,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int head = wk.kv_head * group + i / nq;
         const int qt = qt0 + i % nq;
         const int row = wk.q_row0 + qt * kQTile;
-        if (i >= NS) BWD_WAIT(0, bar(iQEmpty + st), ((i / NS) - 1) & 1, wctx, kBbQEmpty + st);
+        if (i >= NS) mbar_wait(bar(iQEmpty + st), ((i / NS) - 1) & 1, wctx, kBbQEmpty + st);
         if (lane == 0) {
           mbar_arrive_expect_tx(bar(iQFull + st), L::kTileBytes);
           for (int bx = 0; bx < L::kBoxes; ++bx)
@@ -348,7 +332,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         // dO has a single buffer: it is reloaded as soon as dV of the previous step has read it.
         if (lane == 0) {
-          if (i >= 1) BWD_WAIT(21, bar(iDoEmpty), (i - 1) & 1, wctx, kBbDoEmpty);
+          if (i >= 1) mbar_wait(bar(iDoEmpty), (i - 1) & 1, wctx, kBbDoEmpty);
           mbar_arrive_expect_tx(bar(iDoFull), L::kTileBytes);
           for (int bx = 0; bx < L::kBoxes; ++bx)
             tma_load_4d(sbase + L::kDoOff + bx * L::kBoxBytes, &tm_do, bar(iDoFull), bx * 64, row, head,
@@ -451,7 +435,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_commit(bar(iDpReady));
         }
         // dV += P^T(i) dO(i): P^T as packed fp16 in TMEM; query columns [0,64) at +0, [64,128) at +64
-        BWD_WAIT(2, bar(iPReady), i & 1, wctx, kBbPReady);
+        mbar_wait(bar(iPReady), i & 1, wctx, kBbPReady);
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kQTile / 16; ++ks) {
@@ -463,12 +447,12 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_commit(bar(iDoEmpty));  // dO(i) has no reader left once dV(i) is done
         // S^T(i+1) overwrites P^T(i): issued after dV(i), which reads it.
         if (!SPLIT && i + 1 < n_iter) {
-          BWD_WAIT(3, bar(iQFull + st1), ((i + 1) / NS) & 1, wctx, kBbQFull + st1);
+          mbar_wait(bar(iQFull + st1), ((i + 1) / NS) & 1, wctx, kBbQFull + st1);
           tc_fence_after_sync();
           issue_xyT(kColS, k_lo_k, sbase + L::kQOff + st1 * L::kTileBytes);
           tc_commit(bar(iSReady));
         }
-        BWD_WAIT(5, bar(iDsReady), i & 1, wctx, kBbDsReady);
+        mbar_wait(bar(iDsReady), i & 1, wctx, kBbDsReady);
         tc_fence_after_sync();
         // dK += dS^T(i) Q(i)
         auto issue_dk = [&]() {
@@ -501,8 +485,8 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_commit(bar(iDsFree));  // both readers of the dS^T buffer are done
         // dP^T(i+1) goes where dQ(i) is: the write-back warps must have read it out first.
         if (!SPLIT && i + 1 < n_iter) {
-          BWD_WAIT(1, bar(iDoFull), (i + 1) & 1, wctx, kBbDoFull);
-          BWD_WAIT(4, bar(iDqFree), i & 1, wctx, kBbDqFree);
+          mbar_wait(bar(iDoFull), (i + 1) & 1, wctx, kBbDoFull);
+          mbar_wait(bar(iDqFree), i & 1, wctx, kBbDqFree);
           tc_fence_after_sync();
           issue_xyT(kColDpq, v_lo_k, sbase + L::kDoOff);
           tc_commit(bar(iDpReady));
@@ -530,10 +514,9 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const float* stat = reinterpret_cast<const float*>(sgen + L::kStatOff) + st * 2 * kQTile + half * 64;
       const bool tile_mask = !kv_ok || (CAUSAL && (kv0 + kKvTile - 1 > qt * kQTile));
 
-      BWD_WAIT(6, bar(iStatFull + st), (i / NS) & 1, wctx, kBbStatFull + st);
-      BWD_WAIT(7, bar(iSReady), i & 1, wctx, kBbSReady);
+      mbar_wait(bar(iStatFull + st), (i / NS) & 1, wctx, kBbStatFull + st);
+      mbar_wait(bar(iSReady), i & 1, wctx, kBbSReady);
       tc_fence_after_sync();
-      BWD_TIMING_ONLY(const long long t_p0 = clock64();)
 
       // ---- P^T = exp2(S^T * c2 - lse2), kept as packed fp16 for the dS step ----
       uint32_t pk[32];
@@ -542,7 +525,6 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tmem_ld_32x32b_x32(tmem_base + lane_addr + kColS + half * 64, r[0]);
         tmem_ld_32x32b_x32(tmem_base + lane_addr + kColS + half * 64 + 32, r[1]);
         tmem_wait_ld();
-        BWD_TIMING_ONLY(tacc[16] += clock64() - t_p0; const long long t_p1 = clock64();)
         if (tile_mask) {  // hidden scores become -inf before the exponential (exp2(-inf) = 0)
 #pragma unroll
           for (int c = 0; c < 2; ++c)
@@ -574,10 +556,8 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
         // P^T overwrites this thread's own S^T columns: 32 packed columns at [64*half, 64*half+32)
-        BWD_TIMING_ONLY(tacc[17] += clock64() - t_p1; const long long t_p2 = clock64();)
         tmem_st_32x32b_x32(tmem_base + lane_addr + kColS + half * 64, pk);
         tmem_wait_st();
-        BWD_TIMING_ONLY(tacc[18] += clock64() - t_p2;)
       }
       tc_fence_before_sync();
 #if FAL_BWD_ELECT_ARRIVE
@@ -586,19 +566,16 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #else
       mbar_arrive(bar(iPReady));
 #endif
-      BWD_TIMING_ONLY(tacc[22] += clock64() - t_p0;)
 
       // ---- dS^T = P^T o (dP^T - delta) ------------------------------------------
-      BWD_WAIT(8, bar(iDpReady), i & 1, wctx, kBbDpReady);
+      mbar_wait(bar(iDpReady), i & 1, wctx, kBbDpReady);
       tc_fence_after_sync();
-      BWD_TIMING_ONLY(const long long t_s0 = clock64();)
       uint32_t dsp[32];
       {
         uint32_t r[2][32];
         tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + half * 64, r[0]);
         tmem_ld_32x32b_x32(tmem_base + lane_addr + kColDpq + half * 64 + 32, r[1]);
         tmem_wait_ld();
-        BWD_TIMING_ONLY(tacc[19] += clock64() - t_s0;)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
@@ -613,8 +590,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
-      BWD_TIMING_ONLY(tacc[20] += clock64() - t_s0;)
-      if (i > 0) BWD_WAIT(9, bar(iDsFree), (i - 1) & 1, wctx, kBbDqReady);
+      if (i > 0) mbar_wait(bar(iDsFree), (i - 1) & 1, wctx, kBbDqReady);
       // dS^T row -> shared memory, 128-byte XOR swizzle (16-byte chunk index ^ row % 8)
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -629,7 +605,6 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #else
       mbar_arrive(bar(iDsReady));
 #endif
-      BWD_TIMING_ONLY(tacc[23] += clock64() - t_s0;)
     }
 
     // ---- epilogue: dV (warps 0-3) and dK (warps 4-7) -------------------------
@@ -681,9 +656,8 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int i = 0; i < n_iter; ++i) {
       const int head = wk.kv_head * group + i / nq;
       const int qt = qt0 + i % nq;
-      BWD_WAIT(10, bar(iDqReady), i & 1, wctx, kBbDqReady);
+      mbar_wait(bar(iDqReady), i & 1, wctx, kBbDqReady);
       tc_fence_after_sync();
-      BWD_TIMING_ONLY(const long long t_red0 = clock64();)
       const int grow = wk.q_row0 + qt * kQTile;  // accumulator row of the tile's first query
 #pragma unroll
       for (int hf = 0; hf < D / 64; ++hf) {
@@ -706,41 +680,17 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 make_uint4(r[c][4 * v + 0], r[c][4 * v + 1], r[c][4 * v + 2], r[c][4 * v + 3]);
         fence_proxy_async_smem();
         named_barrier_sync(1, 128);
-#ifdef FAL_BWD_DEBUG_NO_REDUCE  // tuning aid: dQ is staged but never added (dQ comes out zero)
-        if (false) {
-#else
         if (issuer) {
-#endif
-#ifdef FAL_BWD_DEBUG_LOCAL_REDUCE  // tuning aid: every CTA adds into one small region (wrong dQ)
-          const int dbg_head = blockIdx.x % p.heads_q, dbg_batch = (blockIdx.x / p.heads_q) % p.batch;
-          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff, hf * 64, 0, dbg_head, dbg_batch);
-          tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff + L::kBoxBytes, hf * 64 + 32, 0, dbg_head, dbg_batch);
-#else
           tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff, col_own + hf * 64, grow, head, wk.batch);
           tma_reduce_add_4d(&tm_dq, sbase + L::kStageOff + L::kBoxBytes, col_own + hf * 64 + 32, grow, head,
                             wk.batch);
-#endif
           bulk_commit_group();
         }
       }
-      BWD_TIMING_ONLY(tacc[11] += clock64() - t_red0;)
     }
     if (issuer) bulk_wait_group0();
   }
 
-#ifdef FAL_BWD_TIMING
-  if (lane == 0 && (warp == 0 || warp == 8 || warp == 9 || warp == 10)) {
-    for (int i = 0; i < 12; ++i)
-      if (tacc[i]) atomicAdd(&g_bwd_wait_cycles[i], static_cast<unsigned long long>(tacc[i]));
-    for (int i = 16; i < 24; ++i)
-      if (tacc[i]) atomicAdd(&g_bwd_wait_cycles[i], static_cast<unsigned long long>(tacc[i]));
-    if (warp == 0) {
-      atomicAdd(&g_bwd_wait_cycles[12], static_cast<unsigned long long>(clock64() - t_cta0));
-      atomicAdd(&g_bwd_wait_cycles[13], static_cast<unsigned long long>(n_iter));
-      atomicAdd(&g_bwd_wait_cycles[14], 1ull);
-    }
-  }
-#endif
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 9) {
@@ -748,21 +698,6 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tmem_dealloc(tmem_base, 512);
   }
 }
-
-#ifdef FAL_BWD_TIMING
-}  // namespace
-}  // namespace fal
-extern "C" __attribute__((visibility("default"))) int fal_debug_bwd_waits(unsigned long long* out32, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out32, fal::g_bwd_wait_cycles, sizeof(unsigned long long) * 32);
-  if (e == cudaSuccess && reset) {
-    unsigned long long z[32] = {};
-    e = cudaMemcpyToSymbol(fal::g_bwd_wait_cycles, z, sizeof(z));
-  }
-  return static_cast<int>(e);
-}
-namespace fal {
-namespace {
-#endif
 
 // ---------------------------------------------------------------------------
 // Pre-pass: delta[row] = sum_d dO*O  (precompute_D_kernel, bwd.cu:76-107 of the reference) and

@@ -88,26 +88,6 @@ static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 168 * 384,
               "setmaxnreg split exceeds the registers the CTA was launched with");
 static_assert(kRegsSoftmax % 8 == 0 && kRegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
 
-// Tuning aid, compiled in only with -DFAL_FWD_TIMING: cycles per role and phase, summed over CTAs.
-#ifdef FAL_FWD_TIMING
-__device__ unsigned long long g_fwd_cycles[32];
-#define FWD_T(slot, stmt)                  \
-  do {                                     \
-    const long long _t0 = clock64();       \
-    stmt;                                  \
-    tacc[slot] += clock64() - _t0;         \
-  } while (0)
-#define FWD_MARK(slot)                     \
-  do {                                     \
-    const long long _t1 = clock64();       \
-    tacc[slot] += _t1 - tmark;             \
-    tmark = _t1;                           \
-  } while (0)
-#else
-#define FWD_T(slot, stmt) stmt
-#define FWD_MARK(slot)
-#endif
-
 // Barrier ids (only used to label a wait that gave up).
 enum FwdBarrier : int {
   kBarQFull = 0,
@@ -339,13 +319,8 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
-#ifdef FAL_FWD_DEBUG_QK_FROM_TMEM  // tuning aid: A operand from TMEM (garbage) to take Q's shared-memory reads away
-          umma_ts(tmem_base + w * kTileN, tmem_base + 256 + w * D + ks * 8,
-                  smem_desc_join(k_lo + off, kHi), idesc_qk, ks > 0 ? 1u : 0u);
-#else
           umma_ss(tmem_base + w * kTileN, smem_desc_join(q_lo[w] + off, kHi),
                   smem_desc_join(k_lo + off, kHi), idesc_qk, ks > 0 ? 1u : 0u);
-#endif
         }
       };
       // O[w] += P[w] V_j : A = P from TMEM (8 columns of packed fp16 per 16 keys), B = V
@@ -362,10 +337,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       };
 
-#ifdef FAL_FWD_TIMING
-      long long tacc[8] = {};
-      const long long t_begin = clock64();
-#endif
       if (n_max > 0) {
         mbar_wait(bar(iKFull + 0), 0, wctx, kBarKFull);
         for (int w = 0; w < 2; ++w) {
@@ -384,32 +355,25 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (j >= ntile[w]) continue;
           // P arrives in two halves of 64 keys, so that PV starts while the softmax warps are
           // still exponentiating the second half.
-          FWD_T(0, mbar_wait(bar(iPHalf + w), j & 1, wctx, kBarPReady + w));
-          FWD_T(1, mbar_wait(bar(iVFull + s), use & 1, wctx, kBarVFull + s));
+          mbar_wait(bar(iPHalf + w), j & 1, wctx, kBarPReady + w);
+          mbar_wait(bar(iVFull + s), use & 1, wctx, kBarVFull + s);
           tc_fence_after_sync();
-          FWD_T(5, issue_pv(w, j, 0));
-          FWD_T(2, mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w));
+          issue_pv(w, j, 0);
+          mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w);
           tc_fence_after_sync();
-          FWD_T(6, issue_pv(w, j, 1));
+          issue_pv(w, j, 1);
           tc_commit(bar(iODone + w));
           if (w == 1 || j >= ntile[1]) tc_commit(bar(iVEmpty + s));
           if (j + 1 < ntile[w]) {
             const int s1 = (j + 1) % NS;
-            FWD_T(3, mbar_wait(bar(iKFull + s1), ((j + 1) / NS) & 1, wctx, kBarKFull + s1));
+            mbar_wait(bar(iKFull + s1), ((j + 1) / NS) & 1, wctx, kBarKFull + s1);
             tc_fence_after_sync();
-            FWD_T(7, issue_qk(w, j + 1));
+            issue_qk(w, j + 1);
             tc_commit(bar(iSReady + w));
             if (w == 1 || j + 1 >= ntile[1]) tc_commit(bar(iKEmpty + s1));
           }
         }
       }
-#ifdef FAL_FWD_TIMING
-      for (int i = 0; i < 4; ++i) atomicAdd(&g_fwd_cycles[i], static_cast<unsigned long long>(tacc[i]));
-      for (int i = 5; i < 8; ++i) atomicAdd(&g_fwd_cycles[18 + i], static_cast<unsigned long long>(tacc[i]));
-      atomicAdd(&g_fwd_cycles[4], static_cast<unsigned long long>(clock64() - t_begin));
-      atomicAdd(&g_fwd_cycles[5], static_cast<unsigned long long>(ntile[0] + ntile[1]));
-      atomicAdd(&g_fwd_cycles[6], 1ull);
-#endif
     }
     __syncwarp();
   }
@@ -430,22 +394,9 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     float m_ref = kNegInf;
     float l = 0.f;
 
-#ifdef FAL_FWD_TIMING
-    long long tacc[8] = {};
-    long long tmark = clock64();
-    const long long t_begin = tmark;
-#endif
     for (int j = 0; j < nt; ++j) {
-      FWD_MARK(7);  // loop overhead
       mbar_wait(bar(iSReady + wg), j & 1, wctx, kBarSReady + wg);
       tc_fence_after_sync();
-      FWD_MARK(0);  // wait for S
-#ifdef FAL_FWD_DEBUG_NO_SOFTMAX  // tuning aid: the MMA side alone (results are meaningless)
-      tc_fence_before_sync();
-      mbar_arrive(bar(iPHalf + wg));
-      mbar_arrive(bar(iPReady + wg));
-      continue;
-#endif
       const int kv0 = j * kTileN;
       int limit = wk.seqlen_k - kv0;  // columns c < limit are visible
       const int cshift = SHIFTED ? p.causal_shift : 0;
@@ -458,7 +409,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tS + c * 32, sr[c]);
       tmem_wait_ld();
-      FWD_MARK(1);  // S into registers
       if (tile_mask) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -487,7 +437,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mx = fmax3(mx, part[6], part[7]);
       }
       const float m_new = fmaxf(m_ref, mx);
-      FWD_MARK(2);  // mask + row max
 
       if (j == 0) {
         m_ref = m_new;
@@ -512,7 +461,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       const float moff = (m_ref == kNegInf) ? 0.f : m_ref * c2;
-      FWD_MARK(3);  // rescale decision (and rescale)
 
       // P = exp2(s * c2 - m * c2) from the registers, four independent row-sum chains,
       // fp16 P back into TMEM over the first half of S.
@@ -544,7 +492,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tmem_wait_st();
           tc_fence_before_sync();
           mbar_arrive(bar(iPHalf + wg));
-          FWD_MARK(4);  // first half of P
         }
       }
       float sum0, sum1, sum2, sum3;
@@ -582,17 +529,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar(iPReady + wg));
-      FWD_MARK(5);  // second half of P
     }
-#ifdef FAL_FWD_TIMING
-    if (lane == 0 && quarter == 0) {
-      for (int i = 0; i < 8; ++i)
-        if (i != 6) atomicAdd(&g_fwd_cycles[8 + i], static_cast<unsigned long long>(tacc[i]));
-      atomicAdd(&g_fwd_cycles[8 + 6], static_cast<unsigned long long>(clock64() - t_begin));
-      atomicAdd(&g_fwd_cycles[16], static_cast<unsigned long long>(nt));
-    }
-    const long long t_epi = clock64();
-#endif
 
     // ---- epilogue: O / l -> fp16, LSE -----------------------------------------
     if (nt > 0) {
@@ -630,10 +567,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                                       : kNegInf;
       p.lse[wk.lse_base + static_cast<int64_t>(q_local) * p.lse_strides.row] = lse;
     }
-#ifdef FAL_FWD_TIMING
-    if (lane == 0 && quarter == 0)
-      atomicAdd(&g_fwd_cycles[17], static_cast<unsigned long long>(clock64() - t_epi));
-#endif
   }
 
   // ---- teardown -------------------------------------------------------------
@@ -644,21 +577,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tmem_dealloc(tmem_base, 512);
   }
 }
-
-#ifdef FAL_FWD_TIMING
-}  // namespace
-}  // namespace fal
-extern "C" __attribute__((visibility("default"))) int fal_debug_fwd_cycles(unsigned long long* out32, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out32, fal::g_fwd_cycles, sizeof(unsigned long long) * 32);
-  if (e == cudaSuccess && reset) {
-    unsigned long long z[32] = {};
-    e = cudaMemcpyToSymbol(fal::g_fwd_cycles, z, sizeof(z));
-  }
-  return static_cast<int>(e);
-}
-namespace fal {
-namespace {
-#endif
 
 template <int D, bool CAUSAL, bool SHIFTED = false>
 cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,

@@ -39,11 +39,6 @@ class DeviceOnce {
 cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream);
 
-// Forward on CTA pairs, head_dim 128 only: grid = 2 x number of (512-row block, batch*head) units
-// (p.num_qblk counts 512-row blocks); tk_half has 64-row boxes.
-cudaError_t launch_fwd_pair(bool causal, const CUtensorMap& tq, const CUtensorMap& tk_half,
-                            const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream);
-
 // Backward pre-pass: delta = rowsum(dO * O) and zero of the fp32 dQ accumulator.
 struct BwdPrepParams {
   const void* o;

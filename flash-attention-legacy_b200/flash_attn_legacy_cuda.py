@@ -98,24 +98,6 @@ def profile_read(kind):
 _status = {}
 
 
-def debug_cycles(which, reset=True):
-    """The 32 cycle counters of a kernel built with its timing switch, else None.
-
-    `which`: "fwd" (-DFAL_FWD_TIMING, fal_fwd.cu), "fwd_pair" (same switch, fal_fwd_pair.cu) or
-    "bwd" (-DFAL_BWD_TIMING).  The product library is built without them; see build.py --define.
-    """
-    name = {"fwd": "fal_debug_fwd_cycles", "fwd_pair": "fal_debug_fwd_pair_cycles",
-            "bwd": "fal_debug_bwd_waits"}[which]
-    try:
-        fn = getattr(_lib, name)
-    except AttributeError:
-        return None
-    buf = (ctypes.c_ulonglong * 32)()
-    if fn(buf, int(bool(reset))) != 0:
-        raise RuntimeError(f"{name} failed")
-    return list(buf)
-
-
 def _status_word(device):
     idx = device.index if device.index is not None else torch.cuda.current_device()
     t = _status.get(idx)
