@@ -157,6 +157,25 @@ BwdWorkspace bwd_workspace_layout(int batch, int heads_q, int rows, int head_dim
 
 constexpr int kDecodeSplitLen = 1024;
 
+// Decode scratch layout: [partial O fp32 rows*d][partial (max, sum) fp32 rows*2][arrival counters int32
+// batch*heads_q], rows = batch*heads_q*splits.  The counters must be zero when a call starts; every
+// call leaves them zero.
+struct DecodeWorkspace {
+  int64_t splits;
+  size_t partial_bytes;
+  size_t counter_bytes;
+  size_t total() const { return partial_bytes + counter_bytes; }
+};
+
+DecodeWorkspace decode_workspace_layout(int batch, int heads_q, int capacity, int head_dim) {
+  DecodeWorkspace w;
+  w.splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
+  const int64_t rows = static_cast<int64_t>(batch) * heads_q * w.splits;
+  w.partial_bytes = static_cast<size_t>(round_up(rows * (head_dim + 2) * static_cast<int64_t>(sizeof(float)), 16));
+  w.counter_bytes = static_cast<size_t>(round_up(static_cast<int64_t>(batch) * heads_q * 4, 16));
+  return w;
+}
+
 // ---------------------------------------------------------------------------
 // Optional event timing around the main kernels (off by default).
 // ---------------------------------------------------------------------------
@@ -203,7 +222,7 @@ const char* fal_strerror(int code) {
     case FAL_ERR_UNSUPPORTED_DEVICE: return "device is not compute capability 10.x (B200)";
     case FAL_ERR_STATIC_SCRATCH_EXCEEDED:
       return "problem too large for fal_decode_static's fixed 8 MiB scratch "
-             "(batch*heads_q*ceil(capacity/1024)*(head_dim+2)*4 bytes must fit); use fal_decode";
+             "(fal_decode_workspace_bytes(batch, heads_q, capacity, head_dim) must fit); use fal_decode";
     default: return "unknown error";
   }
 }
@@ -283,6 +302,8 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   if (num_seqs <= 0 || total_q <= 0 || total_k < 0 || heads_q <= 0 || heads_kv <= 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
+  // the packed kernels know the reference's top-left-aligned mask only
+  if (is_causal != FAL_CAUSAL_NONE && is_causal != FAL_CAUSAL_TOP_LEFT) return FAL_ERR_INVALID_ARGUMENT;
   if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
       o_strides->head % 8 != 0)
@@ -357,6 +378,8 @@ int run_bwd(const BwdCall& c) {
   if (c.batch <= 0 || c.heads_q <= 0 || c.heads_kv <= 0 || c.rows_q <= 0 || c.rows_k <= 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (c.heads_q % c.heads_kv != 0 || !(c.scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
+  // no backward exists for the bottom-right-aligned mask: refuse it instead of masking top-left
+  if (c.causal != FAL_CAUSAL_NONE && c.causal != FAL_CAUSAL_TOP_LEFT) return FAL_ERR_INVALID_ARGUMENT;
   if (!head_dim_ok(c.head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   auto out_ok = [](const void* ptr, const fal::RowStrides& s) {
     return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && s.row % 8 == 0 && s.head % 8 == 0 &&
@@ -515,19 +538,16 @@ int fal_bwd_varlen(const void* d_out, const void* q, const void* k, const void* 
 
 size_t fal_decode_workspace_bytes(int batch, int heads_q, int capacity, int head_dim) {
   if (batch <= 0 || heads_q <= 0 || capacity <= 0 || head_dim <= 0) return 0;
-  const int64_t splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
-  const int64_t rows = static_cast<int64_t>(batch) * heads_q * splits;
-  return static_cast<size_t>(rows) * (head_dim + 2) * sizeof(float);
+  return decode_workspace_layout(batch, heads_q, capacity, head_dim).total();
 }
 
 namespace {
-int decode_with_workspace(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,
-                          const fal_strides* v_strides, const int32_t* cache_starts,
-                          const int32_t* cache_seqlens, const void* k_new, const void* v_new, void* o,
-                          float* lse, int batch, int heads_q, int heads_kv, int capacity, int head_dim,
-                          float softmax_scale, void* workspace, size_t workspace_bytes, int* status,
-                          void* stream) {
-  if (!q || !k_cache || !v_cache || !k_strides || !v_strides || !cache_seqlens || !o || !workspace)
+// Argument checks shared by every decode entry point (no CUDA call is made here).
+int decode_check_args(const void* q, const void* k_cache, const void* v_cache, const fal_strides* k_strides,
+                      const fal_strides* v_strides, const int32_t* cache_seqlens, const void* k_new,
+                      const void* v_new, const void* o, int batch, int heads_q, int heads_kv, int capacity,
+                      int head_dim, float softmax_scale) {
+  if (!q || !k_cache || !v_cache || !k_strides || !v_strides || !cache_seqlens || !o)
     return FAL_ERR_INVALID_ARGUMENT;
   if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || capacity <= 0) return FAL_ERR_INVALID_ARGUMENT;
@@ -540,9 +560,23 @@ int decode_with_workspace(const void* q, void* k_cache, void* v_cache, const fal
   const fal_strides* both[2] = {k_strides, v_strides};
   for (const fal_strides* s : both)
     if (s->row % 8 != 0 || s->head % 8 != 0 || s->batch % 8 != 0) return FAL_ERR_INVALID_ARGUMENT;
-  if (workspace_bytes < fal_decode_workspace_bytes(batch, heads_q, capacity, head_dim))
-    return FAL_ERR_WORKSPACE_TOO_SMALL;
-  int rc = check_device();
+  return FAL_OK;
+}
+
+int decode_with_workspace(const void* q, void* k_cache, void* v_cache, const fal_strides* k_strides,
+                          const fal_strides* v_strides, const int32_t* cache_starts,
+                          const int32_t* cache_seqlens, const void* k_new, const void* v_new, void* o,
+                          float* lse, int batch, int heads_q, int heads_kv, int capacity, int head_dim,
+                          float softmax_scale, void* workspace, size_t workspace_bytes, int* status,
+                          void* stream) {
+  int rc = decode_check_args(q, k_cache, v_cache, k_strides, v_strides, cache_seqlens, k_new, v_new, o, batch,
+                             heads_q, heads_kv, capacity, head_dim, softmax_scale);
+  if (rc != FAL_OK) return rc;
+  if (!workspace) return FAL_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return FAL_ERR_INVALID_ARGUMENT;
+  const DecodeWorkspace w = decode_workspace_layout(batch, heads_q, capacity, head_dim);
+  if (workspace_bytes < w.total()) return FAL_ERR_WORKSPACE_TOO_SMALL;
+  rc = check_device();
   if (rc != FAL_OK) return rc;
 
   fal::DecodeParams p{};
@@ -563,22 +597,16 @@ int decode_with_workspace(const void* q, void* k_cache, void* v_cache, const fal
   p.capacity = capacity;
   p.head_dim = head_dim;
   p.split_len = kDecodeSplitLen;
-  p.splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
+  p.splits = static_cast<int>(w.splits);
   p.scale = softmax_scale;
   p.status = status;
   p.part_o = static_cast<float*>(workspace);
   p.part_ml = p.part_o + static_cast<int64_t>(batch) * heads_q * p.splits * head_dim;
+  p.arrivals = reinterpret_cast<int*>(static_cast<char*>(workspace) + w.partial_bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e;
-  if (k_new != nullptr) {
-    e = fal::launch_decode_append(p, st);
-    if (e != cudaSuccess) return cuda_fail(e);
-  }
   const int rec = g_timer.begin(FAL_KERNEL_DECODE_SPLITK, st);
-  e = fal::launch_decode_splitk(p, st);
+  cudaError_t e = fal::launch_decode(p, st);
   g_timer.end(FAL_KERNEL_DECODE_SPLITK, rec, st);
-  if (e != cudaSuccess) return cuda_fail(e);
-  e = fal::launch_decode_combine(p, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
 }  // namespace
@@ -609,59 +637,21 @@ int fal_decode_static(const void* q, void* k_cache, void* v_cache, const fal_str
                       const fal_strides* v_strides, const int32_t* cache_seqlens, const void* k_new,
                       const void* v_new, void* o, float* lse, int batch, int heads_q, int heads_kv,
                       int capacity, int head_dim, float softmax_scale, int* status, void* stream) {
-  if (!q || !k_cache || !v_cache || !k_strides || !v_strides || !cache_seqlens || !o)
-    return FAL_ERR_INVALID_ARGUMENT;
-  if ((k_new == nullptr) != (v_new == nullptr)) return FAL_ERR_INVALID_ARGUMENT;
-  if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || capacity <= 0) return FAL_ERR_INVALID_ARGUMENT;
-  if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
-  auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
-  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o) ||
-      !aligned16(k_new) || !aligned16(v_new))
-    return FAL_ERR_INVALID_ARGUMENT;
-  const fal_strides* both[2] = {k_strides, v_strides};
-  for (const fal_strides* s : both)
-    if (s->row % 8 != 0 || s->head % 8 != 0 || s->batch % 8 != 0) return FAL_ERR_INVALID_ARGUMENT;
-  // The partials of this problem must fit the fixed array; nothing is launched otherwise.
+  int rc = decode_check_args(q, k_cache, v_cache, k_strides, v_strides, cache_seqlens, k_new, v_new, o, batch,
+                             heads_q, heads_kv, capacity, head_dim, softmax_scale);
+  if (rc != FAL_OK) return rc;
+  // The scratch of this problem (partials + arrival counters) must fit the fixed array; nothing is
+  // launched otherwise.
   if (fal_decode_workspace_bytes(batch, heads_q, capacity, head_dim) > fal::kDecodeStaticScratchBytes)
     return FAL_ERR_STATIC_SCRATCH_EXCEEDED;
-  int rc = check_device();
+  rc = check_device();
   if (rc != FAL_OK) return rc;
   float* scratch = nullptr;
   cudaError_t e = fal::decode_static_scratch(&scratch);  // first call per device: address look-up
   if (e != cudaSuccess) return cuda_fail(e);
-
-  fal::DecodeParams p{};
-  p.q = q;
-  p.k_cache = k_cache;
-  p.v_cache = v_cache;
-  p.k_strides = to_rs(k_strides);
-  p.v_strides = to_rs(v_strides);
-  p.k_new = k_new;
-  p.v_new = v_new;
-  p.cache_seqlens = cache_seqlens;
-  p.o = o;
-  p.lse = lse;
-  p.batch = batch;
-  p.heads_q = heads_q;
-  p.heads_kv = heads_kv;
-  p.capacity = capacity;
-  p.head_dim = head_dim;
-  p.split_len = kDecodeSplitLen;
-  p.splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
-  p.scale = softmax_scale;
-  p.status = status;
-  p.part_o = scratch;
-  p.part_ml = scratch + static_cast<int64_t>(batch) * heads_q * p.splits * head_dim;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (k_new != nullptr) {
-    e = fal::launch_decode_append(p, st);
-    if (e != cudaSuccess) return cuda_fail(e);
-  }
-  e = fal::launch_decode_splitk(p, st);
-  if (e != cudaSuccess) return cuda_fail(e);
-  e = fal::launch_decode_combine(p, st);
-  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+  return decode_with_workspace(q, k_cache, v_cache, k_strides, v_strides, nullptr, cache_seqlens, k_new, v_new,
+                               o, lse, batch, heads_q, heads_kv, capacity, head_dim, softmax_scale, scratch,
+                               fal::kDecodeStaticScratchBytes, status, stream);
 }
 
 int fal_profile_enable(int on) {

@@ -1,5 +1,5 @@
-// Single-token decode against an fp16 KV cache: a split-K streaming kernel
-// followed by a log-sum-exp combine.
+// Single-token decode against an fp16 KV cache: ONE launch that appends the new
+// token's K/V row, streams the cache split-K and merges the splits (log-sum-exp).
 //
 // Stands in for the eager matmul -> softmax -> matmul fallback that the
 // reference's attention hook uses whenever q_len != kv_len
@@ -18,8 +18,12 @@
 //   - scores and PV use mma.sync m16n8k16 with the query heads as the M rows:
 //     tensor throughput is irrelevant here, the MMA only keeps the issue slots
 //     free for the loads;
-//   - each split writes an unnormalised fp32 partial (O, max, sum); the combine
-//     kernel merges the splits that the sequence length actually reaches.
+//   - the CTA whose split holds the position the new token goes to writes that
+//     row into the cache before it starts streaming (no separate append launch);
+//   - each split writes an unnormalised fp32 partial (O, max, sum) and then counts
+//     itself in on a per-(entry, head group) arrival counter; the CTA that arrives
+//     last merges the splits the sequence length actually reaches and puts the
+//     counter back to zero (no separate combine launch, no CTA waits for another).
 // An optional first position per batch entry (cache_starts) skips a padded prefix
 // of the cache: the entry's row pointers start there and its length shrinks.
 #include "fal_common.h"
@@ -72,29 +76,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 }
 
 // ---------------------------------------------------------------------------
-// Cache append: k_new/v_new [B,Hkv,d] -> position cache_seqlens[b].
-// ---------------------------------------------------------------------------
-__global__ void fal_decode_append_kernel(const DecodeParams p) {
-  const int bh = blockIdx.x;
-  const int b = bh / p.heads_kv;
-  const int h = bh % p.heads_kv;
-  const int pos = __ldg(p.cache_seqlens + b);
-  if (pos < 0 || pos >= p.capacity) return;
-  const int chunks = p.head_dim / 8;
-  for (int c = threadIdx.x; c < 2 * chunks; c += blockDim.x) {
-    const bool is_v = c >= chunks;
-    const int cc = is_v ? c - chunks : c;
-    const __half* src = static_cast<const __half*>(is_v ? p.v_new : p.k_new) +
-                        static_cast<int64_t>(bh) * p.head_dim + cc * 8;
-    const RowStrides& st = is_v ? p.v_strides : p.k_strides;
-    __half* dst = static_cast<__half*>(is_v ? p.v_cache : p.k_cache) + b * st.batch + h * st.head +
-                  static_cast<int64_t>(pos) * st.row + cc * 8;
-    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-  }
-}
-
-// ---------------------------------------------------------------------------
-// Split-K pass.
+// Append + split-K pass + merge by the last CTA to arrive.
 // ---------------------------------------------------------------------------
 template <int D>
 struct DecSmem {
@@ -126,14 +108,54 @@ fal_decode_splitk_kernel(const DecodeParams p) {
   const int split = blockIdx.y;
   const int b = blockIdx.z;
 
-  int len = __ldg(p.cache_seqlens + b);
-  if (p.k_new != nullptr) len += 1;
-  len = min(max(len, 0), p.capacity);
+  const int len_old = __ldg(p.cache_seqlens + b);
+  const bool append = p.k_new != nullptr;
+  // The new token goes to position len_old.  A cache that is already full (or a negative length)
+  // cannot take it: the token is then neither stored nor attended to, and the status word says so.
+  const bool can_append = append && len_old >= 0 && len_old < p.capacity;
+  if (append && !can_append && split == 0 && threadIdx.x == 0 && p.status)
+    atomicCAS(p.status, 0, kDevAppendOverflow);
+  int len = min(max(len_old + (can_append ? 1 : 0), 0), p.capacity);
   // With a first attended position the entry's keys are [start, len): positions below are counted
   // from `start` (the row pointers are moved there).
   const int start = p.cache_starts ? min(max(__ldg(p.cache_starts + b), 0), len) : 0;
   len -= start;
   const int pos0 = split * p.split_len;
+
+  const int rows_valid = min(16, group - head_chunk * 16);
+  const int hq0 = kv_head * group + head_chunk * 16;  // first query head of this CTA
+
+  // ---- append: the split that holds the new position stores the row, then streams it like any
+  // other (split 0 stores it when the position lies before `start` and nobody attends to it) ----
+  if (can_append) {
+    const int new_local = len_old - start;
+    const int store_split = new_local >= 0 ? new_local / p.split_len : 0;
+    if (split == store_split) {
+      for (int c = threadIdx.x; c < 2 * kChunks; c += kDecThreads) {
+        const bool is_v = c >= kChunks;
+        const int cc = is_v ? c - kChunks : c;
+        const __half* src = static_cast<const __half*>(is_v ? p.v_new : p.k_new) +
+                            (static_cast<int64_t>(b) * p.heads_kv + kv_head) * D + cc * 8;
+        const RowStrides& st = is_v ? p.v_strides : p.k_strides;
+        __half* dst = static_cast<__half*>(is_v ? p.v_cache : p.k_cache) + b * st.batch + kv_head * st.head +
+                      static_cast<int64_t>(len_old) * st.row + cc * 8;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+      }
+      __threadfence();   // the row is read back through L2 by this CTA's asynchronous copies
+      __syncthreads();
+    }
+  }
+  if (len <= 0) {
+    // nothing to attend to: zeros and LSE = -inf, written by the entry's first split
+    if (split == 0) {
+      for (int idx = threadIdx.x; idx < rows_valid * D; idx += kDecThreads)
+        static_cast<__half*>(p.o)[(static_cast<int64_t>(b) * p.heads_q + hq0 + idx / D) * D + idx % D] =
+            __float2half_rn(0.f);
+      if (p.lse != nullptr && threadIdx.x < rows_valid)
+        p.lse[static_cast<int64_t>(b) * p.heads_q + hq0 + threadIdx.x] = kNegInfD;
+    }
+    return;
+  }
   if (pos0 >= len) return;  // this split lies beyond the sequence
   const int pos_end = min(pos0 + p.split_len, len);
   const int num_slices = (pos_end - pos0 + kSliceKeys - 1) / kSliceKeys;
@@ -142,9 +164,6 @@ fal_decode_splitk_kernel(const DecodeParams p) {
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2;
   const int t = lane & 3;
-
-  const int rows_valid = min(16, group - head_chunk * 16);
-  const int hq0 = kv_head * group + head_chunk * 16;  // first query head of this CTA
 
   // ---- query fragments (A operand: row = head, col = head_dim) ---------------
   uint32_t qa[kKSteps][4];
@@ -327,36 +346,42 @@ fal_decode_splitk_kernel(const DecodeParams p) {
       p.part_ml[prow * 2 + 1] = lsum;
     }
   }
-}
 
-// ---------------------------------------------------------------------------
-// Combine: merge the splits a sequence actually reaches.
-// ---------------------------------------------------------------------------
-__global__ void fal_decode_combine_kernel(const DecodeParams p) {
-  const int bh = blockIdx.x;
-  const int b = bh / p.heads_q;
-  const int D = p.head_dim;
-  int len = __ldg(p.cache_seqlens + b);
-  if (p.k_new != nullptr) len += 1;
-  len = min(max(len, 0), p.capacity);
-  if (p.cache_starts) len -= min(max(__ldg(p.cache_starts + b), 0), len);
-  const int n = (len + p.split_len - 1) / p.split_len;
-  const float* ml = p.part_ml + static_cast<int64_t>(bh) * p.splits * 2;
-  const float* po = p.part_o + static_cast<int64_t>(bh) * p.splits * D;
-
-  float mmax = kNegInfD;
-  for (int i = 0; i < n; ++i) mmax = fmaxf(mmax, ml[2 * i]);
-  const float muse = (mmax == kNegInfD) ? 0.f : mmax;
-  float lsum = 0.f;
-  for (int i = 0; i < n; ++i) lsum += fast_exp2(ml[2 * i] - muse) * ml[2 * i + 1];
-  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
-    float o = 0.f;
-    for (int i = 0; i < n; ++i) o += fast_exp2(ml[2 * i] - muse) * po[static_cast<int64_t>(i) * D + c];
-    static_cast<__half*>(p.o)[static_cast<int64_t>(bh) * D + c] = __float2half_rn(o * inv);
+  // ---- arrival: the last of this (entry, head group)'s active splits merges them ---------------
+  // Every active split counts itself in after its partial is visible device-wide; nobody waits.
+  // The counter goes back to zero for the next call (it must be zero when a call starts).
+  __shared__ int s_is_last;
+  const int n_active = (len + p.split_len - 1) / p.split_len;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* ctr = p.arrivals + static_cast<int64_t>(b) * p.heads_q + blockIdx.x;
+    const int seen = atomicAdd(ctr, 1);
+    s_is_last = (seen == n_active - 1) ? 1 : 0;
+    if (s_is_last) atomicExch(ctr, 0);
   }
-  if (p.lse != nullptr && threadIdx.x == 0) {
-    p.lse[bh] = (lsum > 0.f) ? (mmax + log2f(lsum)) * 0.6931471805599453f : kNegInfD;
+  __syncthreads();
+  if (!s_is_last) return;
+  __threadfence();
+
+  for (int idx = threadIdx.x; idx < rows_valid * D; idx += kDecThreads) {
+    const int r = idx / D;
+    const int c = idx % D;
+    const int64_t bh = static_cast<int64_t>(b) * p.heads_q + hq0 + r;
+    const float* ml = p.part_ml + bh * p.splits * 2;
+    const float* po = p.part_o + bh * p.splits * D;
+    float mmax = kNegInfD;
+    for (int i = 0; i < n_active; ++i) mmax = fmaxf(mmax, __ldcg(ml + 2 * i));
+    const float muse = (mmax == kNegInfD) ? 0.f : mmax;
+    float lsum = 0.f;
+    for (int i = 0; i < n_active; ++i) lsum += fast_exp2(__ldcg(ml + 2 * i) - muse) * __ldcg(ml + 2 * i + 1);
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    float o = 0.f;
+    for (int i = 0; i < n_active; ++i)
+      o += fast_exp2(__ldcg(ml + 2 * i) - muse) * __ldcg(po + static_cast<int64_t>(i) * D + c);
+    static_cast<__half*>(p.o)[bh * D + c] = __float2half_rn(o * inv);
+    if (c == 0 && p.lse != nullptr)
+      p.lse[bh] = (lsum > 0.f) ? (mmax + log2f(lsum)) * 0.6931471805599453f : kNegInfD;
   }
 }
 
@@ -379,9 +404,10 @@ cudaError_t launch_splitk_t(const DecodeParams& p, cudaStream_t stream) {
 }  // namespace
 
 // ---------------------------------------------------------------------------
-// Fixed scratch for fal_decode_static: split-K partials for callers that cannot
-// allocate device memory.  It lives in the library image, so every GPU that
-// loads the library carries these bytes until the process exits.
+// Fixed scratch for fal_decode_static: split-K partials and arrival counters for
+// callers that cannot allocate device memory.  It lives in the library image, so
+// every GPU that loads the library carries these bytes until the process exits;
+// it is zero-initialised at load, which is what the arrival counters need.
 // ---------------------------------------------------------------------------
 namespace {
 static __device__ __align__(256) float g_decode_static_scratch[kDecodeStaticScratchBytes / sizeof(float)];
@@ -407,21 +433,11 @@ cudaError_t decode_static_scratch(float** ptr) {
   return cudaSuccess;
 }
 
-cudaError_t launch_decode_append(const DecodeParams& p, cudaStream_t stream) {
-  fal_decode_append_kernel<<<p.batch * p.heads_kv, 32, 0, stream>>>(p);
-  return cudaGetLastError();
-}
-
-cudaError_t launch_decode_splitk(const DecodeParams& p, cudaStream_t stream) {
+cudaError_t launch_decode(const DecodeParams& p, cudaStream_t stream) {
   if (p.head_dim == 128) return launch_splitk_t<128>(p, stream);
   if (p.head_dim == 64) return launch_splitk_t<64>(p, stream);
   if (p.head_dim == 256) return launch_splitk_t<256>(p, stream);
   return cudaErrorInvalidValue;
-}
-
-cudaError_t launch_decode_combine(const DecodeParams& p, cudaStream_t stream) {
-  fal_decode_combine_kernel<<<p.batch * p.heads_q, p.head_dim, 0, stream>>>(p);
-  return cudaGetLastError();
 }
 
 }  // namespace fal

@@ -80,7 +80,7 @@ struct BwdPostParams {
 };
 cudaError_t launch_bwd_post(const BwdPostParams& p, cudaStream_t stream);
 
-// Split-K decode over a KV cache, then the log-sum-exp combine.
+// Decode over a KV cache in one launch: append, split-K streaming pass, log-sum-exp merge.
 struct DecodeParams {
   const void* q;        // [batch, heads_q, head_dim] fp16, contiguous
   void* k_cache;        // fp16
@@ -95,6 +95,7 @@ struct DecodeParams {
   float* lse;           // optional [batch, heads_q]
   float* part_o;        // workspace [batch, heads_q, splits, head_dim] fp32
   float* part_ml;       // workspace [batch, heads_q, splits, 2] (max, sum)
+  int* arrivals;        // workspace [batch, heads_q] arrival counters: zero on entry, zero again on exit
   int batch;
   int heads_q;
   int heads_kv;
@@ -109,8 +110,6 @@ struct DecodeParams {
 constexpr size_t kDecodeStaticScratchBytes = 8u << 20;
 cudaError_t decode_static_scratch(float** ptr);
 
-cudaError_t launch_decode_append(const DecodeParams& p, cudaStream_t stream);
-cudaError_t launch_decode_splitk(const DecodeParams& p, cudaStream_t stream);
-cudaError_t launch_decode_combine(const DecodeParams& p, cudaStream_t stream);
+cudaError_t launch_decode(const DecodeParams& p, cudaStream_t stream);
 
 }  // namespace fal

@@ -19,7 +19,8 @@ namespace fal {
 // ---------------------------------------------------------------------------
 enum DeviceStatus : int {
   kDevOk = 0,
-  kDevWaitTimeout = 1000,  // + barrier id
+  kDevWaitTimeout = 1000,     // + barrier id
+  kDevAppendOverflow = 2000,  // decode: a new token did not fit the cache (length >= capacity) and was dropped
 };
 
 // Cycles a single mbarrier wait may take before it gives up (about one

@@ -94,7 +94,8 @@ def profile_read(kind):
     _check(_lib.fal_profile_read(int(kind), ctypes.byref(total), ctypes.byref(n)))
     return total.value, n.value
 
-# One device status word per GPU; kernels set it non-zero if an internal wait ran out.
+# One device status word per GPU (a 4-byte tensor created on first use); kernels set it non-zero if
+# an internal wait ran out (1000 + barrier id) or a decode append found its cache full (2000).
 _status = {}
 
 
@@ -118,6 +119,7 @@ def device_status(device=None):
 
 
 def reset_device_status(device=None):
+    """Clears the device status word (and creates it if this is the first use on the device)."""
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
     _status_word(torch.device(device)).zero_()
@@ -330,27 +332,33 @@ def backward_varlen(dO, Q, K, V, O, L, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
 _decode_ws = {}
 
 
-def decode(q, k_cache, v_cache, cache_seqlens, softmax_scale, k_new=None, v_new=None,
-           cache_layout="bshd", return_lse=False, out=None, cache_starts=None):
-    """Single-token decode.  q [B,Hq,d]; caches [B,S,Hkv,d] ("bshd") or [B,Hkv,S,d] ("bhsd").
+def _decode_workspace(device, nbytes):
+    """Zero-initialised decode workspace of the current stream, kept across calls.
 
-    If k_new / v_new ([B,Hkv,d]) are given they are written into the caches at position
-    cache_seqlens[b] first.  `cache_starts` (int32 [B], optional) is the first position each
-    entry attends to -- the positions before it are padding (a left-padded batch).
-    Returns O [B,Hq,d] fp16 (and LSE [B,Hq] fp32 if asked).
+    One workspace per (device, stream): calls on different streams may overlap on the GPU and must
+    not share partial results or arrival counters.  A workspace is replaced when a call needs more
+    room.  It is created zeroed (the library's arrival counters must start at zero and are left at
+    zero by every call).
     """
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _decode_ws.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _decode_ws[key] = ws
+    return ws
+
+
+def _decode_args(q, k_cache, v_cache, cache_seqlens, k_new, v_new, cache_layout, out, lse, cache_starts=None):
+    """Checks every buffer a decode call reads or writes; returns (B, Hq, Hkv, S, d, k strides, v strides)."""
     _require_cuda_half("q", q, 3)
     _require_cuda_half("k_cache", k_cache, 4)
     _require_cuda_half("v_cache", v_cache, 4)
-    _same_device(q, k_cache, v_cache, cache_seqlens, k_new, v_new, cache_starts)
+    _same_device(q, k_cache, v_cache, cache_seqlens, k_new, v_new, cache_starts, out, lse)
     if not q.is_contiguous():
         raise RuntimeError("q must be contiguous [B, H_q, d]")
-    if cache_seqlens.dtype != torch.int32:
-        raise RuntimeError("cache_seqlens must be int32")
-    if cache_starts is not None and (cache_starts.dtype != torch.int32 or cache_starts.numel() != q.shape[0]
-                                     or not cache_starts.is_contiguous()):
-        raise RuntimeError("cache_starts must be a contiguous int32 [B] tensor")
     B, Hq, d = q.shape
+    if tuple(v_cache.shape) != tuple(k_cache.shape):
+        raise RuntimeError("k_cache and v_cache must have the same shape")
     if cache_layout == "bshd":
         S, Hkv = k_cache.shape[1], k_cache.shape[2]
         ks = _Strides(k_cache.stride(0), k_cache.stride(2), k_cache.stride(1))
@@ -361,25 +369,49 @@ def decode(q, k_cache, v_cache, cache_seqlens, softmax_scale, k_new=None, v_new=
         vs = _Strides(v_cache.stride(0), v_cache.stride(1), v_cache.stride(2))
     else:
         raise ValueError("cache_layout must be 'bshd' or 'bhsd'")
+    if k_cache.shape[0] != B or k_cache.shape[3] != d:
+        raise RuntimeError("the caches must have q's batch size and head_dim")
+    if Hkv == 0 or Hq % Hkv != 0:
+        raise RuntimeError("H_q must be divisible by H_kv")
+    if cache_seqlens.dtype != torch.int32 or cache_seqlens.numel() != B or not cache_seqlens.is_contiguous():
+        raise RuntimeError("cache_seqlens must be a contiguous int32 [B] tensor")
+    if cache_starts is not None and (cache_starts.dtype != torch.int32 or cache_starts.numel() != B
+                                     or not cache_starts.is_contiguous()):
+        raise RuntimeError("cache_starts must be a contiguous int32 [B] tensor")
+    if (k_new is None) != (v_new is None):
+        raise RuntimeError("k_new and v_new go together")
     if k_new is not None:
-        _require_cuda_half("k_new", k_new, 3)
-        _require_cuda_half("v_new", v_new, 3)
-        if not (k_new.is_contiguous() and v_new.is_contiguous()):
-            raise RuntimeError("k_new / v_new must be contiguous [B, H_kv, d]")
+        for name, t in (("k_new", k_new), ("v_new", v_new)):
+            _require_cuda_half(name, t, 3)
+            if tuple(t.shape) != (B, Hkv, d) or not t.is_contiguous():
+                raise RuntimeError(f"{name} must be contiguous [B, H_kv, d]")
+    if out is not None and (out.dtype != torch.float16 or tuple(out.shape) != (B, Hq, d) or not out.is_contiguous()):
+        raise RuntimeError("out must be contiguous float16 [B, H_q, d]")
+    if lse is not None and (lse.dtype != torch.float32 or tuple(lse.shape) != (B, Hq) or not lse.is_contiguous()):
+        raise RuntimeError("lse must be contiguous float32 [B, H_q]")
+    return B, Hq, Hkv, S, d, ks, vs
+
+
+def decode(q, k_cache, v_cache, cache_seqlens, softmax_scale, k_new=None, v_new=None,
+           cache_layout="bshd", return_lse=False, out=None, cache_starts=None):
+    """Single-token decode.  q [B,Hq,d]; caches [B,S,Hkv,d] ("bshd") or [B,Hkv,S,d] ("bhsd").
+
+    If k_new / v_new ([B,Hkv,d]) are given they are written into the caches at position
+    cache_seqlens[b] first (an entry whose cache is full drops its new token and the device status
+    word becomes 2000).  `cache_starts` (int32 [B], optional) is the first position each entry
+    attends to -- the positions before it are padding (a left-padded batch).  The split-K scratch is
+    kept per (device, stream) between calls.  Returns O [B,Hq,d] fp16 (and LSE [B,Hq] fp32 if asked).
+    """
+    B, Hq, Hkv, S, d, ks, vs = _decode_args(q, k_cache, v_cache, cache_seqlens, k_new, v_new, cache_layout,
+                                            out, None, cache_starts)
     o = torch.empty((B, Hq, d), dtype=torch.float16, device=q.device) if out is None else out
     lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if return_lse else None
     nbytes = _lib.fal_decode_workspace_bytes(B, Hq, S, d)
-    key = (q.device.index, nbytes)
-    ws = _decode_ws.get(key)
-    if ws is None:
-        # Kept across calls: decode loops call this once per generated token.
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-        _decode_ws.clear()
-        _decode_ws[key] = ws
+    ws = _decode_workspace(q.device, nbytes)
     tail = (k_new.data_ptr() if k_new is not None else None,
             v_new.data_ptr() if v_new is not None else None,
             o.data_ptr(), lse.data_ptr() if lse is not None else None,
-            B, Hq, Hkv, S, d, float(softmax_scale), ws.data_ptr(), nbytes,
+            B, Hq, Hkv, S, d, float(softmax_scale), ws.data_ptr(), ws.numel(),
             _status_word(q.device).data_ptr(), _stream(q))
     if cache_starts is None:
         _check(_lib.fal_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ks, vs,
@@ -397,32 +429,18 @@ def decode_static(q, k_cache, v_cache, cache_seqlens, softmax_scale, out, k_new=
     Some users of this library run where device allocation is off limits -- a serving loop with
     a memory budget fixed at start-up, an operator callback that only gets the operator's own
     tensors, code that cannot afford the device-wide synchronisation an allocation may imply.
-    This call therefore allocates nothing, in the library or here: the caller passes every
-    buffer, `out` ([B,Hq,d] fp16) and the optional `lse` ([B,Hq] fp32) included, and the split-K
-    partials go to an 8 MiB scratch array inside the library.  Problems whose partials do not
-    fit (fal_decode_workspace_bytes > 8 MiB) raise RuntimeError.  Make the first call on a
-    device outside stream capture (it looks up the scratch address once), and do not let two
-    calls overlap on the GPU: they share the scratch.  Returns `out`.
+    This call therefore allocates nothing in the library, and nothing here once the device's
+    status word exists: the caller passes every buffer, `out` ([B,Hq,d] fp16) and the optional
+    `lse` ([B,Hq] fp32) included, and the split-K scratch is an 8 MiB array inside the library.
+    The status word is a 4-byte tensor this module creates on the first call of ANY of its
+    functions on a device; a caller that cannot allocate even that once calls
+    `reset_device_status()` during start-up.  Problems whose scratch does not fit
+    (fal_decode_workspace_bytes > 8 MiB) raise RuntimeError.  Make the first call on a device
+    outside stream capture (it looks up the scratch address once), and do not let two calls
+    overlap on the GPU: they share the scratch.  Returns `out`.
     """
-    _require_cuda_half("q", q, 3)
-    _require_cuda_half("k_cache", k_cache, 4)
-    _require_cuda_half("v_cache", v_cache, 4)
-    _same_device(q, k_cache, v_cache, cache_seqlens, k_new, v_new, out, lse)
-    if not q.is_contiguous() or not out.is_contiguous() or out.dtype != torch.float16:
-        raise RuntimeError("q and out must be contiguous [B, H_q, d] float16")
-    if cache_seqlens.dtype != torch.int32:
-        raise RuntimeError("cache_seqlens must be int32")
-    B, Hq, d = q.shape
-    if cache_layout == "bshd":
-        S, Hkv = k_cache.shape[1], k_cache.shape[2]
-        ks = _Strides(k_cache.stride(0), k_cache.stride(2), k_cache.stride(1))
-        vs = _Strides(v_cache.stride(0), v_cache.stride(2), v_cache.stride(1))
-    elif cache_layout == "bhsd":
-        Hkv, S = k_cache.shape[1], k_cache.shape[2]
-        ks = _Strides(k_cache.stride(0), k_cache.stride(1), k_cache.stride(2))
-        vs = _Strides(v_cache.stride(0), v_cache.stride(1), v_cache.stride(2))
-    else:
-        raise ValueError("cache_layout must be 'bshd' or 'bhsd'")
+    B, Hq, Hkv, S, d, ks, vs = _decode_args(q, k_cache, v_cache, cache_seqlens, k_new, v_new, cache_layout,
+                                            out, lse)
     _check(_lib.fal_decode_static(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ks, vs,
                                   cache_seqlens.data_ptr(),
                                   k_new.data_ptr() if k_new is not None else None,

@@ -146,18 +146,29 @@ FAL_API int fal_bwd_varlen(const void* d_out, const void* q, const void* k, cons
                    float softmax_scale, int is_causal,
                    void* workspace, size_t workspace_bytes, int* status, void* stream);
 
-/* Bytes of scratch fal_decode needs for its split-K partial results. */
+/*
+ * Bytes of scratch fal_decode needs: its split-K partial results followed by one int32 arrival
+ * counter per (batch entry, query head).  The counters must be ZERO when a call starts and every
+ * call puts them back to zero, so a workspace is cleared once (cudaMemsetAsync over the whole
+ * workspace is enough) after it is allocated and can then serve any number of calls, also with
+ * other shapes that fit it.  The partial results need no initialisation.  Calls that use the same
+ * workspace must not overlap on the GPU.  The workspace must be 16-byte aligned.
+ */
 FAL_API size_t fal_decode_workspace_bytes(int batch, int heads_q, int capacity, int head_dim);
 
 /*
- * Single-token decode against a KV cache (q_len = 1): split-K streaming pass
- * plus a log-sum-exp combine.  Stands in for the eager fallback branch of the
+ * Single-token decode against a KV cache (q_len = 1) in ONE kernel launch: the new token's
+ * K/V row is written by the thread block whose split contains its position, every block
+ * streams its split of the cache once, and the block that finishes last for a (batch entry,
+ * head group) merges the splits (log-sum-exp).  Stands in for the eager fallback branch of the
  * reference's attention hook (flash_attn_legacy/integrations.py:77-98): no
  * causal mask, GQA by head mapping, softmax over the cached positions.
  *   q, o [B,Hq,d] contiguous; caches addressed by strides as [B,Hkv,position,d];
  *   cache_seqlens device int32 [B] (positions already valid); if k_new/v_new
  *   ([B,Hkv,d] contiguous) are given they are first written at position
  *   cache_seqlens[b] and attended to as well.  lse [B,Hq] is optional.
+ *   A new token for an entry whose cache is already full (cache_seqlens[b] >= capacity) is
+ *   neither stored nor attended to; the kernel then sets *status to 2000 (append overflow).
  */
 FAL_API int fal_decode(const void* q, void* k_cache, void* v_cache,
                const fal_strides* k_strides, const fal_strides* v_strides,
@@ -205,10 +216,12 @@ FAL_API int fal_decode_ranged(const void* q, void* k_cache, void* v_cache,
  *   - the first call on each device looks up the scratch's device address
  *     (cudaGetSymbolAddress); make that first call before any stream capture;
  *   - all calls on a device share the one array, which keeps whatever the last call
- *     left in it.  Nothing in it has to start at zero (every slot the combine step
- *     reads is written earlier in the same call), but two calls that overlap on the
- *     GPU -- different streams, or different host threads without ordering -- race
- *     on it and corrupt each other's results.  Serialise them on one stream.
+ *     left in it.  The partial results need no clearing (every slot the merge step reads
+ *     is written earlier in the same call); the arrival counters behind them start at
+ *     zero because the array is zero-initialised when the library is loaded, and every
+ *     call leaves them at zero.  Two calls that overlap on the GPU -- different streams,
+ *     or different host threads without ordering -- race on the array and corrupt each
+ *     other's results.  Serialise them on one stream.
  */
 #define FAL_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
 FAL_API int fal_decode_static(const void* q, void* k_cache, void* v_cache,
@@ -229,7 +242,7 @@ FAL_API int fal_decode_static(const void* q, void* k_cache, void* v_cache,
 enum fal_kernel_kind {
   FAL_KERNEL_FWD = 0,          /* forward main kernel */
   FAL_KERNEL_BWD = 1,          /* backward dK/dV/dQ kernel (without pre/post passes) */
-  FAL_KERNEL_DECODE_SPLITK = 2 /* decode streaming pass (without append / combine) */
+  FAL_KERNEL_DECODE_SPLITK = 2 /* the decode kernel (append, split-K streaming pass, merge) */
 };
 FAL_API int fal_profile_enable(int on);
 FAL_API int fal_profile_read(int kind, double* total_ms, int* launches);

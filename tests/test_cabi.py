@@ -58,9 +58,11 @@ def test_workspace_sizes(lib):
     expect = 4 * 32 * rows * 128 * 4 + 4 * 32 * rows * 4
     assert lib.fal_bwd_workspace_bytes(4, 32, 4096, 128) == expect
     assert lib.fal_bwd_workspace_bytes(0, 32, 4096, 128) == 0
-    # 32 splits of 1024 positions, (d + 2) floats per (batch, head, split)
-    assert lib.fal_decode_workspace_bytes(64, 32, 32768, 128) == 64 * 32 * 32 * 130 * 4
-    assert lib.fal_decode_workspace_bytes(1, 8, 1000, 64) == 1 * 8 * 1 * 66 * 4
+    # 32 splits of 1024 positions, (d + 2) floats per (batch, head, split), then one int32 arrival
+    # counter per (batch, head); both parts rounded up to 16 bytes
+    assert lib.fal_decode_workspace_bytes(64, 32, 32768, 128) == 64 * 32 * 32 * 130 * 4 + 64 * 32 * 4
+    assert lib.fal_decode_workspace_bytes(1, 8, 1000, 64) == 1 * 8 * 1 * 66 * 4 + 8 * 4
+    assert lib.fal_decode_workspace_bytes(1, 1, 10, 64) == 272 + 16
 
 
 class Strides(ctypes.Structure):
@@ -88,6 +90,22 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     # misaligned output pointer
     assert lib.fal_fwd(fake, fake, fake, fake + 2, fake, 1, 2, 2, 128, 128, 64, st, st, st, st, 0.125, 0, None, None) == -1
 
+    # the bottom-right-aligned mask (2) exists for the batched forward only: the packed forward and both
+    # backward entry points refuse it instead of silently masking top-left
+    cu = fake
+    lib.fal_fwd_varlen.restype = i
+    lib.fal_fwd_varlen.argtypes = [vp] * 7 + [i] * 8 + [sp] * 4 + [f, i, vp, vp]
+    assert lib.fal_fwd_varlen(fake, fake, fake, fake, fake, cu, cu, 1, 128, 128, 128, 128, 2, 2, 64,
+                              st, st, st, st, 0.125, 2, None, None) == -1
+    lib.fal_bwd.restype = i
+    lib.fal_bwd.argtypes = [vp] * 9 + [i] * 6 + [sp] * 8 + [f, i, vp, ctypes.c_size_t, vp, vp]
+    assert lib.fal_bwd(fake, fake, fake, fake, fake, fake, fake, fake, fake, 1, 2, 2, 128, 128, 64,
+                       st, st, st, st, st, st, st, st, 0.125, 2, fake, 1 << 30, None, None) == -1
+    lib.fal_bwd_varlen.restype = i
+    lib.fal_bwd_varlen.argtypes = [vp] * 9 + [vp, vp] + [i] * 8 + [sp] * 8 + [f, i, vp, ctypes.c_size_t, vp, vp]
+    assert lib.fal_bwd_varlen(fake, fake, fake, fake, fake, fake, fake, fake, fake, cu, cu, 1, 128, 128, 128, 128,
+                              2, 2, 64, st, st, st, st, st, st, st, st, 0.125, 2, fake, 1 << 30, None, None) == -1
+
     lib.fal_decode.restype = i
     lib.fal_decode.argtypes = [vp, vp, vp, sp, sp, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp, ctypes.c_size_t, vp, vp]
     # k_new without v_new
@@ -104,6 +122,13 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
                                  0.125, fake, 1 << 20, None, None) == -1
     assert lib.fal_decode_ranged(fake, fake, fake, st, st, fake, fake, None, None, fake, None, 1, 8, 2, 128, 64,
                                  0.125, fake, 16, None, None) == -3
+    # the allocation-free form validates the same arguments, then its size limit (8 MiB), before any CUDA call
+    lib.fal_decode_static.restype = i
+    lib.fal_decode_static.argtypes = [vp, vp, vp, sp, sp, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp, vp]
+    assert lib.fal_decode_static(fake, fake, fake, st, st, fake, fake, None, fake, None, 1, 8, 2, 128, 64, 0.125,
+                                 None, None) == -1
+    assert lib.fal_decode_static(fake, fake, fake, st, st, fake, None, None, fake, None, 64, 32, 8, 32768, 128,
+                                 0.125, None, None) == -7
 
 
 def test_profile_api_is_inert_without_launches(lib):
