@@ -14,6 +14,14 @@ region.  With --gpus N each rank (one process per GPU) runs the same workload on
 shard of independent (batch, head-group) units -- no collective on the data path -- and
 the time is the maximum over ranks.
 
+With --gpus N > 1 the line also carries `extra.sharded`: one timed leg per partitioning of the other
+sharded configurations on the same ranks (strong scaling: the total work is that of one GPU's
+problem) -- the headline workload with its 32 (batch, KV-head group) units dealt to the ranks, the
+packed workload with its heads dealt, the decode workload with its batch entries dealt, and the
+131072-token sequence in the zigzag ring -- each with its own one-GPU time taken in the same run,
+the efficiency against it, the device status word and a sampled error against the CPU oracle
+(rank 0, outside every timed region; the oracle is only ever the checker).
+
 --impl reference times the reference's CPU math path (the fp32 naive attention its
 tests use, restated in oracle/attention_oracle.py) on the host cores, on a bounded
 sample of the same workload.
@@ -51,6 +59,37 @@ def measured_peaks():
         return {"bf16_tflops": m.get("bf16_tflops"), "bf16_tflops_sustained": m.get("bf16_tflops_sustained"),
                 "hbm_gbs": m.get("hbm_gbs"), "source": "measured"}
     return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+KERNEL_SOURCES = ("fal_bwd.cu", "sm100_ptx.cuh", "fal_common.h", "fal_launch.h")
+
+
+def kernel_source_hash():
+    """sha256 over the files the backward kernel is compiled from (what an ncu capture belongs to)."""
+    import hashlib
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, "flash-attention-legacy_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def recorded_traffic():
+    """DRAM bytes per launch of the backward kernel on the bench workload, from the tracked record of
+    the last ncu capture -- or None with the reason when that record belongs to other kernel sources
+    or another workload (a stale figure must not ride along with a new build)."""
+    path = os.path.join(ROOT, "profiles", "bwd_kernel_config2.traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+    except (OSError, ValueError):
+        return None, "no capture record"
+    if rec.get("workload") != WORKLOAD_NAME:
+        return None, "the capture record is for another workload"
+    if rec.get("kernel_source_sha256") != kernel_source_hash():
+        return None, "kernel sources changed since the capture (%s)" % rec.get("captured_at_commit", "?")
+    return float(rec["dram_bytes_read"]) + float(rec["dram_bytes_write"]), "ncu capture at commit %s" % rec.get(
+        "captured_at_commit", "?")
 
 
 class ClockSampler:
@@ -201,10 +240,10 @@ def run_reference(args):
     }))
 
 
-def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False):
+def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False, check=False):
     """Secondary metric: KV-cache split-K decode with appends, B=64 Hq=32 Hkv=8 d=128, cache 32768.
 
-    graph=True captures one step (append + split-K + combine + the length increment) in a CUDA graph
+    graph=True captures one step (split-K with append, combine, the length increment) in a CUDA graph
     and replays it `steps` times: a small per-GPU batch is otherwise bound by the host's launch path,
     not by the kernels.  Every replay appends the same new token (at a new position) and uses the same
     query; the kernels and the bytes they move are those of the eager loop."""
@@ -250,10 +289,17 @@ def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False):
     res = {"workload": f"decode_B{B}_Hq32_Hkv8_d128_cache32768_{steps}steps_with_append",
            "ms_per_step": ms, "kv_bytes_per_step": kv_bytes, "kv_gbs": kv_bytes / ms / 1e6,
            "frac_of_hbm_peak": kv_bytes / ms / 1e6 / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
-           "launches_per_step": 3, "launch_path": "cuda graph replay" if graph else "eager"}
+           "launches_per_step": 2, "launch_path": "cuda graph replay" if graph else "eager"}
     if k_n:
         res["splitk_kernel_ms"] = k_ms / k_n
         res["splitk_kernel_gbs"] = kv_bytes / (k_ms / k_n) / 1e6
+    if check and not graph:
+        # the last step's output of two entries against the CPU oracle (the checker, never the product)
+        orc = _oracle()
+        idx = torch.tensor([0, B - 1], device="cuda")
+        o_ref, _ = orc.decode_fwd(q[steps - 1][idx].cpu(), kc[idx].cpu(), vc[idx].cpu(), lens[idx].cpu(), scale)
+        res["check"] = {"checked": "entries 0 and %d after the last step" % (B - 1),
+                        "o": orc.rel_max_err(out[idx], o_ref)}
     del kc, vc
     torch.cuda.empty_cache()
     return res
@@ -353,16 +399,25 @@ def run_shapes(args, ext):
         for _ in range(args.warmup):
             fn()
         torch.cuda.synchronize()
+        kind_id = ext.KERNEL_BWD if kind == "bwd" else ext.KERNEL_FWD
+        ext.profile_enable(True)
+        ext.profile_read(kind_id)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
             fn()
         e1.record()
         torch.cuda.synchronize()
+        k_ms, k_n = ext.profile_read(kind_id)
+        ext.profile_enable(False)
         ms = e0.elapsed_time(e1) / args.steps
         flops = mult * 4.0 * B * Hq * d * pairs
+        # ms_per_step: back-to-back calls from Python (a small problem is bound by the host there);
+        # main_kernel_ms: the library's event pair around the main kernel alone
         print(json.dumps({"metric": "attn_kernel_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT,
                           "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                          "main_kernel_ms": k_ms / k_n if k_n else None,
+                          "main_kernel_tflops": flops / (k_ms / k_n * 1e-3) / 1e12 if k_n else None,
                           "dtype": "f16", "data": "synthetic",
                           "config": {"workload": spec, "pass": kind, "causal": causal,
                                      "l2_policy": "back-to-back launches on the same tensors"},
@@ -464,6 +519,233 @@ def run_long_context(args, rank, world, local, dist, ext):
     if dist is not None:
         dist.destroy_process_group()
 
+# ---------------------------------------------------------------------------------------------
+# Sharded legs (--gpus N > 1): strong scaling of the other partitionings, on the same ranks
+# ---------------------------------------------------------------------------------------------
+def _time_steps(fn, steps, warmup, dist, dev):
+    """Device time per step of fn(): warm-up, barrier + sync on both sides, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    return _max_over_ranks(dist, dev, e0.elapsed_time(e1) / steps)
+
+
+def _oracle():
+    sys.path.insert(0, ROOT)
+    from oracle import attention_oracle as orc
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))  # torchrun exports OMP_NUM_THREADS=1
+    return orc
+
+
+def leg_units_split(args, rank, world, dev, dist, ext, full_ms):
+    """The headline workload's 32 (batch, KV-head group) units dealt to the ranks: every rank gets all
+    four batch entries and 8 / N KV heads with their query heads."""
+    w = WORKLOAD
+    hkv = w["Hkv"] // world
+    hq = hkv * (w["Hq"] // w["Hkv"])
+    B, N, d = w["B"], w["N"], w["d"]
+    scale = 1.0 / math.sqrt(d)
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    q, do = (torch.randn(B, hq, N, d, device=dev, generator=gen).half() for _ in range(2))
+    k, v = (torch.randn(B, hkv, N, d, device=dev, generator=gen).half() for _ in range(2))
+    o = torch.empty_like(q)
+    lse = torch.empty(B, hq, N, device=dev, dtype=torch.float32)
+    grads = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    ws = torch.empty(ext.backward_workspace_bytes(B, hq, N, d), dtype=torch.uint8, device=dev)
+
+    def step():
+        ext.forward(q, k, v, scale, True, out=o, lse=lse)
+        ext.backward(do, q, k, v, o, lse, scale, True, out=grads, workspace=ws)
+
+    ms = _time_steps(step, args.steps, args.warmup, dist, dev)
+    fwd, bwd = step_flops()
+    res = {"workload": WORKLOAD_NAME, "parallelism": f"{B * hkv} of 32 (batch, KV-head group) units per rank, no collective",
+           "ms_per_step": ms, "value": (fwd + bwd) / (ms * 1e-3) / 1e12, "unit": UNIT,
+           "one_gpu_ms_per_step": full_ms, "efficiency_vs_one_gpu": full_ms / (world * ms)}
+    if rank == 0:
+        orc = _oracle()
+        sl = slice(0, 4)
+        qs, ks, vs, gs = q[1:2, sl].cpu(), k[1:2, :1].cpu(), v[1:2, :1].cpu(), do[1:2, sl].cpu()
+        o_ref, lse_ref = orc.attention_fwd_blocked(qs, ks, vs, scale, True)
+        ref = orc.attention_bwd_blocked(qs, ks, vs, gs, scale, True)
+        res["sampled_error_vs_oracle"] = {
+            "checked": "one (batch, KV-head group) unit of rank 0 in full",
+            "o": orc.rel_max_err(o[1:2, sl], o_ref), "lse_abs": orc.abs_max_err(lse[1:2, sl], lse_ref),
+            "dq": orc.rel_max_err(grads[0][1:2, sl], ref[0]), "dk": orc.rel_max_err(grads[1][1:2, :1], ref[1]),
+            "dv": orc.rel_max_err(grads[2][1:2, :1], ref[2])}
+    res["device_status"] = ext.device_status()
+    return res
+
+
+def leg_varlen_split(args, rank, world, dev, dist, ext):
+    """16 packed causal sequences of 64..4096 tokens (seed 2), H=16, d=128, forward + backward: the heads
+    dealt to the ranks.  The one-GPU time (all 16 heads) is taken on every rank in the same run."""
+    H, d, num_seqs = 16, 128, 16
+    lens = torch.randint(64, 4097, (num_seqs,), generator=torch.Generator().manual_seed(2))
+    cu_host = torch.zeros(num_seqs + 1, dtype=torch.int32)
+    cu_host[1:] = torch.cumsum(lens, 0)
+    total, max_len = int(cu_host[-1]), int(lens.max())
+    cu = cu_host.to(dev)
+    scale = 1.0 / math.sqrt(d)
+    flops = 3.5 * 2.0 * H * d * float((lens.double() ** 2).sum())
+    out = {}
+    for label, heads in (("one_gpu", H), ("shard", H // world)):
+        gen = torch.Generator(device="cuda").manual_seed(200 + rank)
+        q, k, v, do = (torch.randn(total, heads, d, device=dev, generator=gen).half() for _ in range(4))
+        keep = {}
+
+        def step():
+            o, lse = ext.forward_varlen(q, k, v, cu, cu, max_len, max_len, scale, True)
+            keep["o"], keep["g"] = o, ext.backward_varlen(do, q, k, v, o, lse, cu, cu, max_len, max_len, scale, True)
+
+        out[label] = _time_steps(step, args.steps, args.warmup, dist, dev)
+        if label == "shard":
+            shard = (q, k, v, do, keep["o"], keep["g"])
+    ms = out["shard"]
+    res = {"workload": f"varlen_16seqs_64to4096_{total}tokens_H16_d128_causal_fwd_bwd",
+           "parallelism": f"{H // world} of 16 heads per rank, no collective", "ms_per_step": ms,
+           "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "one_gpu_ms_per_step": out["one_gpu"],
+           "efficiency_vs_one_gpu": out["one_gpu"] / (world * ms)}
+    if rank == 0:
+        orc = _oracle()
+        q, k, v, do, o, g = shard
+        order = torch.argsort(lens)[:6].tolist()   # the six shortest sequences of head 0
+        worst = {"o": 0.0, "dq": 0.0, "dk": 0.0, "dv": 0.0}
+        for s_i in order:
+            a, e = int(cu_host[s_i]), int(cu_host[s_i + 1])
+            pick = lambda t: t[a:e, :1].permute(1, 0, 2).unsqueeze(0).cpu()
+            o_ref, _ = orc.attention_fwd(pick(q), pick(k), pick(v), scale, True)
+            ref = orc.attention_bwd(pick(q), pick(k), pick(v), pick(do), scale, True)
+            worst["o"] = max(worst["o"], orc.rel_max_err(pick(o), o_ref))
+            for name, got, want in zip(("dq", "dk", "dv"), g, ref):
+                worst[name] = max(worst[name], orc.rel_max_err(pick(got), want))
+        res["sampled_error_vs_oracle"] = dict(worst, checked="head 0 of rank 0 on the six shortest sequences")
+    res["device_status"] = ext.device_status()
+    return res
+
+
+def leg_decode_split(args, rank, world, dev, dist, ext, peaks):
+    """The decode workload (batch 64, cache 32768, 256 steps with appends): the batch entries dealt to the
+    ranks.  The one-GPU time (all 64 entries) is taken on every rank in the same run."""
+    full = run_decode_extra(ext, peaks, steps=256, batch=64, seed=300 + rank)
+    full_ms = _max_over_ranks(dist, dev, full["ms_per_step"])
+    shard_n = 64 // world
+    part = run_decode_extra(ext, peaks, steps=256, batch=shard_n, seed=300 + rank, check=(rank == 0))
+    ms = _max_over_ranks(dist, dev, part["ms_per_step"])
+    total_bytes = part["kv_bytes_per_step"]
+    if dist is not None:
+        t = torch.tensor([total_bytes], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        total_bytes = t.item()
+    res = {"workload": "decode_B64_Hq32_Hkv8_d128_cache32768_256steps_with_append",
+           "parallelism": f"{shard_n} of 64 batch entries per rank, no collective", "launch_path": "eager, two launches per step",
+           "ms_per_step": ms, "value": total_bytes / ms / 1e6, "unit": "GB/s",
+           "frac_of_hbm_peak_per_gpu": total_bytes / ms / 1e6 / world / peaks["hbm_gbs"],
+           "one_gpu_ms_per_step": full_ms, "efficiency_vs_one_gpu": full_ms / (world * ms)}
+    if "check" in part:
+        res["sampled_error_vs_oracle"] = part["check"]
+    res["device_status"] = ext.device_status()
+    return res
+
+
+def leg_ring(args, rank, world, local, dev, dist, ext):
+    """One 131072-token causal sequence, forward + backward, zigzag rows over the ranks with the ring K/V
+    exchange.  The one-GPU time (the whole sequence on one GPU) is taken on every rank in the same run."""
+    from flash_attn_legacy import distributed as fd
+    B, Hq, Hkv, N, d = 1, 32, 8, 131072, 128
+    scale = 1.0 / math.sqrt(d)
+    flops = 3.5 * 4.0 * B * Hq * N * N * d * 0.5
+
+    def local_inputs(r, rows):
+        gen = torch.Generator(device="cuda").manual_seed(400 + r)
+        return [torch.randn(B, h, rows, d, device=dev, generator=gen).half() for h in (Hq, Hkv, Hkv, Hq)]
+
+    q, k, v, do = local_inputs(1000 + rank, N)
+
+    def whole():
+        o, lse = ext.forward(q, k, v, scale, True)
+        ext.backward(do, q, k, v, o, lse, scale, True)
+
+    one_gpu_ms = _time_steps(whole, 2, 1, dist, dev)
+    del q, k, v, do
+    torch.cuda.empty_cache()
+    rows = N // world
+    q, k, v, do = local_inputs(rank, rows)
+    keep = {}
+
+    def step():
+        o, lse = fd.ring_attention_forward(q, k, v, scale, True, layout="zigzag", check_shards=False)
+        keep["o"], keep["lse"] = o, lse
+        keep["g"] = fd.ring_attention_backward(do, q, k, v, o, lse, scale, True, layout="zigzag", check_shards=False)
+
+    ms = _time_steps(step, 3, 1, dist, dev)
+    res = {"workload": "long_context_B1_Hq32_Hkv8_N131072_d128_causal_fwd_bwd",
+           "parallelism": f"zigzag sequence shards over {world} ranks, ring K/V exchange (NCCL point-to-point)",
+           "ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT,
+           "one_gpu_ms_per_step": one_gpu_ms, "efficiency_vs_one_gpu": one_gpu_ms / (world * ms)}
+    if rank == 0:
+        # Rank 0 holds the first and the LAST chunk of the sequence: its last 256 local rows are the last
+        # 256 rows of the whole problem and see every key.  Every rank's K/V of one KV head is regenerated
+        # here from its seed and put in sequence order.
+        orc = _oracle()
+        h = 3
+        c = rows // 2
+        kf = torch.empty(1, 1, N, d)
+        vf = torch.empty(1, 1, N, d)
+        for r in range(world):
+            _, kr, vr, _ = local_inputs(r, rows)
+            (a0, a1), (b0, b1) = fd.zigzag_rows(N, world, r)
+            kf[:, :, a0:a1], kf[:, :, b0:b1] = kr[:, h:h + 1, :c].float().cpu(), kr[:, h:h + 1, c:].float().cpu()
+            vf[:, :, a0:a1], vf[:, :, b0:b1] = vr[:, h:h + 1, :c].float().cpu(), vr[:, h:h + 1, c:].float().cpu()
+            del kr, vr
+        sl = slice(4 * h, 4 * h + 4)
+        r0, r1 = N - 256, N
+        qf, gf = q[:, sl, rows - 256:].float().cpu(), do[:, sl, rows - 256:].float().cpu()
+        s_ = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+        s_.masked_fill_(torch.arange(N).view(1, -1) > torch.arange(r0, r1).view(-1, 1), float("-inf"))
+        lse_ref = torch.logsumexp(s_, -1)
+        p = torch.softmax(s_, -1)
+        o_ref = torch.matmul(p, vf)
+        ds = p * (torch.matmul(gf, vf.transpose(-1, -2)) - (gf * o_ref).sum(-1, keepdim=True))
+        dq, dk, dv = keep["g"]
+        res["sampled_error_vs_oracle"] = {
+            "checked": "the last 256 rows of the sequence (rank 0's last rows), one KV-head group: O, LSE, dQ, and dK, dV of the last 256 keys",
+            "o": orc.rel_max_err(keep["o"][:, sl, rows - 256:], o_ref),
+            "lse_abs": orc.abs_max_err(keep["lse"][:, sl, rows - 256:], lse_ref),
+            "dq": orc.rel_max_err(dq[:, sl, rows - 256:], torch.matmul(ds, kf) * scale),
+            "dk": orc.rel_max_err(dk[:, h:h + 1, rows - 256:],
+                                  (torch.matmul(ds[..., r0:r1].transpose(-1, -2), qf) * scale).sum(1, keepdim=True)),
+            "dv": orc.rel_max_err(dv[:, h:h + 1, rows - 256:],
+                                  torch.matmul(p[..., r0:r1].transpose(-1, -2), gf).sum(1, keepdim=True))}
+    res["device_status"] = ext.device_status()
+    return res
+
+
+def run_sharded_legs(args, rank, world, local, dev, dist, ext, full_ms):
+    peaks = measured_peaks()
+    out = {}
+    for name, fn in (("units_split", lambda: leg_units_split(args, rank, world, dev, dist, ext, full_ms)),
+                     ("varlen_head_split", lambda: leg_varlen_split(args, rank, world, dev, dist, ext)),
+                     ("decode_batch_split", lambda: leg_decode_split(args, rank, world, dev, dist, ext, peaks)),
+                     ("long_context_ring", lambda: leg_ring(args, rank, world, local, dev, dist, ext))):
+        try:
+            out[name] = fn()
+        except RuntimeError as e:
+            # every rank must leave the leg: a failure on one rank is one on all (collectives inside)
+            out[name] = {"error": str(e)[:300]}
+        torch.cuda.empty_cache()
+    return out
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -481,16 +763,24 @@ def main():
                     help="long_context with more than one rank: how the sequence rows are dealt to the ranks")
     ap.add_argument("--shape", action="append", default=[],
                     help="--workload shape: pass:B,Hq,Hkv,Nq,Nk,d[:noncausal] with pass = fwd | bwd | chunk; repeatable")
+    ap.add_argument("--fwd-variant", type=int, default=0, choices=[0, 1, 2],
+                    help="--workload shape: forward kernel variant (0 = the library's own choice, 1 = one query tile "
+                         "per thread block, 2 = two tiles)")
     ap.add_argument("--decode-graph", action="store_true",
                     help="decode workload: replay one captured step as a CUDA graph instead of launching eagerly")
     ap.add_argument("--decode-batch", type=int, default=0,
                     help="decode workload on one rank: run this many of the 64 batch entries (what one of "
                          "64/N ranks holds), to see a shard's step without the other GPUs")
+    ap.add_argument("--kernel-source-hash", action="store_true",
+                    help="print the hash an ncu capture record of the backward kernel must carry, and exit")
     ap.add_argument("--decode-profile", action="store_true",
                     help="run only a small decode case (batch 16, a few steps): the case profilers capture")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
+    if args.kernel_source_hash:
+        print(kernel_source_hash())
+        return
     if args.impl == "reference":
         run_reference(args)
         return
@@ -511,6 +801,7 @@ def main():
         run_decode(args, rank, world, local, dist, ext)
         return
     if args.workload == "shape":
+        ext.set_forward_variant(args.fwd_variant)
         run_shapes(args, ext)
         return
 
@@ -648,15 +939,14 @@ def main():
     peak_tf = peaks["bf16_tflops"]
     roofline = None
     extra = {}
+    traffic, traffic_source = recorded_traffic()
     if bwd_n:
         bwd_kernel_ms = bwd_ms / bwd_n
         achieved = bwd_flops / (bwd_kernel_ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": "fal_bwd_kernel<128,causal>", "achieved": achieved,
                     "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
-                    # DRAM read + write bytes of one launch on this workload, from the ncu capture
-                    # summarised in profiles/bwd_kernel_config2.md (not re-measured here).
-                    "traffic": 1.088e9, "traffic_unit": "bytes per launch",
+                    "traffic": traffic, "traffic_unit": "bytes per launch", "traffic_source": traffic_source,
                     "kernel_ms": bwd_kernel_ms, "frac_of_nominal_2250": achieved / 2250.0}
     if fwd_n:
         fwd_kernel_ms = fwd_ms / fwd_n
@@ -664,6 +954,37 @@ def main():
         extra["fwd_kernel"] = {"kernel": "fal_fwd_kernel<128,causal>", "kernel_ms": fwd_kernel_ms,
                                "achieved_tflops": fa, "frac_of_measured_peak": fa / peak_tf,
                                "frac_of_nominal_2250": fa / 2250.0}
+
+    # ---------------- the same step for several seconds (clocks settle under the power cap) ----------
+    if world == 1 and not args.no_extras:
+        sampler = ClockSampler(local)
+        sampler.start()
+        time.sleep(0.3)
+        for _ in range(20):   # the reference's benchmark method: 20 warm-up iterations, then >= 100 timed
+            step()
+        torch.cuda.synchronize()
+        n_sus = max(100, int(math.ceil(3000.0 / ms_step)))
+        sampler.mark_begin()
+        e0.record()
+        for _ in range(n_sus):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        sampler.mark_end()
+        sus_ms = e0.elapsed_time(e1) / n_sus
+        time.sleep(0.1)
+        sus_clocks = sampler.stop()
+        sus_tf = (fwd_flops + bwd_flops) / (sus_ms * 1e-3) / 1e12
+        med, mx = sus_clocks.get("sm_mhz"), sus_clocks.get("sm_max_mhz")
+        extra["sustained"] = {
+            "steps": n_sus, "seconds": sus_ms * n_sus / 1e3, "ms_per_step": sus_ms, "tflops": sus_tf,
+            "sm_mhz_median": med, "sm_max_mhz": mx, "reasons": sus_clocks.get("reasons"),
+            "tflops_scaled_to_max_clock": sus_tf * mx / med if med and mx else None,
+            "frac_of_sustained_peak": sus_tf / peaks["bf16_tflops_sustained"] if peaks.get("bf16_tflops_sustained") else None,
+            "sustained_peak_tflops": peaks.get("bf16_tflops_sustained"),
+            "peak_source": f"{peaks['source']} cuBLAS bf16, seconds-long loop"}
+    if world > 1 and not args.no_extras:
+        extra["sharded"] = run_sharded_legs(args, rank, world, local, dev, dist, ext, ms_step)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_extras:

@@ -23,7 +23,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(LIB_DIR, "libfal_b200.so")
 
-SOURCES = ["fal_api.cu", "fal_fwd.cu", "fal_bwd.cu", "fal_decode.cu"]
+SOURCES = ["fal_api.cu", "fal_fwd.cu", "fal_bwd.cu", "fal_decode.cu", "fal_ring.cu", "fal_selftest.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -80,16 +81,22 @@ int make_tensor_map(CUtensorMap* map, const void* base, int head_dim, int64_t ro
   return FAL_OK;
 }
 
-// fp32 accumulator [batch, head, row, head_dim] (contiguous rows); box = 32 floats x 128 rows,
-// 128-byte swizzle: the shape of one dQ staging box of the backward kernel.
-int make_accum_tensor_map(CUtensorMap* map, const float* base, int head_dim, int64_t padded_rows,
-                          int64_t heads, int64_t batch) {
+// fp32 dQ accumulator addressed as [batch, head, row, head_dim] through strides in floats (rows of
+// head_dim contiguous floats); box = 32 floats x 128 rows, 128-byte swizzle: the shape of one dQ
+// staging box of the backward kernel.  `rows` is the extent reductions are clipped to.
+int make_accum_tensor_map(CUtensorMap* map, const float* base, int head_dim, int64_t rows, int64_t heads,
+                          int64_t batch, const fal::RowStrides& st) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return FAL_ERR_TENSOR_MAP;
-  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(padded_rows),
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return FAL_ERR_INVALID_ARGUMENT;
+  if ((rows > 1 && st.row <= 0) || (heads > 1 && st.head <= 0) || (batch > 1 && st.batch <= 0))
+    return FAL_ERR_INVALID_ARGUMENT;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows),
                               static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
-  const cuuint64_t row_bytes = static_cast<cuuint64_t>(head_dim) * 4u;
-  const cuuint64_t strides[3] = {row_bytes, row_bytes * padded_rows, row_bytes * padded_rows * heads};
+  auto fix = [&](int64_t s) -> cuuint64_t { return static_cast<cuuint64_t>(s > 0 ? s : head_dim) * 4u; };
+  const cuuint64_t strides[3] = {fix(st.row), fix(st.head), fix(st.batch)};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] % 16u != 0) return FAL_ERR_INVALID_ARGUMENT;
   const cuuint32_t box[4] = {32u, 128u, 1u, 1u};
   const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box,
@@ -132,8 +139,31 @@ int check_device() {
 
 // 64, 128 and 256 in every entry point (the head_dim-256 backward runs on column halves).
 bool head_dim_ok(int d) { return d == 64 || d == 128 || d == 256; }
-// Query rows per forward CTA (one 128-row tile at head_dim 256, two otherwise).
-int forward_cta_rows(int d) { return d == 256 ? 128 : 256; }
+// Number of SMs of the current device (cached per device; 0 if it cannot be read).
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  std::lock_guard<std::mutex> g(mu);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// Forward kernel variant.  Two 128-row tiles per CTA let one tile's softmax run under the other's
+// MMAs; when that grid would leave SMs without a CTA, one tile per CTA (both softmax warpgroups on
+// it, half the score columns each) doubles the number of CTAs and shortens each tile's softmax.
+std::atomic<int> g_fwd_variant{FAL_FWD_AUTO};  // fal_set_fwd_variant
+
+int forward_cta_rows(int head_dim, int64_t blocks_of_256_rows, int64_t units) {
+  const int forced = g_fwd_variant.load(std::memory_order_relaxed);
+  const bool one_tile = forced == FAL_FWD_ONE_TILE ||
+                        (forced == FAL_FWD_AUTO && blocks_of_256_rows * units < sm_count());
+  return fal::fwd_cta_rows(head_dim, one_tile);
+}
 
 int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
@@ -157,22 +187,19 @@ BwdWorkspace bwd_workspace_layout(int batch, int heads_q, int rows, int head_dim
 
 constexpr int kDecodeSplitLen = 1024;
 
-// Decode scratch layout: [partial O fp32 rows*d][partial (max, sum) fp32 rows*2][arrival counters int32
-// batch*heads_q], rows = batch*heads_q*splits.  The counters must be zero when a call starts; every
-// call leaves them zero.
+// Decode scratch layout: [partial O fp32 rows*d][partial (max, sum) fp32 rows*2], rows =
+// batch*heads_q*splits.  Nothing in it needs initialising.
 struct DecodeWorkspace {
   int64_t splits;
   size_t partial_bytes;
-  size_t counter_bytes;
-  size_t total() const { return partial_bytes + counter_bytes; }
+  size_t total() const { return partial_bytes; }
 };
 
 DecodeWorkspace decode_workspace_layout(int batch, int heads_q, int capacity, int head_dim) {
   DecodeWorkspace w;
   w.splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
   const int64_t rows = static_cast<int64_t>(batch) * heads_q * w.splits;
-  w.partial_bytes = static_cast<size_t>(round_up(rows * (head_dim + 2) * static_cast<int64_t>(sizeof(float)), 16));
-  w.counter_bytes = static_cast<size_t>(round_up(static_cast<int64_t>(batch) * heads_q * 4, 16));
+  w.partial_bytes = static_cast<size_t>(rows) * (head_dim + 2) * sizeof(float);
   return w;
 }
 
@@ -277,7 +304,8 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int cta_rows = forward_cta_rows(head_dim);
+  const int cta_rows = forward_cta_rows(head_dim, (seqlen_q + 255) / 256, static_cast<int64_t>(batch) * heads_q);
+  p.cta_rows = cta_rows;
   p.num_qblk = (seqlen_q + cta_rows - 1) / cta_rows;
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
@@ -338,7 +366,8 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The lengths stay on the device.  Every sequence rounds up to whole query blocks: at most one
   // extra block each.
-  p.num_qblk = total_q / forward_cta_rows(head_dim) + num_seqs;
+  p.cta_rows = forward_cta_rows(head_dim, total_q / 256 + num_seqs, heads_q);
+  p.num_qblk = total_q / p.cta_rows + num_seqs;
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
@@ -370,11 +399,18 @@ struct BwdCall {
   size_t workspace_bytes;
   int* status;
   cudaStream_t stream;
+  // Partial mode (fal_bwd_partial): dQ is ADDED into the caller's fp32 accumulator (never zeroed, no
+  // cast pass) and dK / dV leave as fp32; dq, dk, dv above are then unused.
+  float* dq_acc = nullptr;
+  float* dk_f32 = nullptr;
+  float* dv_f32 = nullptr;
+  fal::RowStrides s_dq_acc{};
 };
 
 int run_bwd(const BwdCall& c) {
-  if (!c.d_out || !c.q || !c.k || !c.v || !c.o || !c.lse || !c.dq || !c.dk || !c.dv || !c.workspace)
-    return FAL_ERR_INVALID_ARGUMENT;
+  const bool partial = c.dq_acc != nullptr;
+  if (!c.d_out || !c.q || !c.k || !c.v || !c.o || !c.lse || !c.workspace) return FAL_ERR_INVALID_ARGUMENT;
+  if (partial ? (!c.dk_f32 || !c.dv_f32) : (!c.dq || !c.dk || !c.dv)) return FAL_ERR_INVALID_ARGUMENT;
   if (c.batch <= 0 || c.heads_q <= 0 || c.heads_kv <= 0 || c.rows_q <= 0 || c.rows_k <= 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (c.heads_q % c.heads_kv != 0 || !(c.scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
@@ -385,25 +421,33 @@ int run_bwd(const BwdCall& c) {
     return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && s.row % 8 == 0 && s.head % 8 == 0 &&
            s.batch % 8 == 0;
   };
-  if (!out_ok(c.dq, c.s_dq) || !out_ok(c.dk, c.s_dk) || !out_ok(c.dv, c.s_dv) ||
-      !out_ok(c.o, c.s_o) || !out_ok(c.d_out, c.s_do))
+  if (partial) {
+    if (!out_ok(c.dk_f32, c.s_dk) || !out_ok(c.dv_f32, c.s_dv) || !out_ok(c.dq_acc, c.s_dq_acc) ||
+        c.s_dq_acc.row != c.head_dim)
+      return FAL_ERR_INVALID_ARGUMENT;
+  } else if (!out_ok(c.dq, c.s_dq) || !out_ok(c.dk, c.s_dk) || !out_ok(c.dv, c.s_dv)) {
     return FAL_ERR_INVALID_ARGUMENT;
+  }
+  if (!out_ok(c.o, c.s_o) || !out_ok(c.d_out, c.s_do)) return FAL_ERR_INVALID_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(c.workspace) & 255u) != 0) return FAL_ERR_INVALID_ARGUMENT;
-  const BwdWorkspace w = bwd_workspace_layout(c.batch, c.heads_q, c.rows_q, c.head_dim);
+  BwdWorkspace w = bwd_workspace_layout(c.batch, c.heads_q, c.rows_q, c.head_dim);
+  if (partial) w.dq_bytes = 0;  // the accumulator is the caller's; the workspace holds delta only
   if (c.workspace_bytes < w.total()) return FAL_ERR_WORKSPACE_TOO_SMALL;
   int rc = check_device();
   if (rc != FAL_OK) return rc;
 
-  float* dq_accum = static_cast<float*>(c.workspace);
+  float* dq_accum = partial ? c.dq_acc : static_cast<float*>(c.workspace);
   float* delta = reinterpret_cast<float*>(static_cast<char*>(c.workspace) + w.dq_bytes);
-  const int64_t acc_head = w.padded_rows * c.head_dim;
-  const int64_t acc_batch = acc_head * c.heads_q;
+  const int64_t acc_head = partial ? c.s_dq_acc.head : w.padded_rows * c.head_dim;
+  const int64_t acc_batch = partial ? c.s_dq_acc.batch : acc_head * c.heads_q;
+  const int64_t acc_rows = partial ? c.rows_q : w.padded_rows;
 
   CUtensorMap tq, tk, tv, tdo, tdq;
   if ((rc = make_tensor_map(&tq, c.q, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_q, 128))) return rc;
   if ((rc = make_tensor_map(&tdo, c.d_out, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_do, 128)))
     return rc;
-  if ((rc = make_accum_tensor_map(&tdq, dq_accum, c.head_dim, w.padded_rows, c.heads_q, c.batch)))
+  if ((rc = make_accum_tensor_map(&tdq, dq_accum, c.head_dim, acc_rows, c.heads_q, c.batch,
+                                  fal::RowStrides{acc_batch, acc_head, c.head_dim})))
     return rc;
   if ((rc = make_tensor_map(&tk, c.k, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_k, 128))) return rc;
   if ((rc = make_tensor_map(&tv, c.v, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_v, 128))) return rc;
@@ -416,7 +460,7 @@ int run_bwd(const BwdCall& c) {
   pp.delta = delta;
   pp.delta_head_stride = w.padded_rows;
   pp.delta_batch_stride = w.padded_rows * c.heads_q;
-  pp.dq_accum = dq_accum;
+  pp.dq_accum = partial ? nullptr : dq_accum;  // a caller-owned accumulator is continued, not cleared
   pp.dq_accum_head_stride = acc_head;
   pp.dq_accum_batch_stride = acc_batch;
   pp.batch = c.batch;
@@ -430,6 +474,8 @@ int run_bwd(const BwdCall& c) {
   fal::BwdParams p{};
   p.dk = c.dk;
   p.dv = c.dv;
+  p.dk_f32 = c.dk_f32;
+  p.dv_f32 = c.dv_f32;
   p.dk_strides = c.s_dk;
   p.dv_strides = c.s_dv;
   p.dq_accum = dq_accum;
@@ -459,6 +505,7 @@ int run_bwd(const BwdCall& c) {
                       c.stream);
   g_timer.end(FAL_KERNEL_BWD, rec, c.stream);
   if (e != cudaSuccess) return cuda_fail(e);
+  if (partial) return FAL_OK;  // the caller casts its accumulator once, after the last partial call
 
   fal::BwdPostParams po{};
   po.dq_accum = dq_accum;
@@ -536,6 +583,98 @@ int fal_bwd_varlen(const void* d_out, const void* q, const void* k, const void* 
   return run_bwd(c);
 }
 
+size_t fal_bwd_partial_workspace_bytes(int batch, int heads_q, int rows, int head_dim) {
+  if (batch <= 0 || heads_q <= 0 || rows <= 0 || head_dim <= 0) return 0;
+  return bwd_workspace_layout(batch, heads_q, rows, head_dim).delta_bytes;
+}
+
+int fal_bwd_partial(const void* d_out, const void* q, const void* k, const void* v, const void* o,
+                    const float* lse, float* dq_accum, float* dk_partial, float* dv_partial, int batch,
+                    int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
+                    const fal_strides* do_strides, const fal_strides* q_strides, const fal_strides* k_strides,
+                    const fal_strides* v_strides, const fal_strides* o_strides,
+                    const fal_strides* dq_accum_strides, const fal_strides* dk_strides,
+                    const fal_strides* dv_strides, const fal_strides* lse_strides, float softmax_scale,
+                    int is_causal, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+  if (!do_strides || !q_strides || !k_strides || !v_strides || !o_strides || !dq_accum_strides ||
+      !dk_strides || !dv_strides || !lse_strides || !dq_accum)
+    return FAL_ERR_INVALID_ARGUMENT;
+  BwdCall c{};
+  c.d_out = d_out; c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse;
+  c.dq = nullptr; c.dk = nullptr; c.dv = nullptr;
+  c.dq_acc = dq_accum; c.dk_f32 = dk_partial; c.dv_f32 = dv_partial;
+  c.cu_q = nullptr; c.cu_k = nullptr; c.num_seqs = 0;
+  c.batch = batch; c.heads_q = heads_q; c.heads_kv = heads_kv;
+  c.rows_q = seqlen_q; c.rows_k = seqlen_k; c.head_dim = head_dim;
+  c.s_do = to_rs(do_strides); c.s_q = to_rs(q_strides); c.s_k = to_rs(k_strides);
+  c.s_v = to_rs(v_strides); c.s_o = to_rs(o_strides); c.s_dq_acc = to_rs(dq_accum_strides);
+  c.s_dk = to_rs(dk_strides); c.s_dv = to_rs(dv_strides);
+  c.s_lse = to_rs(lse_strides);
+  c.scale = softmax_scale; c.causal = is_causal;
+  c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+  c.status = status; c.stream = static_cast<cudaStream_t>(stream);
+  return run_bwd(c);
+}
+
+namespace {
+bool elementwise_shape_ok(int batch, int heads, int rows, int head_dim) {
+  return batch > 0 && heads > 0 && rows > 0 && head_dim > 0 && head_dim % 8 == 0 && head_dim <= 256;
+}
+// 16-byte accesses of 8 fp16 / 4 fp32 elements: base and every stride must keep that alignment.
+bool vec_ok(const void* ptr, const fal_strides* s, int elem_bytes) {
+  const int64_t per16 = 16 / elem_bytes;
+  return ptr != nullptr && s != nullptr && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 &&
+         s->row % per16 == 0 && s->head % per16 == 0 && s->batch % per16 == 0;
+}
+}  // namespace
+
+int fal_merge_partial(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int batch,
+                      int heads, int rows, int head_dim, const fal_strides* o_acc_strides,
+                      const fal_strides* lse_acc_strides, const fal_strides* o_part_strides,
+                      const fal_strides* lse_part_strides, int init, void* stream) {
+  if (!elementwise_shape_ok(batch, heads, rows, head_dim) || !lse_acc || !lse_part || !lse_acc_strides ||
+      !lse_part_strides || !vec_ok(o_acc, o_acc_strides, 4) || !vec_ok(o_part, o_part_strides, 2))
+    return FAL_ERR_INVALID_ARGUMENT;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+  fal::MergeParams p{};
+  p.o_acc = o_acc; p.lse_acc = lse_acc; p.o_part = o_part; p.lse_part = lse_part;
+  p.o_acc_strides = to_rs(o_acc_strides); p.lse_acc_strides = to_rs(lse_acc_strides);
+  p.o_part_strides = to_rs(o_part_strides); p.lse_part_strides = to_rs(lse_part_strides);
+  p.batch = batch; p.heads = heads; p.rows = rows; p.head_dim = head_dim; p.init = init != 0;
+  cudaError_t e = fal::launch_merge_partial(p, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+int fal_accumulate_f32(float* dst, const float* src, int batch, int heads, int rows, int head_dim,
+                       const fal_strides* dst_strides, const fal_strides* src_strides, void* stream) {
+  if (!elementwise_shape_ok(batch, heads, rows, head_dim) || !vec_ok(dst, dst_strides, 4) ||
+      !vec_ok(src, src_strides, 4))
+    return FAL_ERR_INVALID_ARGUMENT;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+  fal::AccumulateParams p{};
+  p.dst = dst; p.src = src; p.dst_strides = to_rs(dst_strides); p.src_strides = to_rs(src_strides);
+  p.batch = batch; p.heads = heads; p.rows = rows; p.head_dim = head_dim;
+  cudaError_t e = fal::launch_accumulate(p, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+int fal_scale_cast_f16(void* dst, const float* src, int batch, int heads, int rows, int head_dim,
+                       const fal_strides* dst_strides, const fal_strides* src_strides, float scale,
+                       void* stream) {
+  if (!elementwise_shape_ok(batch, heads, rows, head_dim) || !vec_ok(dst, dst_strides, 2) ||
+      !vec_ok(src, src_strides, 4))
+    return FAL_ERR_INVALID_ARGUMENT;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+  fal::ScaleCastParams p{};
+  p.dst = dst; p.src = src; p.dst_strides = to_rs(dst_strides); p.src_strides = to_rs(src_strides);
+  p.batch = batch; p.heads = heads; p.rows = rows; p.head_dim = head_dim; p.scale = scale;
+  cudaError_t e = fal::launch_scale_cast(p, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
 size_t fal_decode_workspace_bytes(int batch, int heads_q, int capacity, int head_dim) {
   if (batch <= 0 || heads_q <= 0 || capacity <= 0 || head_dim <= 0) return 0;
   return decode_workspace_layout(batch, heads_q, capacity, head_dim).total();
@@ -602,11 +741,12 @@ int decode_with_workspace(const void* q, void* k_cache, void* v_cache, const fal
   p.status = status;
   p.part_o = static_cast<float*>(workspace);
   p.part_ml = p.part_o + static_cast<int64_t>(batch) * heads_q * p.splits * head_dim;
-  p.arrivals = reinterpret_cast<int*>(static_cast<char*>(workspace) + w.partial_bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int rec = g_timer.begin(FAL_KERNEL_DECODE_SPLITK, st);
-  cudaError_t e = fal::launch_decode(p, st);
+  cudaError_t e = fal::launch_decode_splitk(p, st);
   g_timer.end(FAL_KERNEL_DECODE_SPLITK, rec, st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = fal::launch_decode_combine(p, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
 }  // namespace
@@ -640,8 +780,7 @@ int fal_decode_static(const void* q, void* k_cache, void* v_cache, const fal_str
   int rc = decode_check_args(q, k_cache, v_cache, k_strides, v_strides, cache_seqlens, k_new, v_new, o, batch,
                              heads_q, heads_kv, capacity, head_dim, softmax_scale);
   if (rc != FAL_OK) return rc;
-  // The scratch of this problem (partials + arrival counters) must fit the fixed array; nothing is
-  // launched otherwise.
+  // The partials of this problem must fit the fixed array; nothing is launched otherwise.
   if (fal_decode_workspace_bytes(batch, heads_q, capacity, head_dim) > fal::kDecodeStaticScratchBytes)
     return FAL_ERR_STATIC_SCRATCH_EXCEEDED;
   rc = check_device();
@@ -652,6 +791,20 @@ int fal_decode_static(const void* q, void* k_cache, void* v_cache, const fal_str
   return decode_with_workspace(q, k_cache, v_cache, k_strides, v_strides, nullptr, cache_seqlens, k_new, v_new,
                                o, lse, batch, heads_q, heads_kv, capacity, head_dim, softmax_scale, scratch,
                                fal::kDecodeStaticScratchBytes, status, stream);
+}
+
+int fal_set_fwd_variant(int variant) {
+  if (variant < FAL_FWD_AUTO || variant > FAL_FWD_TWO_TILES) return FAL_ERR_INVALID_ARGUMENT;
+  g_fwd_variant.store(variant, std::memory_order_relaxed);
+  return FAL_OK;
+}
+
+int fal_selftest_wait_timeout(int barrier_id, int* status, int* waits_given_up, void* stream) {
+  if (!status || barrier_id < 0 || barrier_id >= 1000) return FAL_ERR_INVALID_ARGUMENT;
+  int rc = check_device();
+  if (rc != FAL_OK) return rc;
+  cudaError_t e = fal::launch_selftest_wait(barrier_id, status, waits_given_up, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
 
 int fal_profile_enable(int on) {

@@ -135,20 +135,36 @@ __device__ __forceinline__ bool bwd_decode_work(const BwdParams& p, int idx, Bwd
   const int slot = idx / p.heads_kv;
   w.kv_head = idx % p.heads_kv;
   w.batch = 0;
+  // Which sequence owns key block `slot`: every warp scans the lengths 32 sequences at a time (one
+  // coalesced load, a prefix sum of the block counts, a vote) instead of walking them one by one.
+  const int lane = threadIdx.x & 31;
   int first = 0;
-  for (int s = 0; s < p.num_seqs; ++s) {
-    const int a = __ldg(p.cu_k + s);
-    const int e = __ldg(p.cu_k + s + 1);
+  for (int base = 0; base < p.num_seqs; base += 32) {
+    const int s = base + lane;
+    int a = 0, e = 0;
+    if (s < p.num_seqs) {
+      a = __ldg(p.cu_k + s);
+      e = __ldg(p.cu_k + s + 1);
+    }
     const int nblk = (e - a + kKvTile - 1) / kKvTile;
-    if (slot < first + nblk) {
-      w.kvblk = slot - first;
-      w.k_row0 = a;
-      w.seqlen_k = e - a;
-      w.q_row0 = __ldg(p.cu_q + s);
-      w.seqlen_q = __ldg(p.cu_q + s + 1) - w.q_row0;
+    int incl = nblk;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    const int excl = first + incl - nblk;
+    const unsigned hit = __ballot_sync(0xffffffffu, slot >= excl && slot < excl + nblk);
+    if (hit != 0u) {
+      const int src = __ffs(hit) - 1;
+      w.kvblk = slot - __shfl_sync(0xffffffffu, excl, src);
+      w.k_row0 = __shfl_sync(0xffffffffu, a, src);
+      w.seqlen_k = __shfl_sync(0xffffffffu, e, src) - w.k_row0;
+      w.q_row0 = __ldg(p.cu_q + base + src);
+      w.seqlen_q = __ldg(p.cu_q + base + src + 1) - w.q_row0;
       return true;
     }
-    first += nblk;
+    first += __shfl_sync(0xffffffffu, incl, 31);
   }
   return false;
 }
@@ -614,9 +630,10 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     const bool is_dk = half == 1;
     const RowStrides& st_o = is_dk ? p.dk_strides : p.dv_strides;
-    __half* out_row = static_cast<__half*>(is_dk ? p.dk : p.dv) + wk.batch * st_o.batch +
-                      wk.kv_head * st_o.head +
-                      (static_cast<int64_t>(wk.k_row0) + kv_local) * st_o.row + col_own;
+    const int64_t out_off = wk.batch * st_o.batch + wk.kv_head * st_o.head +
+                            (static_cast<int64_t>(wk.k_row0) + kv_local) * st_o.row + col_own;
+    __half* out_row = static_cast<__half*>(is_dk ? p.dk : p.dv) + out_off;
+    float* out_row32 = p.dk_f32 != nullptr ? (is_dk ? p.dk_f32 : p.dv_f32) + out_off : nullptr;
     const float mul = is_dk ? p.scale : 1.f;
     const uint32_t t_acc = tmem_base + lane_addr + (is_dk ? kColDk : kColDv);
 #pragma unroll
@@ -629,7 +646,14 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = 0u;
       }
-      if (kv_ok) {
+      if (kv_ok && out_row32 != nullptr) {
+        // unrounded partial for a caller that sums the key shard's gradient over several calls
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          *reinterpret_cast<float4*>(out_row32 + c * 32 + v * 4) =
+              make_float4(__uint_as_float(r[v * 4 + 0]) * mul, __uint_as_float(r[v * 4 + 1]) * mul,
+                          __uint_as_float(r[v * 4 + 2]) * mul, __uint_as_float(r[v * 4 + 3]) * mul);
+      } else if (kv_ok) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           uint4 out;
@@ -740,7 +764,7 @@ __global__ void __launch_bounds__(256) fal_bwd_prep_kernel(const BwdPrepParams p
   // The fp32 dQ accumulator must start at zero (the main kernel only ever adds to it): this thread
   // clears the 8 columns of the row it has just read from O and dO.  Rows between p.rows and the
   // padded row count may be added into by partial tiles but are never read, so they stay as they are.
-  if (ok) {
+  if (ok && p.dq_accum != nullptr) {  // (a caller-owned accumulator that is being continued is left alone)
     float4* acc_row = reinterpret_cast<float4*>(p.dq_accum + b * p.dq_accum_batch_stride +
                                                 h * p.dq_accum_head_stride + static_cast<int64_t>(r) * D + sub * 8);
     acc_row[0] = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -32,7 +32,8 @@ struct FwdParams {
   int heads_kv;
   int seqlen_q;   // batched mode only
   int seqlen_k;   // batched mode only
-  int num_qblk;   // batched: ceil(seqlen_q / 256); packed: bound on all sequences' blocks
+  int cta_rows;   // query rows per CTA: 256 (two tiles) or 128 (one tile, both softmax warpgroups on it)
+  int num_qblk;   // batched: ceil(seqlen_q / cta_rows); packed: bound on all sequences' blocks
   int causal_shift;  // causal kernels: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
   float scale;       // softmax scale
   float scale_log2;  // softmax scale * log2(e)
@@ -43,6 +44,8 @@ struct BwdParams {
   // outputs
   void* dk;  // fp16
   void* dv;  // fp16
+  float* dk_f32;  // when set, dK and dV leave as unrounded fp32 here instead (same strides, in floats)
+  float* dv_f32;
   RowStrides dk_strides;
   RowStrides dv_strides;
   float* dq_accum;  // fp32 [batch, heads_q, padded_q_rows, head_dim] (packed: [heads_q, padded_total, head_dim])

@@ -1,5 +1,5 @@
-// Single-token decode against an fp16 KV cache: ONE launch that appends the new
-// token's K/V row, streams the cache split-K and merges the splits (log-sum-exp).
+// Single-token decode against an fp16 KV cache: a split-K streaming kernel (which
+// also appends the new token's K/V row) followed by a log-sum-exp combine.
 //
 // Stands in for the eager matmul -> softmax -> matmul fallback that the
 // reference's attention hook uses whenever q_len != kv_len
@@ -20,10 +20,13 @@
 //     free for the loads;
 //   - the CTA whose split holds the position the new token goes to writes that
 //     row into the cache before it starts streaming (no separate append launch);
-//   - each split writes an unnormalised fp32 partial (O, max, sum) and then counts
-//     itself in on a per-(entry, head group) arrival counter; the CTA that arrives
-//     last merges the splits the sequence length actually reaches and puts the
-//     counter back to zero (no separate combine launch, no CTA waits for another).
+//   - each split writes an unnormalised fp32 partial (O, max, sum); the combine
+//     kernel merges the splits that the sequence length actually reaches.  (Letting
+//     the last split of an entry to finish do the merge instead -- an arrival
+//     counter per entry, one launch in all -- was built and measured: every CTA then
+//     ends with a fence and an atomic round trip to L2, which cost more than the
+//     second launch saves, 84 against 80 us per step on an 8-entry batch replayed as
+//     a CUDA graph and 0.797 against 0.787 ms at batch 64.)
 // An optional first position per batch entry (cache_starts) skips a padded prefix
 // of the cache: the entry's row pointers start there and its length shrinks.
 #include "fal_common.h"
@@ -78,6 +81,26 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // ---------------------------------------------------------------------------
 // Append + split-K pass + merge by the last CTA to arrive.
 // ---------------------------------------------------------------------------
+// The keys entry b attends to: [start, start + len) of its cache, the appended token included when
+// there is one and it fits.  `can_append`: a new token is given and position len_old is inside the
+// cache.  A cache that is already full (or a negative length) cannot take the token: it is then
+// neither stored nor attended to, and the status word says so.
+struct DecodeRange {
+  int len_old;
+  int start;
+  int len;
+  bool can_append;
+};
+__device__ __forceinline__ DecodeRange decode_range(const DecodeParams& p, int b) {
+  DecodeRange r;
+  r.len_old = __ldg(p.cache_seqlens + b);
+  r.can_append = p.k_new != nullptr && r.len_old >= 0 && r.len_old < p.capacity;
+  int len = min(max(r.len_old + (r.can_append ? 1 : 0), 0), p.capacity);
+  r.start = p.cache_starts ? min(max(__ldg(p.cache_starts + b), 0), len) : 0;
+  r.len = len - r.start;
+  return r;
+}
+
 template <int D>
 struct DecSmem {
   static constexpr int kRowBytes = D * 2;
@@ -108,18 +131,11 @@ fal_decode_splitk_kernel(const DecodeParams p) {
   const int split = blockIdx.y;
   const int b = blockIdx.z;
 
-  const int len_old = __ldg(p.cache_seqlens + b);
-  const bool append = p.k_new != nullptr;
-  // The new token goes to position len_old.  A cache that is already full (or a negative length)
-  // cannot take it: the token is then neither stored nor attended to, and the status word says so.
-  const bool can_append = append && len_old >= 0 && len_old < p.capacity;
-  if (append && !can_append && split == 0 && threadIdx.x == 0 && p.status)
+  const DecodeRange rg = decode_range(p, b);
+  const int len_old = rg.len_old, start = rg.start, len = rg.len;
+  const bool can_append = rg.can_append;
+  if (p.k_new != nullptr && !can_append && split == 0 && blockIdx.x == 0 && threadIdx.x == 0 && p.status)
     atomicCAS(p.status, 0, kDevAppendOverflow);
-  int len = min(max(len_old + (can_append ? 1 : 0), 0), p.capacity);
-  // With a first attended position the entry's keys are [start, len): positions below are counted
-  // from `start` (the row pointers are moved there).
-  const int start = p.cache_starts ? min(max(__ldg(p.cache_starts + b), 0), len) : 0;
-  len -= start;
   const int pos0 = split * p.split_len;
 
   const int rows_valid = min(16, group - head_chunk * 16);
@@ -144,17 +160,6 @@ fal_decode_splitk_kernel(const DecodeParams p) {
       __threadfence();   // the row is read back through L2 by this CTA's asynchronous copies
       __syncthreads();
     }
-  }
-  if (len <= 0) {
-    // nothing to attend to: zeros and LSE = -inf, written by the entry's first split
-    if (split == 0) {
-      for (int idx = threadIdx.x; idx < rows_valid * D; idx += kDecThreads)
-        static_cast<__half*>(p.o)[(static_cast<int64_t>(b) * p.heads_q + hq0 + idx / D) * D + idx % D] =
-            __float2half_rn(0.f);
-      if (p.lse != nullptr && threadIdx.x < rows_valid)
-        p.lse[static_cast<int64_t>(b) * p.heads_q + hq0 + threadIdx.x] = kNegInfD;
-    }
-    return;
   }
   if (pos0 >= len) return;  // this split lies beyond the sequence
   const int pos_end = min(pos0 + p.split_len, len);
@@ -347,41 +352,33 @@ fal_decode_splitk_kernel(const DecodeParams p) {
     }
   }
 
-  // ---- arrival: the last of this (entry, head group)'s active splits merges them ---------------
-  // Every active split counts itself in after its partial is visible device-wide; nobody waits.
-  // The counter goes back to zero for the next call (it must be zero when a call starts).
-  __shared__ int s_is_last;
-  const int n_active = (len + p.split_len - 1) / p.split_len;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int* ctr = p.arrivals + static_cast<int64_t>(b) * p.heads_q + blockIdx.x;
-    const int seen = atomicAdd(ctr, 1);
-    s_is_last = (seen == n_active - 1) ? 1 : 0;
-    if (s_is_last) atomicExch(ctr, 0);
-  }
-  __syncthreads();
-  if (!s_is_last) return;
-  __threadfence();
+}
 
-  for (int idx = threadIdx.x; idx < rows_valid * D; idx += kDecThreads) {
-    const int r = idx / D;
-    const int c = idx % D;
-    const int64_t bh = static_cast<int64_t>(b) * p.heads_q + hq0 + r;
-    const float* ml = p.part_ml + bh * p.splits * 2;
-    const float* po = p.part_o + bh * p.splits * D;
-    float mmax = kNegInfD;
-    for (int i = 0; i < n_active; ++i) mmax = fmaxf(mmax, __ldcg(ml + 2 * i));
-    const float muse = (mmax == kNegInfD) ? 0.f : mmax;
-    float lsum = 0.f;
-    for (int i = 0; i < n_active; ++i) lsum += fast_exp2(__ldcg(ml + 2 * i) - muse) * __ldcg(ml + 2 * i + 1);
-    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+// ---------------------------------------------------------------------------
+// Combine: merge the splits a sequence actually reaches.
+// ---------------------------------------------------------------------------
+__global__ void fal_decode_combine_kernel(const DecodeParams p) {
+  const int bh = blockIdx.x;
+  const int b = bh / p.heads_q;
+  const int D = p.head_dim;
+  const int len = decode_range(p, b).len;
+  const int n = (len + p.split_len - 1) / p.split_len;
+  const float* ml = p.part_ml + static_cast<int64_t>(bh) * p.splits * 2;
+  const float* po = p.part_o + static_cast<int64_t>(bh) * p.splits * D;
+
+  float mmax = kNegInfD;
+  for (int i = 0; i < n; ++i) mmax = fmaxf(mmax, ml[2 * i]);
+  const float muse = (mmax == kNegInfD) ? 0.f : mmax;
+  float lsum = 0.f;
+  for (int i = 0; i < n; ++i) lsum += fast_exp2(ml[2 * i] - muse) * ml[2 * i + 1];
+  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float o = 0.f;
-    for (int i = 0; i < n_active; ++i)
-      o += fast_exp2(__ldcg(ml + 2 * i) - muse) * __ldcg(po + static_cast<int64_t>(i) * D + c);
-    static_cast<__half*>(p.o)[bh * D + c] = __float2half_rn(o * inv);
-    if (c == 0 && p.lse != nullptr)
-      p.lse[bh] = (lsum > 0.f) ? (mmax + log2f(lsum)) * 0.6931471805599453f : kNegInfD;
+    for (int i = 0; i < n; ++i) o += fast_exp2(ml[2 * i] - muse) * po[static_cast<int64_t>(i) * D + c];
+    static_cast<__half*>(p.o)[static_cast<int64_t>(bh) * D + c] = __float2half_rn(o * inv);
+  }
+  if (p.lse != nullptr && threadIdx.x == 0) {
+    p.lse[bh] = (lsum > 0.f) ? (mmax + log2f(lsum)) * 0.6931471805599453f : kNegInfD;
   }
 }
 
@@ -404,10 +401,9 @@ cudaError_t launch_splitk_t(const DecodeParams& p, cudaStream_t stream) {
 }  // namespace
 
 // ---------------------------------------------------------------------------
-// Fixed scratch for fal_decode_static: split-K partials and arrival counters for
-// callers that cannot allocate device memory.  It lives in the library image, so
-// every GPU that loads the library carries these bytes until the process exits;
-// it is zero-initialised at load, which is what the arrival counters need.
+// Fixed scratch for fal_decode_static: split-K partials for callers that cannot
+// allocate device memory.  It lives in the library image, so every GPU that
+// loads the library carries these bytes until the process exits.
 // ---------------------------------------------------------------------------
 namespace {
 static __device__ __align__(256) float g_decode_static_scratch[kDecodeStaticScratchBytes / sizeof(float)];
@@ -433,7 +429,12 @@ cudaError_t decode_static_scratch(float** ptr) {
   return cudaSuccess;
 }
 
-cudaError_t launch_decode(const DecodeParams& p, cudaStream_t stream) {
+cudaError_t launch_decode_combine(const DecodeParams& p, cudaStream_t stream) {
+  fal_decode_combine_kernel<<<p.batch * p.heads_q, p.head_dim, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_decode_splitk(const DecodeParams& p, cudaStream_t stream) {
   if (p.head_dim == 128) return launch_splitk_t<128>(p, stream);
   if (p.head_dim == 64) return launch_splitk_t<64>(p, stream);
   if (p.head_dim == 256) return launch_splitk_t<256>(p, stream);

@@ -35,7 +35,17 @@ namespace fal {
 
 namespace {
 
-constexpr int kFwdThreads = 384;  // three warpgroups: softmax 0, softmax 1, {producer, issuer, 2 idle}
+// Kernel variants (ONE_TILE):
+//   false  two query tiles per CTA, one softmax warpgroup per tile (a thread owns a 128-column row)
+//   true   one query tile per CTA, both softmax warpgroups on it (a thread owns 64 columns of a row)
+// Three warpgroups either way: softmax 0, softmax 1, {TMA producer, MMA issuer, 2 idle warps}.
+// (Two tiles with two softmax warpgroups EACH -- 640 threads, 104 registers per softmax thread -- was
+// built and measured on B4 Hq32 Hkv8 N4096 d128 causal: 583 against 515 us.  ncu: tensor pipe 45.7 %
+// against 54.3 %, long-scoreboard stalls per issue 4.9 against 2.5, MIO throttle 1.0 against 0.1: the
+// register cut spills inside the exponential loop and five warps per scheduler crowd the one
+// MMA-issuing thread.  It is not part of the library.)
+constexpr int kFwdThreads = 384;
+constexpr int kSmWarps = 8;  // softmax warps; then producer, issuer, 2 idle
 constexpr int kTileM = 128;   // query rows per softmax warpgroup
 constexpr int kTileN = 128;   // keys per step
 constexpr float kNegInf = -INFINITY;
@@ -86,8 +96,6 @@ constexpr int kRegsSoftmax = FAL_FWD_REGS_SOFTMAX;
 constexpr int kRegsOther = FAL_FWD_REGS_OTHER;
 static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 168 * 384,
               "setmaxnreg split exceeds the registers the CTA was launched with");
-static_assert(kRegsSoftmax % 8 == 0 && kRegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
-
 // Barrier ids (only used to label a wait that gave up).
 enum FwdBarrier : int {
   kBarQFull = 0,
@@ -100,11 +108,14 @@ enum FwdBarrier : int {
   kBarODone = 70,
 };
 
-template <int D>
+template <int D, bool ONE_TILE>
 struct FwdSmem {
-  // head_dim 256: one 128-row query tile per CTA (its O accumulator alone takes 256 of the 512 TMEM
-  // columns) and single K and V buffers (a 128 x 256 tile is 64 KB); the second softmax warpgroup idles.
-  static constexpr int kQTiles = (D == 256) ? 1 : 2;
+  // One 128-row query tile per CTA: always at head_dim 256 (its O accumulator alone takes 256 of the
+  // 512 TMEM columns; single K and V buffers, a 128 x 256 tile is 64 KB), and at head_dim 64 / 128
+  // when two-tile CTAs would leave SMs without work.  Both softmax warpgroups then share the one
+  // tile, 64 score columns each.
+  static_assert(ONE_TILE || D != 256, "head_dim 256 runs one query tile per CTA");
+  static constexpr int kQTiles = ONE_TILE ? 1 : 2;
   static constexpr int kCtaRows = kQTiles * kTileM;
   static constexpr int kStages = (D == 256) ? 1 : (D == 128) ? 2 : 4;
   static constexpr int kBoxes = D / 64;                 // 64-element (128-byte) column boxes
@@ -118,7 +129,11 @@ struct FwdSmem {
   //           p_half[2]
   static constexpr int kNumBars = 2 + 4 * kStages + 8;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
-  static constexpr int kBytes = kMiscOff + 16;
+  // split-column softmax: row maxima (two buffers) and row sums the two column halves of a row exchange
+  static constexpr int kXchOff = kMiscOff + 16;
+  static constexpr int kXchTileBytes = 3 * 2 * kTileM * 4;
+  static constexpr int kXchBytes = ONE_TILE ? kXchTileBytes : 0;
+  static constexpr int kBytes = kXchOff + kXchBytes;
   static constexpr int kAllocBytes = kBytes + 1024;  // room to align the base to 1024
 };
 
@@ -156,20 +171,38 @@ __device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, int cta_rows
     const int slot = idx / p.heads_q;
     w.head = idx % p.heads_q;
     w.batch = 0;
+    // Which sequence owns block `slot`: every warp scans the lengths 32 sequences at a time (one
+    // coalesced load, a prefix sum of the block counts, a vote) instead of walking them one by one.
+    const int lane = threadIdx.x & 31;
     int first = 0;
     int seq = -1;
     int q_start = 0;
-    for (int s = 0; s < p.num_seqs; ++s) {
-      const int a = __ldg(p.cu_q + s);
-      const int e = __ldg(p.cu_q + s + 1);
-      const int nblk = (e - a + cta_rows - 1) / cta_rows;
-      if (slot < first + nblk) {
-        seq = s;
-        q_start = a;
-        w.seqlen_q = e - a;
-        break;
+    w.seqlen_q = 0;
+    for (int base = 0; base < p.num_seqs && seq < 0; base += 32) {
+      const int s = base + lane;
+      int a = 0, e = 0;
+      if (s < p.num_seqs) {
+        a = __ldg(p.cu_q + s);
+        e = __ldg(p.cu_q + s + 1);
       }
-      first += nblk;
+      const int nblk = (e - a + cta_rows - 1) / cta_rows;
+      int incl = nblk;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+      }
+      const int excl = first + incl - nblk;
+      const unsigned hit = __ballot_sync(0xffffffffu, slot >= excl && slot < excl + nblk);
+      if (hit != 0u) {
+        const int src = __ffs(hit) - 1;
+        seq = base + src;
+        q_start = __shfl_sync(0xffffffffu, a, src);
+        w.seqlen_q = __shfl_sync(0xffffffffu, e, src) - q_start;
+        first = __shfl_sync(0xffffffffu, excl, src);
+      } else {
+        first += __shfl_sync(0xffffffffu, incl, 31);
+      }
     }
     if (seq < 0) return false;
     w.qblk = slot - first;
@@ -185,11 +218,11 @@ __device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, int cta_rows
 
 // SHIFTED (causal only): the mask's diagonal is moved by p.causal_shift keys (bottom-right
 // alignment); the kernels of the reference's own top-left mask are compiled without it.
-template <int D, bool CAUSAL, bool SHIFTED>
+template <int D, bool CAUSAL, bool SHIFTED, bool ONE_TILE>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
-  using L = FwdSmem<D>;
+  using L = FwdSmem<D, ONE_TILE>;
   constexpr int NS = L::kStages;
 
   FwdWork wk;
@@ -250,7 +283,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tma_load_4d(sbase + L::kVOff + s * L::kTileBytes + bx * L::kBoxBytes, &tm_v, bar(iVFull + s),
                   bx * 64, wk.k_row0 + j * kTileN, wk.kv_head, wk.batch);
   };
-  if (threadIdx.x == 8 * 32) {
+  if (threadIdx.x == kSmWarps * 32) {
     *abort_flag = 0;
     mbar_init(bar(iQFull + 0), 1);
     mbar_init(bar(iQFull + 1), 1);
@@ -277,7 +310,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       load_v(0);
     }
   }
-  if (warp == 9) {
+  if (warp == kSmWarps + 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
     tmem_relinquish();
   }
@@ -288,9 +321,9 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   // Register rebalancing between warpgroups (first statement of every role): the softmax warps
   // keep a whole 128-wide score row in registers, the producer / issuer warpgroup needs few.
-  if (warp >= 8) {
+  if (warp >= kSmWarps) {
     setmaxnreg_dec<kRegsOther>();
-    if (warp == 8) {
+    if (warp == kSmWarps) {
     // ===================== TMA producer =====================================
     if (lane == 0) {
       for (int j = 1; j < n_max; ++j) {  // tile 0 went out during setup
@@ -303,7 +336,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
     __syncwarp();
-  } else if (warp == 9) {
+  } else if (warp == kSmWarps + 1) {
     // ===================== MMA issuer =======================================
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(kTileM, kTileN, 0, 0);
@@ -380,6 +413,191 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else {
     // ===================== softmax + output =================================
     setmaxnreg_inc<kRegsSoftmax>();
+    if constexpr (ONE_TILE) {
+      // Two warps per TMEM lane quarter of the tile: one for score columns [0, 64) (column half 0), one
+      // for [64, 128), on the same 32 rows.  They exchange the row maxima of every step through
+      // shared memory (two buffers, one 64-thread named barrier per quarter), so both hold
+      // the same reference maximum and take the same rescale decision; the row sums are added once,
+      // in the epilogue.  The first 64 keys of P are column half 0's work (p_half), the rest half 1's
+      // (p_ready).  A thread keeps 32 scores in registers at a time; the other 32 are read again from
+      // tensor memory under the first 32 exponentials.
+      const int ch = (warp >> 2) & 1;
+      const int quarter = warp & 3;
+      const int row = quarter * 32 + lane;
+      const int q_tile0 = wk.qblk * kCtaRows;
+      const int q_local = q_tile0 + row;
+      const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+      const uint32_t tS = tmem_base + lane_addr;
+      const uint32_t tO = tmem_base + lane_addr + 256;
+      const int nt = ntile[0];
+      const float c2 = p.scale_log2;
+      float* xch = reinterpret_cast<float*>(sgen + L::kXchOff);  // [3][2 halves][128 rows]
+      const int pair_bar = 1 + quarter;
+      auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+      const int iS = iSReady, iPH = iPHalf, iPR = iPReady, iOD = iODone;
+
+      float m_ref = kNegInf;
+      float l = 0.f;
+      for (int j = 0; j < nt; ++j) {
+        mbar_wait(bar(iS), j & 1, wctx, kBarSReady);
+        tc_fence_after_sync();
+        const int kv0 = j * kTileN;
+        int limit = wk.seqlen_k - kv0;  // columns c < limit of the tile are visible
+        const int cshift = SHIFTED ? p.causal_shift : 0;
+        if (CAUSAL) limit = min(limit, q_local + cshift - kv0 + 1);
+        limit -= ch * 64;  // in this thread's own 64 columns
+        const bool tile_mask =
+            (kv0 + kTileN > wk.seqlen_k) || (CAUSAL && (kv0 + kTileN - 1 > q_tile0 + cshift));
+
+        // Row maximum over this thread's 64 columns; chunk 1 stays in registers, chunk 0 is read again below.
+        uint32_t s1[32];
+        float mx;
+        {
+          uint32_t s0[32];
+          tmem_ld_32x32b_x32(tS + ch * 64, s0);
+          tmem_ld_32x32b_x32(tS + ch * 64 + 32, s1);
+          tmem_wait_ld();
+          if (tile_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i >= limit) s0[i] = __float_as_uint(kNegInf);
+              if (32 + i >= limit) s1[i] = __float_as_uint(kNegInf);
+            }
+          }
+          float part[4];
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            const int b0 = hlf * 16;
+            float a = fmax3(__uint_as_float(s0[b0]), __uint_as_float(s0[b0 + 1]), __uint_as_float(s0[b0 + 2]));
+            float b = fmax3(__uint_as_float(s1[b0]), __uint_as_float(s1[b0 + 1]), __uint_as_float(s1[b0 + 2]));
+#pragma unroll
+            for (int i = 3; i + 1 < 16; i += 2) {
+              a = fmax3(a, __uint_as_float(s0[b0 + i]), __uint_as_float(s0[b0 + i + 1]));
+              b = fmax3(b, __uint_as_float(s1[b0 + i]), __uint_as_float(s1[b0 + i + 1]));
+            }
+            part[hlf] = fmaxf(a, __uint_as_float(s0[b0 + 15]));
+            part[2 + hlf] = fmaxf(b, __uint_as_float(s1[b0 + 15]));
+          }
+          mx = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+        }
+        float* xm = xch + (j & 1) * 2 * kTileM;
+        xm[ch * kTileM + row] = mx;
+        pair_sync();
+        mx = fmaxf(mx, xm[(ch ^ 1) * kTileM + row]);
+        const float m_new = fmaxf(m_ref, mx);
+
+        if (j == 0) {
+          m_ref = m_new;
+        } else {
+          const bool need = (m_new - m_ref) * c2 > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            // PV of the previous step must have landed before O is touched; each half rescales
+            // its own D/2 output columns.
+            mbar_wait(bar(iOD), (j - 1) & 1, wctx, kBarODone);
+            tc_fence_after_sync();
+            const float alpha = (m_new == kNegInf) ? 1.f : fast_exp2((m_ref - m_new) * c2);
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(tO + ch * (D / 2) + c * 32, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32b_x32(tO + ch * (D / 2) + c * 32, r);
+            }
+            l *= alpha;
+            m_ref = m_new;
+          }
+        }
+        const float moff = (m_ref == kNegInf) ? 0.f : m_ref * c2;
+
+        const uint64_t c2p = pack_f32x2(c2, c2);
+        const uint64_t moffp = pack_f32x2(-moff, -moff);
+        uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+        // 32 scores -> exp2 -> packed fp16 P (16 registers)
+        auto exp_chunk = [&](const uint32_t (&sc)[32], uint32_t (&pk)[16]) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const uint64_t x01 = ffma2(pack_f32x2(__uint_as_float(sc[i + 0]), __uint_as_float(sc[i + 1])), c2p, moffp);
+            const uint64_t x23 = ffma2(pack_f32x2(__uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3])), c2p, moffp);
+            const uint64_t p01 = tile_exp2_pair<0>(i, x01);
+            const uint64_t p23 = tile_exp2_pair<1>(i, x23);
+            sum_a = fadd2(sum_a, p01);
+            sum_b = fadd2(sum_b, p23);
+            float p0, p1, p2, p3;
+            unpack_f32x2(p01, p0, p1);
+            unpack_f32x2(p23, p2, p3);
+            pk[(i >> 1) + 0] = pack_half2(p0, p1);
+            pk[(i >> 1) + 1] = pack_half2(p2, p3);
+          }
+        };
+        {
+          // Packed P of keys [64 ch + 32 c, +32) goes to TMEM columns [32 ch + 16 c, +16) of the tile's
+          // S block.  For column half 0 those columns hold its own chunk-0 scores, so chunk 0 is read
+          // back into registers (under the exponentials of chunk 1) before any P is stored.
+          uint32_t s0[32];
+          tmem_ld_32x32b_x32(tS + ch * 64, s0);
+          uint32_t pk[16];
+          exp_chunk(s1, pk);
+          tmem_wait_ld();
+          tmem_st_32x32b_x16(tS + (2 * ch + 1) * 16, pk);
+          if (tile_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i >= limit) s0[i] = __float_as_uint(kNegInf);
+          }
+          exp_chunk(s0, pk);
+          tmem_st_32x32b_x16(tS + (2 * ch) * 16, pk);
+        }
+        float sum0, sum1, sum2, sum3;
+        unpack_f32x2(sum_a, sum0, sum1);
+        unpack_f32x2(sum_b, sum2, sum3);
+        l += (sum0 + sum1) + (sum2 + sum3);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar(ch == 0 ? iPH : iPR));
+      }
+
+      // ---- epilogue: O / l -> fp16, LSE (each half its own D/2 columns) ----------
+      if (nt > 0) {
+        mbar_wait(bar(iOD), (nt - 1) & 1, wctx, kBarODone);
+        tc_fence_after_sync();
+      }
+      float* xl = xch + 2 * 2 * kTileM;
+      xl[ch * kTileM + row] = l;
+      pair_sync();
+      l += xl[(ch ^ 1) * kTileM + row];
+      const float inv = (l > 0.f) ? 1.f / l : 0.f;
+      const bool row_ok = q_local < wk.seqlen_q;
+      __half* o_row = static_cast<__half*>(p.o) + wk.o_base + static_cast<int64_t>(q_local) * p.o_strides.row +
+                      ch * (D / 2);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        uint32_t r[32];
+        if (nt > 0) {
+          tmem_ld_32x32b_x32(tO + ch * (D / 2) + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 out;
+            out.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
+            out.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
+            out.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
+            out.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(o_row + c * 32 + v * 8) = out;
+          }
+        }
+      }
+      if (row_ok && ch == 0) {
+        const float lse = (nt > 0 && m_ref != kNegInf) ? m_ref * p.scale + logf(fmaxf(l, 1e-20f)) : kNegInf;
+        p.lse[wk.lse_base + static_cast<int64_t>(q_local) * p.lse_strides.row] = lse;
+      }
+    } else {
     const int wg = warp >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -537,7 +755,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_after_sync();
     }
     const float inv = (l > 0.f) ? 1.f / l : 0.f;
-    const bool row_ok = wg < L::kQTiles && q_local < wk.seqlen_q;  // an unused second tile owns no rows
+    const bool row_ok = q_local < wk.seqlen_q;
     __half* o_row = static_cast<__half*>(p.o) + wk.o_base +
                     static_cast<int64_t>(q_local) * p.o_strides.row;
 #pragma unroll
@@ -567,52 +785,56 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                                       : kNegInf;
       p.lse[wk.lse_base + static_cast<int64_t>(q_local) * p.lse_strides.row] = lse;
     }
+  
+    }
   }
 
   // ---- teardown -------------------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kSmWarps + 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
 }
 
-template <int D, bool CAUSAL, bool SHIFTED = false>
+template <int D, bool CAUSAL, bool SHIFTED, bool ONE_TILE>
 cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const FwdParams& p, int grid, cudaStream_t stream) {
-  auto kern = fal_fwd_kernel<D, CAUSAL, SHIFTED>;
+  auto kern = fal_fwd_kernel<D, CAUSAL, SHIFTED, ONE_TILE>;
   static DeviceOnce configured;  // one per template instance
   cudaError_t e = configured.run([&] {
     return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                FwdSmem<D>::kAllocBytes);
+                                FwdSmem<D, ONE_TILE>::kAllocBytes);
   });
   if (e != cudaSuccess) return e;
-  kern<<<grid, kFwdThreads, FwdSmem<D>::kAllocBytes, stream>>>(tq, tk, tv, p);
+  kern<<<grid, kFwdThreads, FwdSmem<D, ONE_TILE>::kAllocBytes, stream>>>(tq, tk, tv, p);
   return cudaGetLastError();
+}
+
+template <int D, bool ONE_TILE>
+cudaError_t launch_fwd_d(bool causal, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         const FwdParams& p, int grid, cudaStream_t stream) {
+  if (causal && p.causal_shift != 0) return launch_fwd_t<D, true, true, ONE_TILE>(tq, tk, tv, p, grid, stream);
+  return causal ? launch_fwd_t<D, true, false, ONE_TILE>(tq, tk, tv, p, grid, stream)
+                : launch_fwd_t<D, false, false, ONE_TILE>(tq, tk, tv, p, grid, stream);
 }
 
 }  // namespace
 
+int fwd_cta_rows(int head_dim, bool one_tile) { return (head_dim == 256 || one_tile) ? 128 : 256; }
+
 cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream) {
-  if (causal && p.causal_shift != 0) {
-    if (head_dim == 128) return launch_fwd_t<128, true, true>(tq, tk, tv, p, grid, stream);
-    if (head_dim == 64) return launch_fwd_t<64, true, true>(tq, tk, tv, p, grid, stream);
-    if (head_dim == 256) return launch_fwd_t<256, true, true>(tq, tk, tv, p, grid, stream);
-    return cudaErrorInvalidValue;
-  }
+  const bool one_tile = p.cta_rows == 128;
+  if (head_dim == 256) return one_tile ? launch_fwd_d<256, true>(causal, tq, tk, tv, p, grid, stream) : cudaErrorInvalidValue;
   if (head_dim == 128) {
-    return causal ? launch_fwd_t<128, true>(tq, tk, tv, p, grid, stream)
-                  : launch_fwd_t<128, false>(tq, tk, tv, p, grid, stream);
+    return one_tile ? launch_fwd_d<128, true>(causal, tq, tk, tv, p, grid, stream)
+                    : launch_fwd_d<128, false>(causal, tq, tk, tv, p, grid, stream);
   }
   if (head_dim == 64) {
-    return causal ? launch_fwd_t<64, true>(tq, tk, tv, p, grid, stream)
-                  : launch_fwd_t<64, false>(tq, tk, tv, p, grid, stream);
-  }
-  if (head_dim == 256) {
-    return causal ? launch_fwd_t<256, true>(tq, tk, tv, p, grid, stream)
-                  : launch_fwd_t<256, false>(tq, tk, tv, p, grid, stream);
+    return one_tile ? launch_fwd_d<64, true>(causal, tq, tk, tv, p, grid, stream)
+                    : launch_fwd_d<64, false>(causal, tq, tk, tv, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

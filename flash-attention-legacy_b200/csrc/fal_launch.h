@@ -35,7 +35,9 @@ class DeviceOnce {
   bool done_[kMaxDevices] = {};
 };
 
-// Forward: grid = number of (256-row block, batch*head) units.
+// Forward: grid = number of (p.cta_rows-row block, batch*head) units.  fwd_cta_rows gives the rows
+// a CTA takes: 256 (two query tiles) unless head_dim is 256 or the one-tile variant is asked for.
+int fwd_cta_rows(int head_dim, bool one_tile);
 cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream);
 
@@ -80,7 +82,39 @@ struct BwdPostParams {
 };
 cudaError_t launch_bwd_post(const BwdPostParams& p, cudaStream_t stream);
 
-// Decode over a KV cache in one launch: append, split-K streaming pass, log-sum-exp merge.
+// One block waiting on a barrier that never completes (fal_selftest.cu): the bounded wait must end it.
+cudaError_t launch_selftest_wait(int barrier_id, int* status, int* waits_given_up, cudaStream_t stream);
+
+// Element-wise steps of a ring / context-parallel pass (fal_ring.cu).  Tensors are addressed as
+// [batch, heads, rows, head_dim] through element strides; LSE tensors as [batch, heads, rows].
+struct MergeParams {
+  float* o_acc;          // fp32, in-out
+  float* lse_acc;        // fp32, in-out
+  const void* o_part;    // fp16
+  const float* lse_part;
+  RowStrides o_acc_strides, lse_acc_strides, o_part_strides, lse_part_strides;
+  int batch, heads, rows, head_dim;
+  int init;              // non-zero: the accumulators hold nothing yet and are overwritten
+};
+struct AccumulateParams {
+  float* dst;
+  const float* src;
+  RowStrides dst_strides, src_strides;
+  int batch, heads, rows, head_dim;
+};
+struct ScaleCastParams {
+  void* dst;             // fp16
+  const float* src;
+  RowStrides dst_strides, src_strides;
+  int batch, heads, rows, head_dim;
+  float scale;
+};
+cudaError_t launch_merge_partial(const MergeParams& p, cudaStream_t stream);
+cudaError_t launch_accumulate(const AccumulateParams& p, cudaStream_t stream);
+cudaError_t launch_scale_cast(const ScaleCastParams& p, cudaStream_t stream);
+
+// Decode over a KV cache: split-K streaming pass (which also appends the new row), then the
+// log-sum-exp combine.
 struct DecodeParams {
   const void* q;        // [batch, heads_q, head_dim] fp16, contiguous
   void* k_cache;        // fp16
@@ -95,7 +129,6 @@ struct DecodeParams {
   float* lse;           // optional [batch, heads_q]
   float* part_o;        // workspace [batch, heads_q, splits, head_dim] fp32
   float* part_ml;       // workspace [batch, heads_q, splits, 2] (max, sum)
-  int* arrivals;        // workspace [batch, heads_q] arrival counters: zero on entry, zero again on exit
   int batch;
   int heads_q;
   int heads_kv;
@@ -110,6 +143,7 @@ struct DecodeParams {
 constexpr size_t kDecodeStaticScratchBytes = 8u << 20;
 cudaError_t decode_static_scratch(float** ptr);
 
-cudaError_t launch_decode(const DecodeParams& p, cudaStream_t stream);
+cudaError_t launch_decode_splitk(const DecodeParams& p, cudaStream_t stream);
+cudaError_t launch_decode_combine(const DecodeParams& p, cudaStream_t stream);
 
 }  // namespace fal

@@ -20,14 +20,39 @@ new surface.  One process per GPU, `torch.distributed` for the plumbing.
   is read by all local queries but only its first chunk, a shard from a later rank is read in
   full but only by the second local chunk.
 
-The compute steps are injected (`local_fwd`, `local_bwd`): on a GPU they are the library's
-kernels, in the CPU tests they are the fp32 oracle, so the exchange logic is tested with the
-gloo backend without a GPU.
+Between the attention kernels of a ring step runs ONE small kernel and no tensor arithmetic of
+the framework: the forward merges each partial (O, LSE) into fp32 accumulators with the library's
+merge kernel; the backward lets the kernel add dQ into an fp32 accumulator that lives for the
+whole pass, takes dK/dV as unrounded fp32 partials and adds them to the accumulators that travel
+with their shard.  Every gradient is therefore rounded to fp16 exactly once, at the end, whatever
+the number of ranks.
+
+The compute steps are injected (`steps`): on a GPU they are the library's kernels
+(`KernelSteps`), in the CPU tests they are the fp32 oracle, so the exchange logic is tested
+with the gloo backend without a GPU.
+
+Failure detection (host side): every rank checks at entry that all ranks hold shards of one
+shape (`RingShardError` on every rank otherwise, before any data moves), and a wait for a
+neighbour's shard can be given a time limit (`timeout_s`): when it runs out -- a neighbour left
+between steps -- the call raises `RingTimeoutError` instead of blocking.  The limit is enforced
+by the backend's timed wait for CPU tensors (gloo); for CUDA tensors the wait is a stream dependency
+that never blocks the host, and a neighbour that has gone is reported by the process group's own
+timeout on the next collective.
 """
-from typing import Callable, List, Optional, Tuple
+import datetime
+import time
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+
+class RingShardError(ValueError):
+    """The ranks of a ring do not hold shards of one shape."""
+
+
+class RingTimeoutError(RuntimeError):
+    """A neighbour's shard did not arrive within the time limit."""
 
 
 def shard_range(num_units: int, world_size: int, rank: int) -> Tuple[int, int]:
@@ -63,16 +88,12 @@ def zigzag_take(x: torch.Tensor, world_size: int, rank: int, dim: int = 2) -> to
     return torch.cat([x.narrow(dim, a0, a1 - a0), x.narrow(dim, b0, b1 - b0)], dim)
 
 
-def _merge_into(o_acc, lse_acc, rows: slice, o_part, lse_part):
-    """In-place `merge_partials` restricted to the rows `rows` of the accumulators."""
-    o_new, lse_new = merge_partials(o_acc[:, :, rows], lse_acc[:, :, rows], o_part, lse_part)
-    o_acc[:, :, rows] = o_new
-    lse_acc[:, :, rows] = lse_new
-
-
 def merge_partials(o_acc: Optional[torch.Tensor], lse_acc: Optional[torch.Tensor],
                    o_part: torch.Tensor, lse_part: torch.Tensor):
-    """Exact merge of two softmax partials over disjoint key sets.  O in fp32 [..., N, d], LSE [..., N]."""
+    """Exact merge of two softmax partials over disjoint key sets.  O in fp32 [..., N, d], LSE [..., N].
+
+    The arithmetic the merge kernel implements, written with tensor operations (the CPU steps use it).
+    """
     o_part = o_part.float()
     if o_acc is None:
         return o_part, lse_part.clone()
@@ -81,6 +102,35 @@ def merge_partials(o_acc: Optional[torch.Tensor], lse_acc: Optional[torch.Tensor
     w_acc = torch.exp(lse_acc - lse_new).nan_to_num(nan=0.0).unsqueeze(-1)
     w_part = torch.exp(lse_part - lse_new).nan_to_num(nan=0.0).unsqueeze(-1)
     return o_acc * w_acc + o_part * w_part, lse_new
+
+
+class KernelSteps:
+    """The compute steps of a ring pass on a GPU: the library's kernels, nothing else."""
+
+    def __init__(self):
+        import flash_attn_legacy_cuda as ext
+        self.ext = ext
+
+    def fwd(self, q, k, v, scale, causal):
+        """-> (O fp16, LSE fp32) of the queries over this key shard."""
+        return self.ext.forward_rect(q, k, v, scale, causal)
+
+    def merge(self, o_acc, lse_acc, o_part, lse_part, init):
+        """(o_acc fp32, lse_acc) <- merged with the partial, in place (`init`: accumulators are empty)."""
+        self.ext.merge_partial(o_acc, lse_acc, o_part, lse_part, init)
+
+    def bwd(self, d_out, q, k, v, o, lse, scale, causal, dq_acc, dk_part, dv_part):
+        """dq_acc += this pair's dQ before the softmax scale; dk_part / dv_part <- this pair's dK, dV (fp32)."""
+        self.ext.backward_partial(d_out, q, k, v, o, lse, scale, causal, dq_acc, dk_part, dv_part)
+
+    def add(self, dst, src):
+        """dst += src (fp32)."""
+        self.ext.accumulate_f32(dst, src)
+
+    def cast(self, src, scale, dtype):
+        """scale * src rounded to the model dtype: the one rounding of a gradient."""
+        out = self.ext.scale_cast_f16(src, scale)
+        return out if dtype == torch.float16 else out.to(dtype)
 
 
 def _exchange(send: List[torch.Tensor], recv: List[torch.Tensor], group, rank: int, world: int):
@@ -94,6 +144,25 @@ def _exchange(send: List[torch.Tensor], recv: List[torch.Tensor], group, rank: i
     return dist.batch_isend_irecv(ops)
 
 
+def _wait_all(reqs, timeout_s: Optional[float], on_host: bool):
+    """Waits for posted transfers.  With a time limit and host-side completion (CPU tensors) the
+    backend's timed wait is used and its expiry becomes RingTimeoutError; otherwise it is the
+    backend's plain wait (for CUDA tensors a stream dependency that does not block the host)."""
+    if timeout_s is None or not on_host:
+        for r in reqs:
+            r.wait()
+        return
+    deadline = time.monotonic() + timeout_s
+    for r in reqs:
+        left = max(deadline - time.monotonic(), 0.001)
+        try:
+            r.wait(timeout=datetime.timedelta(seconds=left))
+        except RuntimeError as e:
+            if "imed out" in str(e):
+                raise RingTimeoutError(f"a ring neighbour's shard did not arrive within {timeout_s} s") from e
+            raise
+
+
 class _ShardRing:
     """The K/V (or any) shards a rank holds while they travel the ring.
 
@@ -101,12 +170,14 @@ class _ShardRing:
     land alternately in two private buffers, so the caller's tensors are never written.
     """
 
-    def __init__(self, tensors, group, rank: int, world: int):
+    def __init__(self, tensors, group, rank: int, world: int, timeout_s: Optional[float] = None):
         self.cur = [t.contiguous() for t in tensors]
         self._bufs = [None, None]
         self._turn = 0
         self._group, self._rank, self._world = group, rank, world
         self._incoming = None
+        self._timeout_s = timeout_s
+        self._on_host = not self.cur[0].is_cuda
 
     def start(self):
         """Posts send of `cur` to the next rank and receive of the previous rank's shards."""
@@ -117,22 +188,31 @@ class _ShardRing:
 
     def finish(self, reqs):
         """Waits for the posted exchange and makes the received shards current."""
-        for r in reqs:
-            r.wait()
+        _wait_all(reqs, self._timeout_s, self._on_host)
         if self._incoming is not None:
             self.cur = self._incoming
             self._incoming = None
             self._turn ^= 1
 
 
-def _kernel_fwd(q, k, v, scale, causal):
-    import flash_attn_legacy_cuda as ext
-    return ext.forward_rect(q, k, v, scale, causal)
+def check_ring_shards(tensors, group=None):
+    """Raises RingShardError on EVERY rank unless all ranks hold the same shapes and dtypes.
 
-
-def _kernel_bwd(d_out, q, k, v, o, lse, scale, causal):
-    import flash_attn_legacy_cuda as ext
-    return ext.backward(d_out, q, k, v, o, lse, scale, causal)
+    One small all-gather of the shape descriptors, before any shard moves: a rank that was handed a
+    shard of another length would otherwise receive into buffers of the wrong size (an error on one
+    rank, a hang on its neighbours).
+    """
+    world = dist.get_world_size(group)
+    desc = []
+    for t in tensors:
+        desc += [t.dim(), int(t.element_size()), int(t.is_floating_point())] + list(t.shape)
+    mine = torch.tensor([len(desc)] + desc + [0] * (63 - len(desc)), dtype=torch.int64, device=tensors[0].device)
+    everyone = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine, group=group)
+    rows = [e.cpu().tolist() for e in everyone]
+    if any(r != rows[0] for r in rows):
+        bad = [i for i, r in enumerate(rows) if r != rows[0]]
+        raise RingShardError(f"ring shards differ between ranks: ranks {bad} do not match rank 0")
 
 
 def _check_layout(layout: str, causal: bool, rows: int):
@@ -167,54 +247,63 @@ def _shard_plan(zigzag: bool, causal: bool, rank: int, src: int, rows: int):
 
 
 def ring_attention_forward(q, k, v, softmax_scale: float, causal: bool = True, group=None,
-                           local_fwd: Callable = _kernel_fwd, layout: str = "contiguous"):
+                           steps=None, layout: str = "contiguous", timeout_s: Optional[float] = None,
+                           check_shards: bool = True):
     """Forward over a sequence sharded across the ranks of `group`.
 
     q [B,Hq,Nl,d], k/v [B,Hkv,Nl,d]: this rank's rows (contiguous shard, or its two zigzag chunks
     back to back).  Returns (O [B,Hq,Nl,d] in q's dtype, LSE fp32 [B,Hq,Nl]) for this rank's
     rows, equal to attention over the whole sequence.  The inputs are not modified.
+    `steps`: the compute steps (default: the library's kernels).  `timeout_s`: see the module text.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     zigzag = _check_layout(layout, causal, q.shape[2])
+    if check_shards:
+        check_ring_shards([q, k, v], group)
+    if steps is None:
+        steps = KernelSteps()
     rows = q.shape[2]
-    kv = _ShardRing([k, v], group, rank, world)
-    o_acc, lse_acc = None, None
+    kv = _ShardRing([k, v], group, rank, world, timeout_s)
+    o_acc = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    lse_acc = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
     for step in range(world):
         reqs = kv.start() if step + 1 < world else []
         plan = _shard_plan(zigzag, causal, rank, (rank - step) % world, rows)
         if plan is not None:
             qs, ks, masked = plan
             k_cur, v_cur = kv.cur
-            o_p, lse_p = local_fwd(q[:, :, qs], k_cur[:, :, ks], v_cur[:, :, ks], softmax_scale, masked)
-            if o_acc is None:  # step 0 is the diagonal and covers every local row
-                o_acc, lse_acc = o_p.float(), lse_p.clone()
-            elif qs.stop - qs.start == rows:
-                o_acc, lse_acc = merge_partials(o_acc, lse_acc, o_p, lse_p)
-            else:
-                _merge_into(o_acc, lse_acc, qs, o_p, lse_p)
+            o_p, lse_p = steps.fwd(q[:, :, qs], k_cur[:, :, ks], v_cur[:, :, ks], softmax_scale, masked)
+            # step 0 is the diagonal and covers every local row: it initialises the accumulators
+            steps.merge(o_acc[:, :, qs], lse_acc[:, :, qs], o_p, lse_p, step == 0)
         kv.finish(reqs)
-    return o_acc.to(q.dtype), lse_acc
+    return steps.cast(o_acc, 1.0, q.dtype), lse_acc
 
 
 def ring_attention_backward(d_out, q, k, v, o, lse, softmax_scale: float, causal: bool = True, group=None,
-                            local_bwd: Callable = _kernel_bwd, layout: str = "contiguous"):
+                            steps=None, layout: str = "contiguous", timeout_s: Optional[float] = None,
+                            check_shards: bool = True):
     """Backward of `ring_attention_forward`.  `o`, `lse` are its outputs for this rank's rows.
 
-    dQ stays local (summed over the shards this rank's queries see, in fp32).  Each K/V shard
-    travels the ring together with its fp32 dK/dV accumulator; after the last step one more hop
-    returns the accumulator to the shard's owner.  Returns (dQ, dK, dV) for this rank's rows.
-    The inputs are not modified.
+    dQ stays local: the kernels add every shard pair's contribution into one fp32 accumulator.
+    Each K/V shard travels the ring together with its fp32 dK/dV accumulator, which takes each
+    rank's unrounded partial; after the last step one more hop returns the accumulator to the
+    shard's owner.  Returns (dQ, dK, dV) for this rank's rows.  The inputs are not modified.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     zigzag = _check_layout(layout, causal, q.shape[2])
+    if check_shards:
+        check_ring_shards([d_out, q, k, v, o, lse], group)
+    if steps is None:
+        steps = KernelSteps()
     rows = q.shape[2]
-    kv = _ShardRing([k, v], group, rank, world)
+    kv = _ShardRing([k, v], group, rank, world, timeout_s)
     grads = _ShardRing([torch.zeros(k.shape, dtype=torch.float32, device=k.device),
-                        torch.zeros(v.shape, dtype=torch.float32, device=v.device)], group, rank, world)
-    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
-    lse_late = None
+                        torch.zeros(v.shape, dtype=torch.float32, device=v.device)], group, rank, world, timeout_s)
+    dq_acc = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    dk_part = torch.empty(k.shape, dtype=torch.float32, device=k.device)
+    dv_part = torch.empty(v.shape, dtype=torch.float32, device=v.device)
     grads_in_flight = None
     for step in range(world):
         # K/V of the next step move while this step computes.  The gradient accumulators of the
@@ -222,29 +311,21 @@ def ring_attention_backward(d_out, q, k, v, o, lse, softmax_scale: float, causal
         # left in flight during this step's kernels and only waited for when their result is added.
         kv_reqs = kv.start() if step + 1 < world else []
         plan = _shard_plan(zigzag, causal, rank, (rank - step) % world, rows)
-        partial = None
         if plan is not None:
             qs, ks, masked = plan
             k_cur, v_cur = kv.cur
-            if qs.stop - qs.start == rows:
-                lse_rows = lse
-            else:
-                if lse_late is None:
-                    lse_late = lse[:, :, qs].contiguous()
-                lse_rows = lse_late
-            partial = local_bwd(d_out[:, :, qs], q[:, :, qs], k_cur[:, :, ks], v_cur[:, :, ks],
-                                o[:, :, qs], lse_rows, softmax_scale, masked)
+            steps.bwd(d_out[:, :, qs], q[:, :, qs], k_cur[:, :, ks], v_cur[:, :, ks], o[:, :, qs],
+                      lse[:, :, qs], softmax_scale, masked, dq_acc[:, :, qs], dk_part[:, :, ks], dv_part[:, :, ks])
         if grads_in_flight is not None:
             grads.finish(grads_in_flight)
-        if partial is not None:
-            dq_p, dk_p, dv_p = partial
+        if plan is not None:
             dk_cur, dv_cur = grads.cur
-            dq[:, :, qs] += dq_p
-            dk_cur[:, :, ks] += dk_p
-            dv_cur[:, :, ks] += dv_p
+            steps.add(dk_cur[:, :, ks], dk_part[:, :, ks])
+            steps.add(dv_cur[:, :, ks], dv_part[:, :, ks])
         kv.finish(kv_reqs)
         grads_in_flight = grads.start()
     grads.finish(grads_in_flight)
     # After `world` hops every accumulator is back at its owner.
     dk_own, dv_own = grads.cur
-    return dq.to(q.dtype), dk_own.to(k.dtype), dv_own.to(v.dtype)
+    return (steps.cast(dq_acc, softmax_scale, q.dtype), steps.cast(dk_own, 1.0, k.dtype),
+            steps.cast(dv_own, 1.0, v.dtype))

@@ -77,9 +77,49 @@ _lib.fal_profile_enable.argtypes = [_i]
 _lib.fal_profile_read.restype = _i
 _lib.fal_profile_read.argtypes = [_i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_i)]
 
+_lib.fal_bwd_partial_workspace_bytes.restype = ctypes.c_size_t
+_lib.fal_bwd_partial_workspace_bytes.argtypes = [_i, _i, _i, _i]
+_lib.fal_bwd_partial.restype = _i
+_lib.fal_bwd_partial.argtypes = [_vp] * 9 + [_i] * 6 + [_sp] * 9 + [_f, _i, _vp, ctypes.c_size_t, _vp, _vp]
+_lib.fal_merge_partial.restype = _i
+_lib.fal_merge_partial.argtypes = [_vp] * 4 + [_i] * 4 + [_sp] * 4 + [_i, _vp]
+_lib.fal_accumulate_f32.restype = _i
+_lib.fal_accumulate_f32.argtypes = [_vp, _vp] + [_i] * 4 + [_sp, _sp, _vp]
+_lib.fal_scale_cast_f16.restype = _i
+_lib.fal_scale_cast_f16.argtypes = [_vp, _vp] + [_i] * 4 + [_sp, _sp, _f, _vp]
+
+_lib.fal_selftest_wait_timeout.restype = _i
+_lib.fal_selftest_wait_timeout.argtypes = [_i, _vp, _vp, _vp]
+_lib.fal_set_fwd_variant.restype = _i
+_lib.fal_set_fwd_variant.argtypes = [_i]
+
 __version__ = _lib.fal_version().decode()
 
 KERNEL_FWD, KERNEL_BWD, KERNEL_DECODE_SPLITK = 0, 1, 2
+
+
+FWD_AUTO, FWD_ONE_TILE, FWD_TWO_TILES = 0, 1, 2
+
+
+def set_forward_variant(variant=FWD_AUTO):
+    """Forces a forward kernel variant for later calls (FWD_AUTO: chosen per call); see fal_b200.h."""
+    _check(_lib.fal_set_fwd_variant(int(variant)))
+
+
+def selftest_wait_timeout(barrier_id=7):
+    """Runs the library's bounded-wait self-test on the current device and stream.
+
+    A block waits (about one second) on a barrier that never completes; the wait must give up and
+    report.  Returns (status word, warps whose wait gave up); the status word is left set to
+    1000 + barrier_id until `reset_device_status()`.
+    """
+    dev = torch.device("cuda", torch.cuda.current_device())
+    status = _status_word(dev)
+    gave_up = torch.zeros(1, dtype=torch.int32, device=dev)
+    _check(_lib.fal_selftest_wait_timeout(int(barrier_id), status.data_ptr(), gave_up.data_ptr(),
+                                          ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    torch.cuda.synchronize(dev)
+    return int(status.item()), int(gave_up.item())
 
 
 def profile_enable(on=True):
@@ -194,14 +234,14 @@ def forward(Q, K, V, softmax_scale, is_causal=False, out=None, lse=None):
     return [O, L]
 
 
-def forward_rect(Q, K, V, softmax_scale, is_causal=False, bottom_right=False, out=None):
+def forward_rect(Q, K, V, softmax_scale, is_causal=False, bottom_right=False, out=None, lse=None):
     """Forward with seqlen_k != seqlen_q allowed.
 
     The causal mask is top-left aligned (key j visible to query i iff j <= i, the reference's
     convention) unless `bottom_right` is set: then, with Nk >= Nq, the queries are the last Nq
     positions of the key sequence and query i sees keys j <= i + Nk - Nq (a prompt chunk attending
     to a cache that already holds the earlier chunks).  `out`: optional fp16 [B,Hq,Nq,d] tensor
-    (any strides with a contiguous head_dim) to write into.
+    (any strides with a contiguous head_dim) to write into; `lse`: optional contiguous fp32 [B,Hq,Nq].
     """
     _require_cuda_half("Q", Q, 4)
     _require_cuda_half("K", K, 4)
@@ -216,7 +256,9 @@ def forward_rect(Q, K, V, softmax_scale, is_causal=False, bottom_right=False, ou
         if tuple(out.shape) != (B, Hq, Nq, d):
             raise RuntimeError("out must be [B, H_q, N_q, d]")
     O = out if out is not None else torch.empty((B, Hq, Nq, d), dtype=torch.float16, device=Q.device)
-    L = torch.empty((B, Hq, Nq), dtype=torch.float32, device=Q.device)
+    if lse is not None and (lse.dtype != torch.float32 or tuple(lse.shape) != (B, Hq, Nq) or not lse.is_contiguous()):
+        raise RuntimeError("lse must be contiguous float32 [B, H_q, N_q]")
+    L = lse if lse is not None else torch.empty((B, Hq, Nq), dtype=torch.float32, device=Q.device)
     _check(_lib.fal_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), L.data_ptr(),
                         B, Hq, Hkv, Nq, Nk, d,
                         _bhn_strides(Q), _bhn_strides(K), _bhn_strides(V), _bhn_strides(O),
@@ -329,21 +371,117 @@ def backward_varlen(dO, Q, K, V, O, L, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
     return [dQ, dK, dV]
 
 
+# ---------------------------------------------------------------------------------------------
+# Steps of a ring / context-parallel pass (no counterpart in the reference, which is single-GPU)
+# ---------------------------------------------------------------------------------------------
+def _require_f32(name, t, ndim):
+    if not t.is_cuda or t.dtype != torch.float32 or t.dim() != ndim:
+        raise RuntimeError(f"{name} must be a float32 CUDA tensor with {ndim} dimensions")
+
+
+def _lse_strides(t):
+    """Strides of a [B, H, N] statistics view."""
+    return _Strides(t.stride(0), t.stride(1), t.stride(2))
+
+
+def backward_partial_workspace_bytes(B, Hq, rows, d):
+    return int(_lib.fal_bwd_partial_workspace_bytes(B, Hq, rows, d))
+
+
+def backward_partial(dO, Q, K, V, O, L, softmax_scale, is_causal, dq_accum, dk_partial, dv_partial,
+                     workspace=None):
+    """Backward of one (query rows, key shard) pair of a larger problem, outputs left in fp32.
+
+    `dq_accum` fp32 [B,Hq,Nq,d] (rows contiguous) is ADDED to, without the softmax scale;
+    `dk_partial` / `dv_partial` fp32 [B,Hkv,Nk,d] are overwritten with this pair's dK (scaled) and dV.
+    `O`, `L` are the final output and log-sum-exp of the query rows over all keys.  Views with
+    strides are read and written in place.
+    """
+    for name, t in (("dO", dO), ("Q", Q), ("K", K), ("V", V), ("O", O)):
+        _require_cuda_half(name, t, 4)
+    for name, t in (("dq_accum", dq_accum), ("dk_partial", dk_partial), ("dv_partial", dv_partial)):
+        _require_f32(name, t, 4)
+        if t.stride(-1) != 1:
+            raise RuntimeError(f"{name} must have a contiguous last dimension")
+    _require_f32("L", L, 3)
+    _same_device(dO, Q, K, V, O, L, dq_accum, dk_partial, dv_partial)
+    B, Hq, Nq, d = Q.shape
+    Hkv, Nk = K.shape[1], K.shape[2]
+    if dO.shape != Q.shape or O.shape != Q.shape or tuple(L.shape) != (B, Hq, Nq):
+        raise RuntimeError("dO, O must have Q's shape and L must be [B, H_q, N_q]")
+    if tuple(dq_accum.shape) != (B, Hq, Nq, d) or dq_accum.stride(2) != d:
+        raise RuntimeError("dq_accum must be [B, H_q, N_q, d] with contiguous rows")
+    if tuple(dk_partial.shape) != tuple(K.shape) or tuple(dv_partial.shape) != tuple(V.shape) or V.shape != K.shape:
+        raise RuntimeError("dk_partial / dv_partial must have K's shape")
+    nbytes = _lib.fal_bwd_partial_workspace_bytes(B, Hq, Nq, d)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device) if workspace is None else workspace
+    if ws.numel() < nbytes:
+        raise RuntimeError("workspace too small")
+    _check(_lib.fal_bwd_partial(dO.data_ptr(), Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(),
+                                L.data_ptr(), dq_accum.data_ptr(), dk_partial.data_ptr(), dv_partial.data_ptr(),
+                                B, Hq, Hkv, Nq, Nk, d,
+                                _bhn_strides(dO), _bhn_strides(Q), _bhn_strides(K), _bhn_strides(V),
+                                _bhn_strides(O), _bhn_strides(dq_accum), _bhn_strides(dk_partial),
+                                _bhn_strides(dv_partial), _lse_strides(L),
+                                float(softmax_scale), int(bool(is_causal)),
+                                ws.data_ptr(), ws.numel(), _status_word(Q.device).data_ptr(), _stream(Q)))
+
+
+def merge_partial(o_acc, lse_acc, o_part, lse_part, init=False):
+    """In place: (o_acc fp32, lse_acc) <- exact merge with (o_part fp16, lse_part); see fal_merge_partial."""
+    _require_f32("o_acc", o_acc, 4)
+    _require_cuda_half("o_part", o_part, 4)
+    _require_f32("lse_acc", lse_acc, 3)
+    _require_f32("lse_part", lse_part, 3)
+    _same_device(o_acc, lse_acc, o_part, lse_part)
+    B, H, N, d = o_acc.shape
+    if tuple(o_part.shape) != (B, H, N, d) or tuple(lse_acc.shape) != (B, H, N) or tuple(lse_part.shape) != (B, H, N):
+        raise RuntimeError("merge_partial: shapes must be [B,H,N,d] / [B,H,N]")
+    if o_acc.stride(-1) != 1:
+        raise RuntimeError("o_acc must have a contiguous last dimension")
+    _check(_lib.fal_merge_partial(o_acc.data_ptr(), lse_acc.data_ptr(), o_part.data_ptr(), lse_part.data_ptr(),
+                                  B, H, N, d, _bhn_strides(o_acc), _lse_strides(lse_acc), _bhn_strides(o_part),
+                                  _lse_strides(lse_part), int(bool(init)), _stream(o_acc)))
+
+
+def accumulate_f32(dst, src):
+    """In place: dst += src, both fp32 [B,H,N,d] views."""
+    _require_f32("dst", dst, 4)
+    _require_f32("src", src, 4)
+    _same_device(dst, src)
+    if dst.shape != src.shape or dst.stride(-1) != 1 or src.stride(-1) != 1:
+        raise RuntimeError("accumulate_f32: same shape and contiguous last dimensions needed")
+    B, H, N, d = dst.shape
+    _check(_lib.fal_accumulate_f32(dst.data_ptr(), src.data_ptr(), B, H, N, d, _bhn_strides(dst),
+                                   _bhn_strides(src), _stream(dst)))
+
+
+def scale_cast_f16(src, scale=1.0, out=None):
+    """fp16(scale * src) for an fp32 [B,H,N,d] view; returns the fp16 tensor."""
+    _require_f32("src", src, 4)
+    if src.stride(-1) != 1:
+        raise RuntimeError("src must have a contiguous last dimension")
+    dst = torch.empty(src.shape, dtype=torch.float16, device=src.device) if out is None else out
+    _same_device(src, dst)
+    B, H, N, d = src.shape
+    _check(_lib.fal_scale_cast_f16(dst.data_ptr(), src.data_ptr(), B, H, N, d, _bhn_strides(dst),
+                                   _bhn_strides(src), float(scale), _stream(src)))
+    return dst
+
+
 _decode_ws = {}
 
 
 def _decode_workspace(device, nbytes):
-    """Zero-initialised decode workspace of the current stream, kept across calls.
+    """Split-K scratch of the current stream, kept across calls (decode loops call once per token).
 
     One workspace per (device, stream): calls on different streams may overlap on the GPU and must
-    not share partial results or arrival counters.  A workspace is replaced when a call needs more
-    room.  It is created zeroed (the library's arrival counters must start at zero and are left at
-    zero by every call).
+    not share partial results.  A workspace is replaced when a call needs more room.
     """
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _decode_ws.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _decode_ws[key] = ws
     return ws
 

@@ -90,6 +90,26 @@ FAL_API int fal_fwd(const void* q, const void* k, const void* v, void* o, float*
             float softmax_scale, int is_causal, int* status, void* stream);
 
 /*
+ * Forward kernel variants.  A thread block takes one or two 128-row query tiles:
+ *   FAL_FWD_TWO_TILES        two tiles, one softmax warpgroup each (a thread owns a whole score row),
+ *                            one tile's softmax running under the other tile's MMAs;
+ *   FAL_FWD_ONE_TILE         one tile with both softmax warpgroups on it (a thread owns 64 columns
+ *                            of a row): twice as many blocks, for problems whose two-tile grid would
+ *                            not give every SM a block.
+ * FAL_FWD_AUTO (default) chooses per call (one tile when the two-tile grid has fewer blocks than the
+ * device has SMs; head_dim 256 always runs one tile).  fal_set_fwd_variant forces a variant for
+ * every later call in the process: a tuning and test control -- the results agree within rounding.
+ * The reference picks tile sizes from a compile-time table per architecture instead
+ * (csrc/include/flash_attn_common.h:157-292).
+ */
+enum fal_fwd_variant {
+  FAL_FWD_AUTO = 0,
+  FAL_FWD_ONE_TILE = 1,
+  FAL_FWD_TWO_TILES = 2
+};
+FAL_API int fal_set_fwd_variant(int variant);
+
+/*
  * Packed (variable-length) forward.  Stands in for flash_attn_forward_varlen
  * (csrc/flash_attn_legacy.cpp:193-290; bound as `forward_varlen` at :299-304).
  *   q [total_q,Hq,d], k/v [total_k,Hkv,d], o [total_q,Hq,d]; lse [total_q,Hq] contiguous.
@@ -147,20 +167,71 @@ FAL_API int fal_bwd_varlen(const void* d_out, const void* q, const void* k, cons
                    void* workspace, size_t workspace_bytes, int* status, void* stream);
 
 /*
- * Bytes of scratch fal_decode needs: its split-K partial results followed by one int32 arrival
- * counter per (batch entry, query head).  The counters must be ZERO when a call starts and every
- * call puts them back to zero, so a workspace is cleared once (cudaMemsetAsync over the whole
- * workspace is enough) after it is allocated and can then serve any number of calls, also with
- * other shapes that fit it.  The partial results need no initialisation.  Calls that use the same
- * workspace must not overlap on the GPU.  The workspace must be 16-byte aligned.
+ * Steps of a ring / context-parallel pass over one long sequence whose rows are sharded over
+ * several GPUs.  The reference has no multi-GPU code at all; its long-sequence case
+ * (tests/test_flash_attn.py:486-547) runs on one GPU.  Per ring step a rank calls fal_fwd (or
+ * fal_bwd_partial) on its query rows against the key shard it currently holds, then one of the
+ * small element-wise kernels below; nothing else touches the data between the attention kernels.
+ * All tensors are addressed as [batch, head, row, head_dim] through element strides, LSE tensors
+ * as [batch, head, row].
+ */
+
+/* Bytes of scratch fal_bwd_partial needs (the rowsum(dO*O) vector only). */
+FAL_API size_t fal_bwd_partial_workspace_bytes(int batch, int heads_q, int rows, int head_dim);
+
+/*
+ * Backward of ONE (query rows, key shard) pair of a larger problem: the same kernels as fal_bwd
+ * with the outputs left unrounded, so that a caller can sum them over several calls.
+ *   dq_accum  fp32 [B,Hq,Nq,d] (rows of d contiguous floats), IN-OUT: this pair's dQ, NOT yet
+ *             multiplied by softmax_scale, is ADDED to it (the caller zeroes it before the first
+ *             pair and applies scale * accumulator once at the end, e.g. with fal_scale_cast_f16);
+ *   dk_partial, dv_partial  fp32 [B,Hkv,Nk,d], OUT: this pair's dK (scaled) and dV, overwritten;
+ *   o, lse    the FINAL output and log-sum-exp of the query rows over ALL keys of the larger problem
+ *             (P is recomputed from them), lse addressed through lse_strides;
+ *   is_causal 0 or 1 (top-left aligned on this pair's rows, for the pair on the diagonal).
+ */
+FAL_API int fal_bwd_partial(const void* d_out, const void* q, const void* k, const void* v, const void* o,
+                    const float* lse, float* dq_accum, float* dk_partial, float* dv_partial,
+                    int batch, int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
+                    const fal_strides* do_strides, const fal_strides* q_strides,
+                    const fal_strides* k_strides, const fal_strides* v_strides,
+                    const fal_strides* o_strides, const fal_strides* dq_accum_strides,
+                    const fal_strides* dk_strides, const fal_strides* dv_strides,
+                    const fal_strides* lse_strides, float softmax_scale, int is_causal,
+                    void* workspace, size_t workspace_bytes, int* status, void* stream);
+
+/*
+ * Exact merge of two softmax partials over disjoint key sets, in place:
+ *   lse_new = log(exp(lse_acc) + exp(lse_part)),
+ *   o_acc   = o_acc * exp(lse_acc - lse_new) + o_part * exp(lse_part - lse_new),  lse_acc = lse_new.
+ * o_acc fp32, o_part fp16 (as fal_fwd writes it), LSEs fp32.  A side with lse = -inf has weight 0.
+ * init != 0: the accumulators hold nothing yet and are overwritten with the partial.
+ */
+FAL_API int fal_merge_partial(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part,
+                      int batch, int heads, int rows, int head_dim,
+                      const fal_strides* o_acc_strides, const fal_strides* lse_acc_strides,
+                      const fal_strides* o_part_strides, const fal_strides* lse_part_strides,
+                      int init, void* stream);
+
+/* dst += src, both fp32 (a travelling dK / dV accumulator takes a rank's partial). */
+FAL_API int fal_accumulate_f32(float* dst, const float* src, int batch, int heads, int rows, int head_dim,
+                       const fal_strides* dst_strides, const fal_strides* src_strides, void* stream);
+
+/* dst (fp16) = scale * src (fp32): the one rounding at the end of an accumulation. */
+FAL_API int fal_scale_cast_f16(void* dst, const float* src, int batch, int heads, int rows, int head_dim,
+                       const fal_strides* dst_strides, const fal_strides* src_strides, float scale,
+                       void* stream);
+
+/*
+ * Bytes of scratch fal_decode needs for its split-K partial results (no initialisation needed;
+ * 16-byte aligned; calls that use the same workspace must not overlap on the GPU).
  */
 FAL_API size_t fal_decode_workspace_bytes(int batch, int heads_q, int capacity, int head_dim);
 
 /*
- * Single-token decode against a KV cache (q_len = 1) in ONE kernel launch: the new token's
- * K/V row is written by the thread block whose split contains its position, every block
- * streams its split of the cache once, and the block that finishes last for a (batch entry,
- * head group) merges the splits (log-sum-exp).  Stands in for the eager fallback branch of the
+ * Single-token decode against a KV cache (q_len = 1): a split-K streaming pass -- in which the
+ * thread block whose split contains the new token's position first writes its K/V row -- plus
+ * a log-sum-exp combine.  Stands in for the eager fallback branch of the
  * reference's attention hook (flash_attn_legacy/integrations.py:77-98): no
  * causal mask, GQA by head mapping, softmax over the cached positions.
  *   q, o [B,Hq,d] contiguous; caches addressed by strides as [B,Hkv,position,d];
@@ -216,12 +287,10 @@ FAL_API int fal_decode_ranged(const void* q, void* k_cache, void* v_cache,
  *   - the first call on each device looks up the scratch's device address
  *     (cudaGetSymbolAddress); make that first call before any stream capture;
  *   - all calls on a device share the one array, which keeps whatever the last call
- *     left in it.  The partial results need no clearing (every slot the merge step reads
- *     is written earlier in the same call); the arrival counters behind them start at
- *     zero because the array is zero-initialised when the library is loaded, and every
- *     call leaves them at zero.  Two calls that overlap on the GPU -- different streams,
- *     or different host threads without ordering -- race on the array and corrupt each
- *     other's results.  Serialise them on one stream.
+ *     left in it.  Nothing in it has to start at zero (every slot the combine step
+ *     reads is written earlier in the same call), but two calls that overlap on the
+ *     GPU -- different streams, or different host threads without ordering -- race
+ *     on it and corrupt each other's results.  Serialise them on one stream.
  */
 #define FAL_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
 FAL_API int fal_decode_static(const void* q, void* k_cache, void* v_cache,
@@ -230,6 +299,16 @@ FAL_API int fal_decode_static(const void* q, void* k_cache, void* v_cache,
                       void* o, float* lse,
                       int batch, int heads_q, int heads_kv, int capacity, int head_dim,
                       float softmax_scale, int* status, void* stream);
+
+/*
+ * Self-test of the kernels' bounded waits (no counterpart in the reference, whose kernels only use
+ * __syncthreads).  Launches one small thread block that waits on a barrier nothing will complete,
+ * through the same wait routine and time limit (about one second) as the attention kernels.  The
+ * kernel must end by itself: afterwards *status (device int, must be 0 before) holds
+ * 1000 + barrier_id and *waits_given_up (device int, optional) the number of warps whose wait gave
+ * up.  The device stays usable; nothing traps or faults.
+ */
+FAL_API int fal_selftest_wait_timeout(int barrier_id, int* status, int* waits_given_up, void* stream);
 
 /*
  * Optional kernel timing, off by default.  While enabled, the library records a
@@ -242,7 +321,7 @@ FAL_API int fal_decode_static(const void* q, void* k_cache, void* v_cache,
 enum fal_kernel_kind {
   FAL_KERNEL_FWD = 0,          /* forward main kernel */
   FAL_KERNEL_BWD = 1,          /* backward dK/dV/dQ kernel (without pre/post passes) */
-  FAL_KERNEL_DECODE_SPLITK = 2 /* the decode kernel (append, split-K streaming pass, merge) */
+  FAL_KERNEL_DECODE_SPLITK = 2 /* decode streaming pass incl. the append (without the combine) */
 };
 FAL_API int fal_profile_enable(int on);
 FAL_API int fal_profile_read(int kind, double* total_ms, int* launches);

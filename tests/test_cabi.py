@@ -25,7 +25,7 @@ def declared_functions():
 def test_header_declares_the_expected_entry_points():
     names = declared_functions()
     for must in ("fal_fwd", "fal_fwd_varlen", "fal_bwd", "fal_bwd_varlen", "fal_decode", "fal_decode_ranged",
-                 "fal_bwd_workspace_bytes", "fal_decode_workspace_bytes", "fal_strerror"):
+                 "fal_bwd_workspace_bytes", "fal_decode_workspace_bytes", "fal_strerror", "fal_set_fwd_variant"):
         assert must in names
 
 
@@ -58,11 +58,9 @@ def test_workspace_sizes(lib):
     expect = 4 * 32 * rows * 128 * 4 + 4 * 32 * rows * 4
     assert lib.fal_bwd_workspace_bytes(4, 32, 4096, 128) == expect
     assert lib.fal_bwd_workspace_bytes(0, 32, 4096, 128) == 0
-    # 32 splits of 1024 positions, (d + 2) floats per (batch, head, split), then one int32 arrival
-    # counter per (batch, head); both parts rounded up to 16 bytes
-    assert lib.fal_decode_workspace_bytes(64, 32, 32768, 128) == 64 * 32 * 32 * 130 * 4 + 64 * 32 * 4
-    assert lib.fal_decode_workspace_bytes(1, 8, 1000, 64) == 1 * 8 * 1 * 66 * 4 + 8 * 4
-    assert lib.fal_decode_workspace_bytes(1, 1, 10, 64) == 272 + 16
+    # 32 splits of 1024 positions, (d + 2) floats per (batch, head, split)
+    assert lib.fal_decode_workspace_bytes(64, 32, 32768, 128) == 64 * 32 * 32 * 130 * 4
+    assert lib.fal_decode_workspace_bytes(1, 8, 1000, 64) == 1 * 8 * 1 * 66 * 4
 
 
 class Strides(ctypes.Structure):
@@ -114,6 +112,7 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     # workspace too small
     assert lib.fal_decode(fake, fake, fake, st, st, fake, None, None, fake, None, 1, 8, 2, 128, 64, 0.125,
                           fake, 16, None, None) == -3
+
     # the ranged form without its first-position array
     lib.fal_decode_ranged.restype = i
     lib.fal_decode_ranged.argtypes = [vp, vp, vp, sp, sp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp,

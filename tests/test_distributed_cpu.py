@@ -1,8 +1,9 @@
-"""CPU, gloo, world_size 2 and 3: the sharding helpers and the ring KV exchange.
+"""CPU, gloo, world_size 2 to 4: the sharding helpers and the ring KV exchange.
 
 The ring's compute steps are injected, so here they are the fp32 oracle; what is under test is the
-exchange schedule, the causal shard skipping, the exact merge of partials and the travelling dK/dV
-accumulators.  The same functions run on GPUs with the library's kernels as the compute steps.
+exchange schedule, the causal shard skipping, the exact merge of partials, the travelling dK/dV
+accumulators and the host-side failure detection (a rank that stops between steps, a shard of the
+wrong size).  The same functions run on GPUs with the library's kernels as the compute steps.
 """
 import os
 import socket
@@ -19,10 +20,6 @@ def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
-
-
-def _oracle_fwd(q, k, v, scale, causal):
-    return orc.attention_fwd(q, k, v, scale, causal)
 
 
 def _oracle_bwd(d_out, q, k, v, o, lse, scale, causal):
@@ -44,6 +41,36 @@ def _oracle_bwd(d_out, q, k, v, o, lse, scale, causal):
     dk = (torch.matmul(ds.transpose(-1, -2), q.float()) * scale).view(b, hkv, reps, nk, d).sum(2)
     dv = torch.matmul(p.transpose(-1, -2), g).view(b, hkv, reps, nk, d).sum(2)
     return dq, dk, dv
+
+
+class OracleSteps:
+    """The ring's compute steps on the CPU: the fp32 oracle and plain tensor arithmetic, with the
+    contracts of flash_attn_legacy.distributed.KernelSteps."""
+
+    def fwd(self, q, k, v, scale, causal):
+        return orc.attention_fwd(q, k, v, scale, causal)
+
+    def merge(self, o_acc, lse_acc, o_part, lse_part, init):
+        import flash_attn_legacy.distributed as fd
+        if init:
+            o_acc.copy_(o_part)
+            lse_acc.copy_(lse_part)
+        else:
+            o_new, lse_new = fd.merge_partials(o_acc.clone(), lse_acc.clone(), o_part, lse_part)
+            o_acc.copy_(o_new)
+            lse_acc.copy_(lse_new)
+
+    def bwd(self, d_out, q, k, v, o, lse, scale, causal, dq_acc, dk_part, dv_part):
+        dq, dk, dv = _oracle_bwd(d_out, q, k, v, o, lse, scale, causal)
+        dq_acc += dq / scale          # the accumulator holds dQ before the softmax scale
+        dk_part.copy_(dk)
+        dv_part.copy_(dv)
+
+    def add(self, dst, src):
+        dst += src
+
+    def cast(self, src, scale, dtype):
+        return (src * scale).to(dtype)
 
 
 def _ring_worker(rank, world, port, causal, results, layout="contiguous"):
@@ -68,9 +95,9 @@ def _ring_worker(rank, world, port, causal, results, layout="contiguous"):
                 return x[:, :, lo:hi]
         # contiguous local tensors, reused by both calls: the exchange must leave them as they are
         ql, kl, vl, gl = (take(x).contiguous() for x in (q, k, v, g))
-        o, lse = fd.ring_attention_forward(ql, kl, vl, 0.25, causal, None, _oracle_fwd, layout)
+        o, lse = fd.ring_attention_forward(ql, kl, vl, 0.25, causal, None, OracleSteps(), layout)
         o_ref, lse_ref = orc.attention_fwd(q, k, v, 0.25, causal)
-        dq, dk, dv = fd.ring_attention_backward(gl, ql, kl, vl, o, lse, 0.25, causal, None, _oracle_bwd, layout)
+        dq, dk, dv = fd.ring_attention_backward(gl, ql, kl, vl, o, lse, 0.25, causal, None, OracleSteps(), layout)
         assert torch.equal(kl, take(k)) and torch.equal(vl, take(v)) and torch.equal(ql, take(q))
         dq_ref, dk_ref, dv_ref = orc.attention_bwd(q, k, v, g, 0.25, causal)
         errs = [(o - take(o_ref)).abs().max().item(), (lse - take(lse_ref)).abs().max().item(),
@@ -144,3 +171,105 @@ def test_merge_partials_is_exact():
     # a part that saw no keys (LSE = -inf) leaves the other part unchanged
     o3, l3 = fd.merge_partials(o1, l1, torch.zeros_like(o1), torch.full_like(l1, float("-inf")))
     assert torch.allclose(o3, o1) and torch.allclose(l3, l1)
+
+
+# ---------------------------------------------------------------------------------------------
+# Failure detection on the host: no GPU is involved, nothing is made to fault
+# ---------------------------------------------------------------------------------------------
+class _LeavesAfterFirstStep(OracleSteps):
+    """A rank that computes its first ring step and then stops taking part: it has posted the first
+    exchange, it never posts the second."""
+
+    class Left(Exception):
+        pass
+
+    def merge(self, o_acc, lse_acc, o_part, lse_part, init):
+        super().merge(o_acc, lse_acc, o_part, lse_part, init)
+        raise self.Left()
+
+
+def _stalled_ring_worker(rank, world, port, results, release):
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                    "flash-attention-legacy_b200"))
+    from flash_attn_legacy import distributed as fd
+    torch.manual_seed(rank)
+    q, k, v = torch.randn(1, 2, 8, 16), torch.randn(1, 2, 8, 16), torch.randn(1, 2, 8, 16)
+    leaver = world - 1
+    steps = _LeavesAfterFirstStep() if rank == leaver else OracleSteps()
+    t0 = time.monotonic()
+    try:
+        fd.ring_attention_forward(q, k, v, 0.25, False, None, steps, "contiguous", timeout_s=2.0)
+        outcome = "completed"
+    except _LeavesAfterFirstStep.Left:
+        outcome = "left"
+    except fd.RingTimeoutError:
+        outcome = "timeout"
+    except RuntimeError as e:  # the transport itself noticed
+        outcome = "transport error: " + str(e)[:80]
+    results[rank] = (outcome, time.monotonic() - t0)
+    # The rank that left stays alive (a stalled peer, not a dead one) until the others have reported.
+    release.wait(timeout=60)
+    os._exit(0)  # pending transfers to the stalled rank can never complete: skip the orderly shutdown
+
+
+def test_a_rank_that_stops_between_ring_steps_is_detected_by_its_neighbours():
+    """World 3, no mask (every rank has work in every step).  Rank 2 computes step 0 and stops.  Rank 0
+    waits for the shard rank 2 should forward in step 1: it must give up with RingTimeoutError after the
+    stated 2 s instead of blocking; rank 1 either finishes (it depends on rank 0 only) or reports too."""
+    world = 3
+    mgr = mp.Manager()
+    results, release = mgr.dict(), mgr.Event()
+    ctx = mp.spawn(_stalled_ring_worker, args=(world, _free_port(), results, release), nprocs=world, join=False)
+    import time
+    deadline = time.monotonic() + 40
+    while len(results) < world and time.monotonic() < deadline:
+        time.sleep(0.05)
+    release.set()
+    ctx.join(timeout=30)
+    assert len(results) == world, dict(results)
+    assert results[2][0] == "left"
+    outcome0, seconds0 = results[0]
+    assert outcome0 == "timeout" or outcome0.startswith("transport error"), dict(results)
+    assert seconds0 < 10, seconds0
+    assert results[1][0] in ("completed", "timeout") or results[1][0].startswith("transport error")
+    assert results[1][1] < 20
+
+
+def _wrong_shard_worker(rank, world, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import sys
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                        "flash-attention-legacy_b200"))
+        from flash_attn_legacy import distributed as fd
+
+        class Counting(OracleSteps):
+            calls = 0
+
+            def fwd(self, *a):
+                Counting.calls += 1
+                return super().fwd(*a)
+
+        rows = 8 if rank == 0 else 12  # rank 1 was handed a shard of another length
+        q, k, v = torch.randn(1, 2, rows, 16), torch.randn(1, 2, rows, 16), torch.randn(1, 2, rows, 16)
+        try:
+            fd.ring_attention_forward(q, k, v, 0.25, True, None, Counting(), "contiguous")
+            results[rank] = ("no error", Counting.calls)
+        except fd.RingShardError:
+            results[rank] = ("shard error", Counting.calls)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_shard_of_the_wrong_size_is_rejected_on_every_rank_before_anything_moves():
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_wrong_shard_worker, args=(2, _free_port(), results), nprocs=2, join=True)
+    assert dict(results) == {0: ("shard error", 0), 1: ("shard error", 0)}

@@ -125,7 +125,8 @@ def test_config1_mha_forward_n1024_d64(ext):
 
 def test_config2_gqa_n4096_d128_full_size(ext):
     """B=4, Hq=32, Hkv=8, N=4096, d=128 causal forward + backward at full size on the GPU; the oracle
-    checks two whole (batch, kv-head) groups; the rest is covered by size-independent properties."""
+    checks 11 of the 32 (batch, kv-head) groups in full -- all eight of batch entry 0 and one of each
+    other entry; the rest is covered by size-independent properties."""
     B, Hq, Hkv, N, d = 4, 32, 8, 4096, 128
     gen = torch.Generator(device="cuda").manual_seed(1)
     q = torch.randn(B, Hq, N, d, device="cuda", generator=gen).half()
@@ -135,7 +136,7 @@ def test_config2_gqa_n4096_d128_full_size(ext):
     scale = 1 / math.sqrt(d)
     o, lse = ext.forward(q, k, v, scale, True)
     dq, dk, dv = ext.backward(do, q, k, v, o, lse, scale, True)
-    for b, h in ((0, 0), (3, 5)):
+    for b, h in [(0, h) for h in range(8)] + [(1, 2), (2, 7), (3, 5)]:
         sl = slice(4 * h, 4 * h + 4)
         qs, ks, vs, gs = q[b:b + 1, sl].cpu(), k[b:b + 1, h:h + 1].cpu(), v[b:b + 1, h:h + 1].cpu(), do[b:b + 1, sl].cpu()
         o_ref, lse_ref = orc.attention_fwd_blocked(qs, ks, vs, scale, True)
@@ -220,6 +221,41 @@ def test_rectangular_forward_top_left_causal(ext):
         check_fwd(o, lse, *orc.attention_fwd(q, k, v, 0.125, causal))
 
 
+@pytest.mark.parametrize("tiles", [1, 2])
+@pytest.mark.parametrize("d", [64, 128])
+def test_every_forward_kernel_variant(ext, tiles, d):
+    """Both forward variants -- one 128-row tile per thread block with both softmax warpgroups on it
+    (1), two tiles with one warpgroup each (2) -- on the same problems; by default the library picks
+    by grid size, so small problems would otherwise only ever see the first."""
+    ext.set_forward_variant(tiles)
+    try:
+        for n, hq, hkv, causal in ((1, 4, 2, True), (100, 4, 2, True), (257, 4, 4, False), (777, 8, 2, True),
+                                   (1500, 4, 1, True), (2048, 2, 2, False)):
+            g = torch.Generator().manual_seed(n + d + tiles)
+            q, k, v = rand_half(g, 2, hq, n, d), rand_half(g, 2, hkv, n, d), rand_half(g, 2, hkv, n, d)
+            scale = 1 / math.sqrt(d)
+            o, lse = ext.forward(q.cuda(), k.cuda(), v.cuda(), scale, causal)
+            check_fwd(o, lse, *orc.attention_fwd(q, k, v, scale, causal))
+            o2, lse2 = ext.forward(q.cuda(), k.cuda(), v.cuda(), scale, causal)
+            assert torch.equal(o, o2) and torch.equal(lse, lse2)   # bitwise deterministic either way
+        # large scores: the running maximum moves and O is rescaled (each column half its own columns)
+        g = torch.Generator().manual_seed(77 + tiles)
+        q, k, v = rand_half(g, 1, 2, 600, d) * 6, rand_half(g, 1, 2, 600, d) * 6, rand_half(g, 1, 2, 600, d)
+        o, lse = ext.forward(q.cuda(), k.cuda(), v.cuda(), 1 / math.sqrt(d), True)
+        check_fwd(o, lse, *orc.attention_fwd(q, k, v, 1 / math.sqrt(d), True))
+        # packed sequences and the end-aligned mask
+        lens = [300, 17, 1025, 256]
+        qp, kp, vp, _, cu = packed_inputs(g, lens, 4, 2, d)
+        o, lse = ext.forward_varlen(qp.cuda(), kp.cuda(), vp.cuda(), cu.cuda(), cu.cuda(), 1025, 1025, 0.1, True)
+        check_fwd(o, lse, *orc.varlen_fwd(qp, kp, vp, cu, cu, 0.1, True))
+        q, k, v = rand_half(g, 1, 4, 200, d), rand_half(g, 1, 2, 777, d), rand_half(g, 1, 2, 777, d)
+        o, lse = ext.forward_rect(q.cuda(), k.cuda(), v.cuda(), 0.1, True, bottom_right=True)
+        check_fwd(o, lse, *orc.attention_fwd(q, k, v, 0.1, True, causal_shift=577))
+        assert ext.device_status() == 0
+    finally:
+        ext.set_forward_variant(0)
+
+
 # ---------------------------------------------------------------------------------------------
 # Packed sequences
 # ---------------------------------------------------------------------------------------------
@@ -289,7 +325,7 @@ def test_varlen_with_an_empty_sequence(ext):
 
 def test_config3_varlen_16_sequences(ext):
     """16 sequences, lengths uniform in [64, 4096] (seed 2), H=16, d=128, causal, forward + backward at
-    full size; the oracle checks two of the 16 heads on every sequence."""
+    full size; the oracle checks four of the 16 heads on every sequence."""
     gl = torch.Generator().manual_seed(2)
     lens = torch.randint(64, 4097, (16,), generator=gl).tolist()
     total, H, d = sum(lens), 16, 128
@@ -302,7 +338,7 @@ def test_config3_varlen_16_sequences(ext):
     dq, dk, dv = ext.backward_varlen(do, q, k, v, o, lse, cuc, cuc, max(lens), max(lens), scale, True)
     for t in (o, lse, dq, dk, dv):
         assert torch.isfinite(t).all()
-    for h in (0, 9):
+    for h in (0, 5, 9, 15):
         sl = slice(h, h + 1)
         qs, ks, vs, gs = (t[:, sl].cpu() for t in (q, k, v, do))
         check_fwd(o[:, sl], lse[:, sl], *orc.varlen_fwd(qs, ks, vs, cu, cu, scale, True))
@@ -414,7 +450,7 @@ def test_decode_step_replayed_as_a_cuda_graph(ext):
 def test_config4_decode_256_steps_with_appends(ext):
     """batch 64, Hq=32, Hkv=8, d=128, caches [64,32768,8,128], lengths uniform in [1024, 32768-256]
     (clamped so that 256 appended tokens fit), 256 decode steps with appends.  The oracle checks
-    three batch entries at steps 0, 128 and 255."""
+    eight batch entries (the shortest and the longest among them) at steps 0, 64, 128, 192 and 255."""
     B, Hq, Hkv, S, d, steps = 64, 32, 8, 32768, 128, 256
     gen = torch.Generator(device="cuda").manual_seed(3)
     kc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=gen)
@@ -422,14 +458,14 @@ def test_config4_decode_256_steps_with_appends(ext):
     lens = torch.randint(1024, S - steps + 1, (B,), device="cuda", generator=gen).to(torch.int32)
     lens[0], lens[1] = 1024, S - steps
     scale = 1 / math.sqrt(d)
-    picks = [0, 1, 37]
+    picks = [0, 1, 9, 22, 37, 45, 58, 63]
     for step in range(steps):
         q = torch.randn(B, Hq, d, device="cuda", dtype=torch.float16, generator=gen)
         kn = torch.randn(B, Hkv, d, device="cuda", dtype=torch.float16, generator=gen)
         vn = torch.randn(B, Hkv, d, device="cuda", dtype=torch.float16, generator=gen)
         o, lse = ext.decode(q, kc, vc, lens, scale, kn, vn, return_lse=True)
         lens += 1
-        if step in (0, 128, 255):
+        if step in (0, 64, 128, 192, 255):
             idx = torch.tensor(picks, device="cuda")
             o_ref, lse_ref = orc.decode_fwd(q[idx].cpu(), kc[idx].cpu(), vc[idx].cpu(), lens[idx].cpu(), scale)
             check_fwd(o[idx], lse[idx], o_ref, lse_ref)
@@ -442,11 +478,27 @@ def test_config4_decode_256_steps_with_appends(ext):
 # ---------------------------------------------------------------------------------------------
 # Long context (single GPU, sampled oracle)
 # ---------------------------------------------------------------------------------------------
+def _rows_closed_form(q_rows, g_rows, kf, vf, scale, r0, r1):
+    """fp32 statistics of query rows [r0, r1) of a causal problem against keys [0, r1): the probabilities
+    P, dS = P o (dP - rowsum(dO o O)) and the rows' own O (the closed form of ref_backward,
+    tests/test_flash_attn.py:35-58 of the reference, restricted to a row block)."""
+    s = torch.matmul(q_rows, kf.transpose(-1, -2)) * scale
+    rows = torch.arange(r0, r1).view(-1, 1)
+    s.masked_fill_(torch.arange(kf.shape[2]).view(1, -1) > rows, float("-inf"))
+    p = torch.softmax(s, -1)
+    o = torch.matmul(p, vf)
+    ds = p * (torch.matmul(g_rows, vf.transpose(-1, -2)) - (g_rows * o).sum(-1, keepdim=True))
+    return p, ds
+
+
 def test_config5_long_context_sampled(ext):
     """B=1, Hq=32, Hkv=8, N=131072, d=128, causal forward + backward on one GPU.  One score matrix row
     block of one head is 0.5 GB in fp32, so the oracle checks O, LSE and dQ on sampled 256-row blocks
-    of one KV-head group (dQ rows depend only on their own row block); dK/dV are checked for
-    finiteness here and exactly at smaller sizes by the tests above."""
+    of one KV-head group (dQ rows depend only on their own row block), dK and dV of the group's LAST
+    256 keys (they depend only on the last 256 query rows), and dK and dV of a 256-key block three
+    quarters into the sequence, for which a second backward is run with dO zeroed outside one query
+    head -- that block's gradient then comes from that head's 32 896 later rows alone, which the
+    oracle can afford."""
     B, Hq, Hkv, N, d = 1, 32, 8, 131072, 128
     gen = torch.Generator(device="cuda").manual_seed(4)
     q = torch.randn(B, Hq, N, d, device="cuda", generator=gen).half()
@@ -470,14 +522,36 @@ def test_config5_long_context_sampled(ext):
         # dQ of the block: closed form on the block's rows
         kf, vf = kh[:, :, :r1].float(), vh[:, :, :r1].float()
         qf, gf = q[:, sl, r0:r1].cpu().float(), do[:, sl, r0:r1].cpu().float()
-        s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
-        rows = torch.arange(r0, r1).view(-1, 1)
-        s.masked_fill_(torch.arange(r1).view(1, -1) > rows, float("-inf"))
-        p = torch.softmax(s, -1)
-        ds = p * (torch.matmul(gf, vf.transpose(-1, -2)) - (gf * torch.matmul(p, vf)).sum(-1, keepdim=True))
+        p, ds = _rows_closed_form(qf, gf, kf, vf, scale, r0, r1)
         dq_ref = torch.matmul(ds, kf) * scale
         assert orc.rel_max_err(dq[:, sl, r0:r1], dq_ref) <= orc.TOL_GRAD
-    del q, k, v, do, o, dq, dk, dv
+        if r1 == N:
+            # the last 256 keys are seen by the last 256 queries only: their dK / dV in closed form,
+            # summed over the group's four query heads
+            dk_ref = (torch.matmul(ds[..., r0:r1].transpose(-1, -2), qf) * scale).sum(1, keepdim=True)
+            dv_ref = torch.matmul(p[..., r0:r1].transpose(-1, -2), gf).sum(1, keepdim=True)
+            assert orc.rel_max_err(dk[:, h:h + 1, r0:r1], dk_ref) <= orc.TOL_GRAD
+            assert orc.rel_max_err(dv[:, h:h + 1, r0:r1], dv_ref) <= orc.TOL_GRAD
+
+    # ---- a key block in mid-sequence: gradient through ONE query head ------------------------
+    hq = 4 * h + 1
+    do_one = torch.zeros_like(do)
+    do_one[:, hq] = do[:, hq]
+    _, dk1, dv1 = ext.backward(do_one, q, k, v, o, lse, scale, True)
+    assert ext.device_status() == 0
+    kb0, kb1 = 98176, 98432
+    qh, gh = q[:, hq:hq + 1].cpu().float(), do[:, hq:hq + 1].cpu().float()
+    kf, vf = kh.float(), vh.float()
+    dk_ref = torch.zeros(1, 1, kb1 - kb0, d)
+    dv_ref = torch.zeros(1, 1, kb1 - kb0, d)
+    for r0 in range(kb0, N, 1024):   # rows before kb0 do not see the block
+        r1 = min(N, r0 + 1024)
+        p, ds = _rows_closed_form(qh[:, :, r0:r1], gh[:, :, r0:r1], kf[:, :, :r1], vf[:, :, :r1], scale, r0, r1)
+        dk_ref += torch.matmul(ds[..., kb0:kb1].transpose(-1, -2), qh[:, :, r0:r1]) * scale
+        dv_ref += torch.matmul(p[..., kb0:kb1].transpose(-1, -2), gh[:, :, r0:r1])
+    assert orc.rel_max_err(dk1[:, h:h + 1, kb0:kb1], dk_ref) <= orc.TOL_GRAD
+    assert orc.rel_max_err(dv1[:, h:h + 1, kb0:kb1], dv_ref) <= orc.TOL_GRAD
+    del q, k, v, do, do_one, o, dq, dk, dv, dk1, dv1
     torch.cuda.empty_cache()
 
 

@@ -12,9 +12,14 @@ every other test.
 """
 import ctypes
 import math
+import os
+import subprocess
+import sys
 
 import pytest
 import torch
+
+from oracle import attention_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
@@ -56,7 +61,44 @@ def test_static_decode_matches_regular_decode_on_two_calls_in_a_row(ext):
         assert (lse - lse_ref).abs().max().item() <= 1e-3
         assert torch.equal(out, o_ref)
         assert torch.equal(kc2, kc) and torch.equal(vc2, vc)   # the append wrote the same rows
+        # and against the CPU oracle, so that this file stands on its own
+        seen = lens.cpu() + (1 if kn is not None else 0)
+        o_orc, lse_orc = orc.decode_fwd(q.cpu(), kc2.cpu(), vc2.cpu(), seen, scale)
+        assert orc.rel_max_err(out, o_orc) <= orc.TOL_O and orc.abs_max_err(lse, lse_orc) <= orc.TOL_LSE
     assert ext.device_status() == 0
+
+
+_FRESH_PROCESS = r"""
+import math, torch
+import flash_attn_legacy_cuda as ext
+g = torch.Generator().manual_seed(5)
+B, Hq, Hkv, S, d = 2, 8, 2, 1500, 128
+mk = lambda *shape: torch.randn(*shape, generator=g).half().cuda()
+q, kc, vc, kn, vn = mk(B, Hq, d), mk(B, S, Hkv, d), mk(B, S, Hkv, d), mk(B, Hkv, d), mk(B, Hkv, d)
+lens = torch.tensor([1499, 3], dtype=torch.int32).cuda()
+out = torch.empty(B, Hq, d, dtype=torch.float16, device="cuda")
+lse = torch.empty(B, Hq, dtype=torch.float32, device="cuda")
+ext.reset_device_status()          # start-up: creates the 4-byte status word, the module's only allocation
+torch.cuda.synchronize()
+before, reserved = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+ext.decode_static(q, kc, vc, lens, 1 / math.sqrt(d), out, kn, vn, lse=lse)   # the FIRST call in this process
+torch.cuda.synchronize()
+assert torch.cuda.memory_allocated() == before and torch.cuda.memory_reserved() == reserved
+ref = ext.decode(q, kc.clone(), vc.clone(), lens + 1, 1 / math.sqrt(d))
+assert torch.equal(out, ref)
+assert ext.device_status() == 0
+print("FRESH-OK")
+"""
+
+
+def test_first_static_call_of_a_process_allocates_nothing():
+    """In a process of its own, so that no earlier call has warmed anything up: after the status word
+    exists, the very first decode_static call leaves torch's allocator untouched."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([os.path.join(root, "flash-attention-legacy_b200"), root,
+                                                       os.environ.get("PYTHONPATH", "")]))
+    res = subprocess.run([sys.executable, "-c", _FRESH_PROCESS], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "FRESH-OK" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
 
 
 def test_static_decode_rejects_problems_beyond_its_scratch(ext):
