@@ -330,8 +330,7 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   if (num_seqs <= 0 || total_q <= 0 || total_k < 0 || heads_q <= 0 || heads_kv <= 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  // the packed kernels know the reference's top-left-aligned mask only
-  if (is_causal != FAL_CAUSAL_NONE && is_causal != FAL_CAUSAL_TOP_LEFT) return FAL_ERR_INVALID_ARGUMENT;
+  if (is_causal < 0 || is_causal > FAL_CAUSAL_BOTTOM_RIGHT) return FAL_ERR_INVALID_ARGUMENT;
   if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
       o_strides->head % 8 != 0)
@@ -360,6 +359,7 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   p.heads_kv = heads_kv;
   p.seqlen_q = 0;
   p.seqlen_k = 0;
+  p.shift_per_sequence = is_causal == FAL_CAUSAL_BOTTOM_RIGHT ? 1 : 0;
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
@@ -414,8 +414,9 @@ int run_bwd(const BwdCall& c) {
   if (c.batch <= 0 || c.heads_q <= 0 || c.heads_kv <= 0 || c.rows_q <= 0 || c.rows_k <= 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (c.heads_q % c.heads_kv != 0 || !(c.scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  // no backward exists for the bottom-right-aligned mask: refuse it instead of masking top-left
-  if (c.causal != FAL_CAUSAL_NONE && c.causal != FAL_CAUSAL_TOP_LEFT) return FAL_ERR_INVALID_ARGUMENT;
+  if (c.causal < 0 || c.causal > FAL_CAUSAL_BOTTOM_RIGHT) return FAL_ERR_INVALID_ARGUMENT;
+  // the bottom-right-aligned mask is defined for a query block that ends where the keys end
+  if (c.causal == FAL_CAUSAL_BOTTOM_RIGHT && c.cu_q == nullptr && c.rows_k < c.rows_q) return FAL_ERR_INVALID_ARGUMENT;
   if (!head_dim_ok(c.head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   auto out_ok = [](const void* ptr, const fal::RowStrides& s) {
     return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && s.row % 8 == 0 && s.head % 8 == 0 &&
@@ -495,6 +496,8 @@ int run_bwd(const BwdCall& c) {
   p.seqlen_q = c.cu_q ? 0 : c.rows_q;
   p.seqlen_k = c.cu_k ? 0 : c.rows_k;
   p.num_kvblk = c.cu_k ? (c.rows_k / 128 + c.num_seqs) : (c.rows_k + 127) / 128;
+  p.causal_shift = (c.causal == FAL_CAUSAL_BOTTOM_RIGHT && !c.cu_k) ? c.rows_k - c.rows_q : 0;
+  p.shift_per_sequence = (c.causal == FAL_CAUSAL_BOTTOM_RIGHT && c.cu_k) ? 1 : 0;
   p.scale = c.scale;
   p.scale_log2 = c.scale * 1.4426950408889634f;
   p.status = c.status;

@@ -239,7 +239,11 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int group = p.heads_q / p.heads_kv;
   const int kv0 = wk.kvblk * kKvTile;                       // local index of the tile's first key
   const int nqt = (wk.seqlen_q + kQTile - 1) / kQTile;
-  const int qt0 = CAUSAL ? min(kv0 / kQTile, nqt) : 0;      // first query tile that sees this key tile
+  // Keys the causal diagonal is moved by: query i sees keys <= i + cshift (0 = the reference's
+  // top-left-aligned mask; seqlen_k - seqlen_q aligns it to the end of the keys).
+  const int cshift = !CAUSAL ? 0
+                     : (p.cu_k != nullptr ? (p.shift_per_sequence ? wk.seqlen_k - wk.seqlen_q : 0) : p.causal_shift);
+  const int qt0 = CAUSAL ? min(max(kv0 - cshift, 0) / kQTile, nqt) : 0;  // first query tile that sees this key tile
   const int nq = nqt - qt0;                                  // query tiles per head
   const int n_iter = group * nq;
 
@@ -528,7 +532,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int qt = qt0 + i % nq;
       const int q_col0 = qt * kQTile + half * 64;  // local query index of this thread's first column
       const float* stat = reinterpret_cast<const float*>(sgen + L::kStatOff) + st * 2 * kQTile + half * 64;
-      const bool tile_mask = !kv_ok || (CAUSAL && (kv0 + kKvTile - 1 > qt * kQTile));
+      const bool tile_mask = !kv_ok || (CAUSAL && (kv0 + kKvTile - 1 > qt * kQTile + cshift));
 
       mbar_wait(bar(iStatFull + st), (i / NS) & 1, wctx, kBbStatFull + st);
       mbar_wait(bar(iSReady), i & 1, wctx, kBbSReady);
@@ -546,7 +550,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const bool vis = kv_ok && (!CAUSAL || kv_local <= q_col0 + c * 32 + j);
+              const bool vis = kv_ok && (!CAUSAL || kv_local <= q_col0 + cshift + c * 32 + j);
               r[c][j] = vis ? r[c][j] : 0xff800000u;
             }
         }

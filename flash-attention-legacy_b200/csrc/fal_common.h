@@ -34,7 +34,8 @@ struct FwdParams {
   int seqlen_k;   // batched mode only
   int cta_rows;   // query rows per CTA: 256 (two tiles) or 128 (one tile, both softmax warpgroups on it)
   int num_qblk;   // batched: ceil(seqlen_q / cta_rows); packed: bound on all sequences' blocks
-  int causal_shift;  // causal kernels: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
+  int causal_shift;  // causal kernels, batched: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
+  int shift_per_sequence;  // causal kernels, packed: the shift of a sequence is its seqlen_k - seqlen_q
   float scale;       // softmax scale
   float scale_log2;  // softmax scale * log2(e)
   int* status;       // device status word, may be nullptr
@@ -66,6 +67,8 @@ struct BwdParams {
   int seqlen_q;
   int seqlen_k;
   int num_kvblk;  // batched: ceil(seqlen_k / 128); packed: bound over all sequences
+  int causal_shift;        // causal, batched: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
+  int shift_per_sequence;  // causal, packed: the shift of a sequence is its seqlen_k - seqlen_q
   float scale;
   float scale_log2;
   int* status;

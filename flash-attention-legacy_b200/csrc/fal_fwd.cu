@@ -216,7 +216,7 @@ __device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, int cta_rows
   return true;
 }
 
-// SHIFTED (causal only): the mask's diagonal is moved by p.causal_shift keys (bottom-right
+// SHIFTED (causal only): the mask's diagonal is moved by seqlen_k - seqlen_q keys (bottom-right
 // alignment); the kernels of the reference's own top-left mask are compiled without it.
 template <int D, bool CAUSAL, bool SHIFTED, bool ONE_TILE>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -244,6 +244,8 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  // SHIFTED: keys the causal diagonal is moved by (batched: one value; packed: per sequence).
+  const int cshift = SHIFTED ? (p.cu_q != nullptr ? wk.seqlen_k - wk.seqlen_q : p.causal_shift) : 0;
   // Number of key tiles each 128-row query tile visits.
   const int nk_tiles = (wk.seqlen_k + kTileN - 1) / kTileN;
   int ntile[2];
@@ -253,7 +255,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     int n = 0;
     if (w < L::kQTiles && row0 < wk.seqlen_q) {
       n = nk_tiles;
-      if (CAUSAL) n = min(n, SHIFTED ? (row0 + kTileM - 1 + p.causal_shift) / kTileN + 1 : row0 / kTileN + 1);
+      if (CAUSAL) n = min(n, SHIFTED ? max(row0 + kTileM - 1 + cshift, 0) / kTileN + 1 : row0 / kTileN + 1);
     }
     ntile[w] = n;
   }
@@ -443,7 +445,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after_sync();
         const int kv0 = j * kTileN;
         int limit = wk.seqlen_k - kv0;  // columns c < limit of the tile are visible
-        const int cshift = SHIFTED ? p.causal_shift : 0;
         if (CAUSAL) limit = min(limit, q_local + cshift - kv0 + 1);
         limit -= ch * 64;  // in this thread's own 64 columns
         const bool tile_mask =
@@ -617,7 +618,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_after_sync();
       const int kv0 = j * kTileN;
       int limit = wk.seqlen_k - kv0;  // columns c < limit are visible
-      const int cshift = SHIFTED ? p.causal_shift : 0;
       if (CAUSAL) limit = min(limit, q_local + cshift - kv0 + 1);
       const bool tile_mask =
           (kv0 + kTileN > wk.seqlen_k) || (CAUSAL && (kv0 + kTileN - 1 > q_tile0 + cshift));
@@ -815,7 +815,8 @@ cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
 template <int D, bool ONE_TILE>
 cudaError_t launch_fwd_d(bool causal, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const FwdParams& p, int grid, cudaStream_t stream) {
-  if (causal && p.causal_shift != 0) return launch_fwd_t<D, true, true, ONE_TILE>(tq, tk, tv, p, grid, stream);
+  if (causal && (p.causal_shift != 0 || p.shift_per_sequence != 0))
+    return launch_fwd_t<D, true, true, ONE_TILE>(tq, tk, tv, p, grid, stream);
   return causal ? launch_fwd_t<D, true, false, ONE_TILE>(tq, tk, tv, p, grid, stream)
                 : launch_fwd_t<D, false, false, ONE_TILE>(tq, tk, tv, p, grid, stream);
 }

@@ -131,6 +131,32 @@ def flash_attention(
     return FlashAttentionFunc.apply(q, k, v, softmax_scale, is_causal, out_layout)
 
 
+class FlashAttentionChunkFunc(Function):
+    """Causal attention of the LAST Nq positions of a sequence against all its Nk keys (mask aligned to
+    the end of the keys), with its backward.  Not in the reference, whose hook computes this case
+    eagerly with a top-left mask (integrations.py:77-98)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, out_layout="bhnd"):
+        q, k, v = _kernel_ready(q), _kernel_ready(k), _kernel_ready(v)
+        out = None
+        if out_layout == "bnhd":
+            b, h_q, n, d = q.shape
+            out = torch.empty((b, n, h_q, d), dtype=q.dtype, device=q.device).transpose(1, 2)
+        o, lse = flash_attn_legacy_cuda.forward_rect(q, k, v, softmax_scale, True, bottom_right=True, out=out)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.softmax_scale = softmax_scale
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = flash_attn_legacy_cuda.backward(
+            _kernel_ready(grad_output), q, k, v, o, lse, ctx.softmax_scale, True, bottom_right=True
+        )
+        return dq, dk, dv, None, None
+
+
 def flash_attention_chunk(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -138,14 +164,14 @@ def flash_attention_chunk(
     softmax_scale: Optional[float] = None,
     out_layout: str = "bhnd",
 ) -> torch.Tensor:
-    """Causal attention of a prompt chunk against a longer key sequence (inference only).
+    """Causal attention of a prompt chunk against a longer key sequence.
 
     q [B,Hq,Nq,d] holds the LAST Nq positions of the sequence whose keys and values are
     k, v [B,Hkv,Nk,d] with Nk >= Nq: query i sees keys j <= i + (Nk - Nq) (the causal mask is
     aligned to the bottom-right corner).  This is the step between prefill and single-token
     decode -- prefill in chunks, or a few new tokens after a cached prefix -- which the reference
     sends to its eager fallback with its usual top-left mask (integrations.py:63, :77-98).
-    Not in the reference's API; there is no backward for it.  Head dims 64, 128, 256.
+    Not in the reference's API.  Differentiable; head dims 64, 128, 256.
     """
     assert q.dtype == torch.float16 and k.dtype == torch.float16 and v.dtype == torch.float16
     assert q.is_cuda and q.dim() == 4
@@ -156,14 +182,7 @@ def flash_attention_chunk(
     assert out_layout in ("bhnd", "bnhd"), f"out_layout must be 'bhnd' or 'bnhd', got {out_layout}"
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(d)
-    out = None
-    if out_layout == "bnhd":
-        b, h_q, n, _ = q.shape
-        out = torch.empty((b, n, h_q, d), dtype=q.dtype, device=q.device).transpose(1, 2)
-    with torch.no_grad():
-        o, _ = flash_attn_legacy_cuda.forward_rect(_kernel_ready(q), _kernel_ready(k), _kernel_ready(v),
-                                                   softmax_scale, True, bottom_right=True, out=out)
-    return o
+    return FlashAttentionChunkFunc.apply(q, k, v, softmax_scale, out_layout)
 
 
 class FlashAttnVarlenFunc(Function):
@@ -175,7 +194,7 @@ class FlashAttnVarlenFunc(Function):
 
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                softmax_scale, is_causal):
+                softmax_scale, is_causal, bottom_right=False):
         assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
         assert q.is_cuda and q.dim() == 3
         d = q.shape[-1]
@@ -185,11 +204,13 @@ class FlashAttnVarlenFunc(Function):
         cu_seqlens_q = cu_seqlens_q.contiguous().to(torch.int32)
         cu_seqlens_k = cu_seqlens_k.contiguous().to(torch.int32)
         o, lse = flash_attn_legacy_cuda.forward_varlen(
-            q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, is_causal
+            q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, is_causal,
+            bottom_right=bottom_right,
         )
         ctx.save_for_backward(q, k, v, o, lse, cu_seqlens_q, cu_seqlens_k)
         ctx.softmax_scale = softmax_scale
         ctx.is_causal = is_causal
+        ctx.bottom_right = bottom_right
         ctx.max_seqlen_q = max_seqlen_q
         ctx.max_seqlen_k = max_seqlen_k
         return o
@@ -200,8 +221,9 @@ class FlashAttnVarlenFunc(Function):
         dq, dk, dv = flash_attn_legacy_cuda.backward_varlen(
             grad_output.contiguous(), q, k, v, o, lse, cu_q, cu_k,
             ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.softmax_scale, ctx.is_causal,
+            bottom_right=ctx.bottom_right,
         )
-        return dq, dk, dv, None, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None, None
 
 
 def flash_attn_varlen_func(
@@ -214,6 +236,7 @@ def flash_attn_varlen_func(
     max_seqlen_k: int,
     softmax_scale: Optional[float] = None,
     causal: bool = False,
+    causal_bottom_right: bool = False,
 ) -> torch.Tensor:
     """Attention over sequences packed along the token axis (no padding).
 
@@ -221,7 +244,10 @@ def flash_attn_varlen_func(
     cumulative lengths.  Returns [total_q,H,d].  Same contract as the reference's
     flash_attn_varlen_func (flash_attn.py:162-220).  The causal mask is aligned to the
     top-left corner of each sequence's score matrix (key j hidden when j > i), as in
-    the reference kernels (flash_attn_fwd_volta.cu:448-451).
+    the reference kernels (flash_attn_fwd_volta.cu:448-451).  `causal_bottom_right=True`
+    (not in the reference) aligns it to the bottom-right corner instead: a sequence's queries
+    are the last len_q positions of its len_k keys -- ragged chunks of new tokens behind
+    ragged cached prefixes.
     """
     assert q.dim() == 3, f"q must be [total, heads, d], got shape {q.shape}"
     assert k.dim() == 3, f"k must be [total, heads_k, d], got shape {k.shape}"
@@ -235,10 +261,10 @@ def flash_attn_varlen_func(
     if dn != d:
         out = FlashAttnVarlenFunc.apply(_pad_last(q, dn), _pad_last(k, dn), _pad_last(v, dn),
                                         cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                                        softmax_scale, causal)
+                                        softmax_scale, causal, causal_bottom_right)
         return out[..., :d]
     return FlashAttnVarlenFunc.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                                     softmax_scale, causal)
+                                     softmax_scale, causal, causal_bottom_right)
 
 
 def flash_attn_with_kvcache(

@@ -15,7 +15,7 @@ mask at all, and the reference attends to padding (integrations.py:63-76) -- and
 with such a mask runs un-padded through the packed kernels.  Everything the kernels do not
 cover (an additive 4-D mask, a padding mask outside prefill, unsupported head_dim) keeps the
 reference's eager arithmetic.  A third difference: several new tokens against a longer cache
-(q_len > 1, kv_len > q_len, causal, no mask, no autograd) run through the forward kernel with
+(q_len > 1, kv_len > q_len, causal, no mask) run through the kernels (forward and backward) with
 the causal mask aligned to the END of the key sequence -- the new tokens are its last q_len
 positions -- where the reference's fallback applies its top-left mask (integrations.py:91-96),
 which hides the cached prefix from the first new tokens.  The eager fallback here aligns its
@@ -161,8 +161,7 @@ def flash_attn_legacy_forward(
         out = flash_attention(to_half(query), to_half(key), to_half(value),
                               softmax_scale=scaling, is_causal=is_causal, out_layout="bnhd")
         out = out.to(in_dtype).transpose(1, 2).contiguous()  # no-op for fp16 models
-    elif (1 < q_len < kv_len and attention_mask is None and is_causal and query.is_cuda
-          and d in _DECODE_HEAD_DIMS and not (torch.is_grad_enabled() and query.requires_grad)):
+    elif 1 < q_len < kv_len and attention_mask is None and is_causal and query.is_cuda and d in _DECODE_HEAD_DIMS:
         # A chunk of new tokens against a cache that holds earlier ones.
         out = flash_attention_chunk(to_half(query), to_half(key), to_half(value),
                                     softmax_scale=scaling, out_layout="bnhd")

@@ -267,12 +267,18 @@ def forward_rect(Q, K, V, softmax_scale, is_causal=False, bottom_right=False, ou
     return [O, L]
 
 
+def _causal_code(is_causal, bottom_right):
+    return (2 if bottom_right else 1) if is_causal else 0
+
+
 def forward_varlen(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale,
-                   is_causal=False):
+                   is_causal=False, bottom_right=False):
     """Packed forward.  Q [total_q,Hq,d], K/V [total_k,Hkv,d] -> [O [total_q,Hq,d], L [total_q,Hq]].
 
     Same contract as the reference's `forward_varlen` (csrc/flash_attn_legacy.cpp:193-290), but
     cu_seqlens stay on the device: there is no device-to-host copy or synchronisation.
+    `bottom_right` aligns each sequence's causal mask to the end of its keys (query i sees keys
+    j <= i + len_k - len_q) instead of the reference's top-left alignment.
     """
     _require_cuda_half("Q", Q, 3)
     _require_cuda_half("K", K, 3)
@@ -293,7 +299,7 @@ def forward_varlen(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen
                                cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), num_seqs,
                                total_q, total_k, int(max_seqlen_q), int(max_seqlen_k), Hq, Hkv, d,
                                _packed_strides(Q), _packed_strides(K), _packed_strides(V),
-                               _packed_strides(O), float(softmax_scale), int(bool(is_causal)),
+                               _packed_strides(O), float(softmax_scale), _causal_code(is_causal, bottom_right),
                                _status_word(Q.device).data_ptr(), _stream(Q)))
     return [O, L]
 
@@ -303,12 +309,13 @@ def backward_workspace_bytes(B, Hq, rows, d):
     return int(_lib.fal_bwd_workspace_bytes(B, Hq, rows, d))
 
 
-def backward(dO, Q, K, V, O, L, softmax_scale, is_causal=False, out=None, workspace=None):
+def backward(dO, Q, K, V, O, L, softmax_scale, is_causal=False, out=None, workspace=None, bottom_right=False):
     """Batched backward -> [dQ [B,Hq,N,d], dK [B,Hkv,N,d], dV [B,Hkv,N,d]] fp16.
 
     Same contract as the reference's `backward` (csrc/flash_attn_legacy.cpp:105-186).
     `out` (a [dQ, dK, dV] list) and `workspace` (uint8, backward_workspace_bytes long,
-    256-byte aligned) let a caller reuse buffers across calls.
+    256-byte aligned) let a caller reuse buffers across calls.  `bottom_right`: the causal mask of
+    `forward_rect(..., bottom_right=True)` (needs Nk >= Nq).
     """
     for name, t in (("dO", dO), ("Q", Q), ("K", K), ("V", V), ("O", O)):
         _require_cuda_half(name, t, 4)
@@ -334,13 +341,13 @@ def backward(dO, Q, K, V, O, L, softmax_scale, is_causal=False, out=None, worksp
                         B, Hq, Hkv, Nq, Nk, d,
                         _bhn_strides(dO), _bhn_strides(Q), _bhn_strides(K), _bhn_strides(V),
                         _bhn_strides(O), _bhn_strides(dQ), _bhn_strides(dK), _bhn_strides(dV),
-                        float(softmax_scale), int(bool(is_causal)),
+                        float(softmax_scale), _causal_code(is_causal, bottom_right),
                         ws.data_ptr(), nbytes, _status_word(Q.device).data_ptr(), _stream(Q)))
     return [dQ, dK, dV]
 
 
 def backward_varlen(dO, Q, K, V, O, L, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                    softmax_scale, is_causal=False):
+                    softmax_scale, is_causal=False, bottom_right=False):
     """Packed backward in one native call -> [dQ [total_q,Hq,d], dK, dV [total_k,Hkv,d]] fp16.
 
     Replaces the per-sequence Python loop of the reference
@@ -366,7 +373,7 @@ def backward_varlen(dO, Q, K, V, O, L, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
                                _packed_strides(dO), _packed_strides(Q), _packed_strides(K),
                                _packed_strides(V), _packed_strides(O), _packed_strides(dQ),
                                _packed_strides(dK), _packed_strides(dV),
-                               float(softmax_scale), int(bool(is_causal)),
+                               float(softmax_scale), _causal_code(is_causal, bottom_right),
                                ws.data_ptr(), nbytes, _status_word(Q.device).data_ptr(), _stream(Q)))
     return [dQ, dK, dV]
 

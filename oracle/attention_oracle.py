@@ -63,17 +63,18 @@ def attention_fwd(q, k, v, scale, causal=False, causal_shift=0):
     kf, vf = _expand_kv(k, reps), _expand_kv(v, reps)
     s = _scores(q, kf, scale, causal, causal_shift)
     lse = torch.logsumexp(s, dim=-1)
-    p = torch.softmax(s, dim=-1)
+    p = torch.softmax(s, dim=-1).nan_to_num(nan=0.0)  # a row that sees no key: O = 0, LSE = -inf
     return torch.matmul(p, vf.float()), lse
 
 
-def attention_bwd(q, k, v, d_out, scale, causal=False):
-    """Closed-form gradients -> (dQ [B,Hq,Nq,d], dK [B,Hkv,Nk,d], dV [B,Hkv,Nk,d]) fp32."""
+def attention_bwd(q, k, v, d_out, scale, causal=False, causal_shift=0):
+    """Closed-form gradients -> (dQ [B,Hq,Nq,d], dK [B,Hkv,Nk,d], dV [B,Hkv,Nk,d]) fp32.
+    `causal_shift`: as in attention_fwd."""
     hq, hkv = q.shape[1], k.shape[1]
     reps = hq // hkv
     kf, vf = _expand_kv(k, reps).float(), _expand_kv(v, reps).float()
     qf, gf = q.float(), d_out.float()
-    p = torch.softmax(_scores(q, kf, scale, causal), dim=-1)
+    p = torch.softmax(_scores(q, kf, scale, causal, causal_shift), dim=-1).nan_to_num(nan=0.0)  # rows that see no key
     o = torch.matmul(p, vf)
     dv_full = torch.matmul(p.transpose(-2, -1), gf)
     dp = torch.matmul(gf, vf.transpose(-2, -1))
@@ -92,20 +93,23 @@ def _seq_bounds(cu):
     return list(zip(cu[:-1], cu[1:]))
 
 
-def varlen_fwd(q, k, v, cu_q, cu_k, scale, causal=False):
-    """Packed q [total_q,Hq,d], k/v [total_k,Hkv,d] -> (O fp32 [total_q,Hq,d], LSE fp32 [total_q,Hq])."""
+def varlen_fwd(q, k, v, cu_q, cu_k, scale, causal=False, bottom_right=False):
+    """Packed q [total_q,Hq,d], k/v [total_k,Hkv,d] -> (O fp32 [total_q,Hq,d], LSE fp32 [total_q,Hq]).
+    `bottom_right`: each sequence's causal mask is aligned to the end of its keys (causal_shift =
+    len_k - len_q per sequence) instead of the reference's top-left alignment."""
     outs, lses = [], []
     for (qs, qe), (ks, ke) in zip(_seq_bounds(cu_q), _seq_bounds(cu_k)):
+        shift = (ke - ks) - (qe - qs) if bottom_right else 0
         qi = q[qs:qe].permute(1, 0, 2).unsqueeze(0)
         ki = k[ks:ke].permute(1, 0, 2).unsqueeze(0)
         vi = v[ks:ke].permute(1, 0, 2).unsqueeze(0)
-        oi, li = attention_fwd(qi, ki, vi, scale, causal)
+        oi, li = attention_fwd(qi, ki, vi, scale, causal, shift)
         outs.append(oi.squeeze(0).permute(1, 0, 2))
         lses.append(li.squeeze(0).permute(1, 0))
     return torch.cat(outs, dim=0), torch.cat(lses, dim=0)
 
 
-def varlen_bwd(q, k, v, d_out, cu_q, cu_k, scale, causal=False):
+def varlen_bwd(q, k, v, d_out, cu_q, cu_k, scale, causal=False, bottom_right=False):
     dq = torch.zeros(q.shape, dtype=torch.float32)
     dk = torch.zeros(k.shape, dtype=torch.float32)
     dv = torch.zeros(v.shape, dtype=torch.float32)
@@ -114,7 +118,7 @@ def varlen_bwd(q, k, v, d_out, cu_q, cu_k, scale, causal=False):
         ki = k[ks:ke].permute(1, 0, 2).unsqueeze(0)
         vi = v[ks:ke].permute(1, 0, 2).unsqueeze(0)
         gi = d_out[qs:qe].permute(1, 0, 2).unsqueeze(0)
-        a, b, c = attention_bwd(qi, ki, vi, gi, scale, causal)
+        a, b, c = attention_bwd(qi, ki, vi, gi, scale, causal, (ke - ks) - (qe - qs) if bottom_right else 0)
         dq[qs:qe] = a.squeeze(0).permute(1, 0, 2)
         dk[ks:ke] = b.squeeze(0).permute(1, 0, 2)
         dv[ks:ke] = c.squeeze(0).permute(1, 0, 2)

@@ -88,21 +88,23 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     # misaligned output pointer
     assert lib.fal_fwd(fake, fake, fake, fake + 2, fake, 1, 2, 2, 128, 128, 64, st, st, st, st, 0.125, 0, None, None) == -1
 
-    # the bottom-right-aligned mask (2) exists for the batched forward only: the packed forward and both
-    # backward entry points refuse it instead of silently masking top-left
+    # causal modes outside {0, 1, 2} are refused everywhere; the batched backward refuses the
+    # bottom-right-aligned mask when there are fewer keys than queries, like the forward
     cu = fake
     lib.fal_fwd_varlen.restype = i
     lib.fal_fwd_varlen.argtypes = [vp] * 7 + [i] * 8 + [sp] * 4 + [f, i, vp, vp]
     assert lib.fal_fwd_varlen(fake, fake, fake, fake, fake, cu, cu, 1, 128, 128, 128, 128, 2, 2, 64,
-                              st, st, st, st, 0.125, 2, None, None) == -1
+                              st, st, st, st, 0.125, 3, None, None) == -1
     lib.fal_bwd.restype = i
     lib.fal_bwd.argtypes = [vp] * 9 + [i] * 6 + [sp] * 8 + [f, i, vp, ctypes.c_size_t, vp, vp]
-    assert lib.fal_bwd(fake, fake, fake, fake, fake, fake, fake, fake, fake, 1, 2, 2, 128, 128, 64,
+    assert lib.fal_bwd(fake, fake, fake, fake, fake, fake, fake, fake, fake, 1, 2, 2, 128, 64, 64,
                        st, st, st, st, st, st, st, st, 0.125, 2, fake, 1 << 30, None, None) == -1
+    assert lib.fal_bwd(fake, fake, fake, fake, fake, fake, fake, fake, fake, 1, 2, 2, 128, 128, 64,
+                       st, st, st, st, st, st, st, st, 0.125, 3, fake, 1 << 30, None, None) == -1
     lib.fal_bwd_varlen.restype = i
     lib.fal_bwd_varlen.argtypes = [vp] * 9 + [vp, vp] + [i] * 8 + [sp] * 8 + [f, i, vp, ctypes.c_size_t, vp, vp]
     assert lib.fal_bwd_varlen(fake, fake, fake, fake, fake, fake, fake, fake, fake, cu, cu, 1, 128, 128, 128, 128,
-                              2, 2, 64, st, st, st, st, st, st, st, st, 0.125, 2, fake, 1 << 30, None, None) == -1
+                              2, 2, 64, st, st, st, st, st, st, st, st, 0.125, -1, fake, 1 << 30, None, None) == -1
 
     lib.fal_decode.restype = i
     lib.fal_decode.argtypes = [vp, vp, vp, sp, sp, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp, ctypes.c_size_t, vp, vp]

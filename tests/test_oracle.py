@@ -134,6 +134,25 @@ def test_shifted_causal_mask_is_the_tail_of_the_square_problem():
         o, lse = orc.attention_fwd(q[:, :, -nq:], k, v, 0.2, True, causal_shift=300 - nq)
         assert torch.allclose(o, o_full[:, :, -nq:], atol=1e-6)
         assert torch.allclose(lse, lse_full[:, :, -nq:], atol=1e-6)
+    # gradients too: a gradient that is zero outside the last nq rows of the square problem gives the
+    # chunk's dQ on those rows and the chunk's dK, dV
+    do = torch.randn(2, 4, 300, 32, generator=g).half()
+    for nq in (1, 77):
+        do_tail = torch.zeros_like(do)
+        do_tail[:, :, -nq:] = do[:, :, -nq:]
+        dq_f, dk_f, dv_f = orc.attention_bwd(q, k, v, do_tail, 0.2, True)
+        dq, dk, dv = orc.attention_bwd(q[:, :, -nq:], k, v, do[:, :, -nq:], 0.2, True, causal_shift=300 - nq)
+        assert torch.allclose(dq, dq_f[:, :, -nq:], atol=1e-5)
+        assert torch.allclose(dk, dk_f, atol=1e-5) and torch.allclose(dv, dv_f, atol=1e-5)
+    # packed form: per-sequence shifts; a sequence with more queries than keys has rows that see nothing
+    cu_q, cu_k = torch.tensor([0, 5, 12]), torch.tensor([0, 9, 12])
+    qp, kp, vp = torch.randn(12, 2, 8, generator=g), torch.randn(12, 2, 8, generator=g), torch.randn(12, 2, 8, generator=g)
+    o, lse = orc.varlen_fwd(qp, kp, vp, cu_q, cu_k, 0.3, True, bottom_right=True)
+    o0, _ = orc.attention_fwd(qp[:5].transpose(0, 1)[None], kp[:9].transpose(0, 1)[None], vp[:9].transpose(0, 1)[None],
+                              0.3, True, causal_shift=4)
+    assert torch.allclose(o[:5], o0[0].transpose(0, 1), atol=1e-6)
+    assert torch.isinf(lse[5:9]).all() and (o[5:9] == 0).all()      # 7 queries, 3 keys: the first 4 rows see none
+    assert torch.isfinite(lse[9:]).all()
 
 
 def test_decode_with_a_first_position_equals_the_hook_with_a_padding_mask():

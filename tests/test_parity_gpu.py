@@ -688,6 +688,49 @@ def test_forward_with_the_causal_mask_aligned_to_the_end_of_the_keys(ext, d, nq,
             ext.forward_rect(k.cuda(), q[:, :hkv].cuda(), q[:, :hkv].cuda(), scale, True, bottom_right=True)
 
 
+@pytest.mark.parametrize("d", [64, 128, 256])
+@pytest.mark.parametrize("nq,nk", [(1, 300), (100, 100), (128, 512), (200, 777), (257, 1000), (640, 700)])
+def test_backward_with_the_causal_mask_aligned_to_the_end_of_the_keys(ext, d, nq, nk):
+    """Gradients of a chunk of new tokens behind a cached prefix (query i sees keys j <= i + nk - nq)."""
+    gen = torch.Generator().manual_seed(nq * 5 + nk + d)
+    b, hq, hkv = 2, 4, 2
+    q, k, v, do = (rand_half(gen, b, hq, nq, d), rand_half(gen, b, hkv, nk, d), rand_half(gen, b, hkv, nk, d),
+                   rand_half(gen, b, hq, nq, d))
+    scale = 1.0 / math.sqrt(d)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    o, lse = ext.forward_rect(qc, kc, vc, scale, True, bottom_right=True)
+    grads = ext.backward(do.cuda(), qc, kc, vc, o, lse, scale, True, bottom_right=True)
+    ref = orc.attention_bwd(q, k, v, do, scale, True, causal_shift=nk - nq)
+    if nq == 1 and nk == 1:
+        return
+    check_grads(grads, ref)
+    assert ext.device_status() == 0
+    with pytest.raises(RuntimeError):   # fewer keys than queries: the alignment is not defined
+        ext.backward(do.cuda(), qc, kc[:, :, :max(nq - 1, 0)], vc[:, :, :max(nq - 1, 0)], o, lse, scale, True,
+                     bottom_right=True)
+
+
+@pytest.mark.parametrize("d,h,hkv", [(64, 4, 4), (128, 8, 2)])
+def test_varlen_with_end_aligned_masks_forward_and_backward(ext, d, h, hkv):
+    """Packed sequences whose queries are the LAST len_q positions of their len_k keys: ragged chunks
+    behind ragged prefixes.  One sequence has more queries than keys (its first rows see nothing)."""
+    gen = torch.Generator().manual_seed(77 + d)
+    lq, lk = [40, 130, 7, 256, 50, 1], [100, 130, 300, 1000, 20, 129]
+    cu_q = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(torch.tensor(lk).cumsum(0)), dtype=torch.int32)
+    q, do = rand_half(gen, sum(lq), h, d), rand_half(gen, sum(lq), h, d)
+    k, v = rand_half(gen, sum(lk), hkv, d), rand_half(gen, sum(lk), hkv, d)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = ext.forward_varlen(q.cuda(), k.cuda(), v.cuda(), cu_q.cuda(), cu_k.cuda(), max(lq), max(lk), scale,
+                                True, bottom_right=True)
+    o_ref, lse_ref = orc.varlen_fwd(q, k, v, cu_q, cu_k, scale, True, bottom_right=True)
+    check_fwd(o, lse, o_ref, lse_ref)
+    grads = ext.backward_varlen(do.cuda(), q.cuda(), k.cuda(), v.cuda(), o, lse, cu_q.cuda(), cu_k.cuda(), max(lq),
+                                max(lk), scale, True, bottom_right=True)
+    check_grads(grads, orc.varlen_bwd(q, k, v, do, cu_q, cu_k, scale, True, bottom_right=True))
+    assert ext.device_status() == 0
+
+
 def test_chunked_prefill_equals_one_prefill(fal):
     """Prefill in three chunks through flash_attention_chunk == one causal flash_attention call."""
     gen = torch.Generator().manual_seed(99)
@@ -705,6 +748,12 @@ def test_chunked_prefill_equals_one_prefill(fal):
     out = fal.flash_attention_chunk(q[:, :, -50:], k, v, out_layout="bnhd")
     assert out.transpose(1, 2).is_contiguous()
     assert orc.rel_max_err(out, whole[:, :, -50:].float().cpu()) <= orc.TOL_O
+    # and it is differentiable: the gradients of the last 300 positions against the oracle
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q[:, :, -300:], k, v))
+    do = rand_half(gen, b, hq, 300, d).cuda()
+    fal.flash_attention_chunk(qg, kg, vg).backward(do)
+    ref = orc.attention_bwd(q[:, :, -300:].cpu(), k.cpu(), v.cpu(), do.cpu(), 1 / math.sqrt(d), True, causal_shift=n - 300)
+    check_grads((qg.grad, kg.grad, vg.grad), ref)
 
 
 def test_broadcast_views_are_copied_not_misread(ext, fal):
