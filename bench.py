@@ -257,12 +257,13 @@ def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False, check
     vn = torch.randn(steps, B, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
     out = torch.empty(B, Hq, d, device="cuda", dtype=torch.float16)
     scale = 1.0 / math.sqrt(d)
-    # Warm-up: the first few dozen launches of a process run well below the steady rate (measured:
-    # 141 us per step for the first 256-step loop of a process against 80 us for every later one on an
-    # 8-entry batch), so the timed loop starts after 64 untimed steps at the initial lengths.
+    # Warm-up runs the WHOLE step, the length increment included: the first use of a framework
+    # kernel in a process loads its module (about 15 ms once -- inside a 256-step timed loop that was
+    # 60 us per step on an 8-entry batch).  The appended rows are overwritten by the timed steps.
     lens = lens0.clone()
-    for i in range(64):
-        ext.decode(q[i % steps], kc, vc, lens, scale, kn[i % steps], vn[i % steps], out=out)
+    for i in range(8):
+        ext.decode(q[i], kc, vc, lens, scale, kn[i], vn[i], out=out)
+        lens += 1
     torch.cuda.synchronize()
     lens = lens0.clone()
     ext.profile_read(ext.KERNEL_DECODE_SPLITK)

@@ -137,8 +137,12 @@ int check_device() {
   return cached[dev] == 1 ? FAL_OK : FAL_ERR_UNSUPPORTED_DEVICE;
 }
 
-// 64, 128 and 256 in every entry point (the head_dim-256 backward runs on column halves).
-bool head_dim_ok(int d) { return d == 64 || d == 128 || d == 256; }
+// 32, 64, 96, 128 and 256 in every entry point.  64, 128 and 256 have kernels of their own (the
+// head_dim-256 backward runs on column halves); 32 and 96 run on the 64 / 128 kernels: the TMA
+// descriptors carry the real width, so the missing columns arrive as zeros (they add 0 to every
+// score), and the kernels do not write output columns the tensors do not have.
+bool head_dim_ok(int d) { return d == 32 || d == 64 || d == 96 || d == 128 || d == 256; }
+int kernel_head_dim(int d) { return d == 32 ? 64 : (d == 96 ? 128 : d); }
 // Number of SMs of the current device (cached per device; 0 if it cannot be read).
 int sm_count() {
   static std::mutex mu;
@@ -176,6 +180,7 @@ struct BwdWorkspace {
 };
 
 BwdWorkspace bwd_workspace_layout(int batch, int heads_q, int rows, int head_dim) {
+  head_dim = kernel_head_dim(head_dim);
   BwdWorkspace w;
   // One extra 128-row tile of slack: packed sequences start at arbitrary rows, and a tile's
   // reduction may touch (with zeros) up to 127 rows past the last query.
@@ -196,6 +201,7 @@ struct DecodeWorkspace {
 };
 
 DecodeWorkspace decode_workspace_layout(int batch, int heads_q, int capacity, int head_dim) {
+  head_dim = kernel_head_dim(head_dim);
   DecodeWorkspace w;
   w.splits = (capacity + kDecodeSplitLen - 1) / kDecodeSplitLen;
   const int64_t rows = static_cast<int64_t>(batch) * heads_q * w.splits;
@@ -242,7 +248,7 @@ const char* fal_strerror(int code) {
   switch (code) {
     case FAL_OK: return "ok";
     case FAL_ERR_INVALID_ARGUMENT: return "invalid argument (shape, stride, alignment or null pointer)";
-    case FAL_ERR_UNSUPPORTED_HEAD_DIM: return "unsupported head_dim (64, 128 and 256 are built)";
+    case FAL_ERR_UNSUPPORTED_HEAD_DIM: return "unsupported head_dim (32, 64, 96, 128 and 256 are built)";
     case FAL_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
     case FAL_ERR_CUDA: return "CUDA runtime error";
     case FAL_ERR_TENSOR_MAP: return "TMA descriptor could not be built";
@@ -297,6 +303,7 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   p.batch = batch;
   p.heads_q = heads_q;
   p.heads_kv = heads_kv;
+  p.head_dim = head_dim;
   p.seqlen_q = seqlen_q;
   p.seqlen_k = seqlen_k;
   p.causal_shift = is_causal == FAL_CAUSAL_BOTTOM_RIGHT ? seqlen_k - seqlen_q : 0;
@@ -304,13 +311,14 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int cta_rows = forward_cta_rows(head_dim, (seqlen_q + 255) / 256, static_cast<int64_t>(batch) * heads_q);
+  const int kdim = kernel_head_dim(head_dim);
+  const int cta_rows = forward_cta_rows(kdim, (seqlen_q + 255) / 256, static_cast<int64_t>(batch) * heads_q);
   p.cta_rows = cta_rows;
   p.num_qblk = (seqlen_q + cta_rows - 1) / cta_rows;
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
-  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  cudaError_t e = fal::launch_fwd(kdim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
@@ -357,6 +365,7 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   p.batch = 1;
   p.heads_q = heads_q;
   p.heads_kv = heads_kv;
+  p.head_dim = head_dim;
   p.seqlen_q = 0;
   p.seqlen_k = 0;
   p.shift_per_sequence = is_causal == FAL_CAUSAL_BOTTOM_RIGHT ? 1 : 0;
@@ -366,12 +375,13 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The lengths stay on the device.  Every sequence rounds up to whole query blocks: at most one
   // extra block each.
-  p.cta_rows = forward_cta_rows(head_dim, total_q / 256 + num_seqs, heads_q);
+  const int kdim = kernel_head_dim(head_dim);
+  p.cta_rows = forward_cta_rows(kdim, total_q / 256 + num_seqs, heads_q);
   p.num_qblk = total_q / p.cta_rows + num_seqs;
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
-  cudaError_t e = fal::launch_fwd(head_dim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  cudaError_t e = fal::launch_fwd(kdim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
@@ -422,7 +432,9 @@ int run_bwd(const BwdCall& c) {
     return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && s.row % 8 == 0 && s.head % 8 == 0 &&
            s.batch % 8 == 0;
   };
+  const int kdim = kernel_head_dim(c.head_dim);
   if (partial) {
+    if (kdim != c.head_dim) return FAL_ERR_UNSUPPORTED_HEAD_DIM;  // fp32 partials: head_dim 64, 128, 256
     if (!out_ok(c.dk_f32, c.s_dk) || !out_ok(c.dv_f32, c.s_dv) || !out_ok(c.dq_acc, c.s_dq_acc) ||
         c.s_dq_acc.row != c.head_dim)
       return FAL_ERR_INVALID_ARGUMENT;
@@ -439,7 +451,7 @@ int run_bwd(const BwdCall& c) {
 
   float* dq_accum = partial ? c.dq_acc : static_cast<float*>(c.workspace);
   float* delta = reinterpret_cast<float*>(static_cast<char*>(c.workspace) + w.dq_bytes);
-  const int64_t acc_head = partial ? c.s_dq_acc.head : w.padded_rows * c.head_dim;
+  const int64_t acc_head = partial ? c.s_dq_acc.head : w.padded_rows * kdim;
   const int64_t acc_batch = partial ? c.s_dq_acc.batch : acc_head * c.heads_q;
   const int64_t acc_rows = partial ? c.rows_q : w.padded_rows;
 
@@ -447,8 +459,8 @@ int run_bwd(const BwdCall& c) {
   if ((rc = make_tensor_map(&tq, c.q, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_q, 128))) return rc;
   if ((rc = make_tensor_map(&tdo, c.d_out, c.head_dim, c.rows_q, c.heads_q, c.batch, c.s_do, 128)))
     return rc;
-  if ((rc = make_accum_tensor_map(&tdq, dq_accum, c.head_dim, acc_rows, c.heads_q, c.batch,
-                                  fal::RowStrides{acc_batch, acc_head, c.head_dim})))
+  if ((rc = make_accum_tensor_map(&tdq, dq_accum, kdim, acc_rows, c.heads_q, c.batch,
+                                  fal::RowStrides{acc_batch, acc_head, kdim})))
     return rc;
   if ((rc = make_tensor_map(&tk, c.k, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_k, 128))) return rc;
   if ((rc = make_tensor_map(&tv, c.v, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_v, 128))) return rc;
@@ -468,7 +480,8 @@ int run_bwd(const BwdCall& c) {
   pp.heads_q = c.heads_q;
   pp.rows = c.rows_q;
   pp.padded_rows = static_cast<int>(w.padded_rows);
-  pp.head_dim = c.head_dim;
+  pp.head_dim = kdim;
+  pp.head_dim_real = c.head_dim;
   cudaError_t e = fal::launch_bwd_prep(pp, c.stream);
   if (e != cudaSuccess) return cuda_fail(e);
 
@@ -493,6 +506,7 @@ int run_bwd(const BwdCall& c) {
   p.batch = c.batch;
   p.heads_q = c.heads_q;
   p.heads_kv = c.heads_kv;
+  p.head_dim = c.head_dim;
   p.seqlen_q = c.cu_q ? 0 : c.rows_q;
   p.seqlen_k = c.cu_k ? 0 : c.rows_k;
   p.num_kvblk = c.cu_k ? (c.rows_k / 128 + c.num_seqs) : (c.rows_k + 127) / 128;
@@ -504,7 +518,7 @@ int run_bwd(const BwdCall& c) {
   const int64_t grid = static_cast<int64_t>(p.num_kvblk) * c.batch * c.heads_kv;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_BWD, c.stream);
-  e = fal::launch_bwd(c.head_dim, c.causal != 0, tq, tk, tv, tdo, tdq, p, static_cast<int>(grid),
+  e = fal::launch_bwd(kdim, c.causal != 0, tq, tk, tv, tdo, tdq, p, static_cast<int>(grid),
                       c.stream);
   g_timer.end(FAL_KERNEL_BWD, rec, c.stream);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -519,7 +533,8 @@ int run_bwd(const BwdCall& c) {
   po.batch = c.batch;
   po.heads_q = c.heads_q;
   po.rows = c.rows_q;
-  po.head_dim = c.head_dim;
+  po.head_dim = kdim;
+  po.head_dim_real = c.head_dim;
   po.scale = c.scale;
   e = fal::launch_bwd_post(po, c.stream);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
@@ -737,13 +752,14 @@ int decode_with_workspace(const void* q, void* k_cache, void* v_cache, const fal
   p.heads_q = heads_q;
   p.heads_kv = heads_kv;
   p.capacity = capacity;
-  p.head_dim = head_dim;
+  p.head_dim = kernel_head_dim(head_dim);
+  p.head_dim_real = head_dim;
   p.split_len = kDecodeSplitLen;
   p.splits = static_cast<int>(w.splits);
   p.scale = softmax_scale;
   p.status = status;
   p.part_o = static_cast<float*>(workspace);
-  p.part_ml = p.part_o + static_cast<int64_t>(batch) * heads_q * p.splits * head_dim;
+  p.part_ml = p.part_o + static_cast<int64_t>(batch) * heads_q * p.splits * p.head_dim;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int rec = g_timer.begin(FAL_KERNEL_DECODE_SPLITK, st);
   cudaError_t e = fal::launch_decode_splitk(p, st);

@@ -660,6 +660,7 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       } else if (kv_ok) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
+          if (col_own + c * 32 + v * 8 >= p.head_dim) continue;  // head_dim 32 / 96: no such column
           uint4 out;
           out.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
           out.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
@@ -750,8 +751,11 @@ __global__ void __launch_bounds__(256) fal_bwd_prep_kernel(const BwdPrepParams p
                       static_cast<int64_t>(r) * p.o_strides.row + sub * 8;
     const __half* d_o = static_cast<const __half*>(p.d_o) + b * p.do_strides.batch +
                         h * p.do_strides.head + static_cast<int64_t>(r) * p.do_strides.row + sub * 8;
-    const uint4 ov = *reinterpret_cast<const uint4*>(o);
-    const uint4 dv = *reinterpret_cast<const uint4*>(d_o);
+    uint4 ov = make_uint4(0u, 0u, 0u, 0u), dv = ov;
+    if (sub * 8 < p.head_dim_real) {  // head_dim 32 / 96: the columns beyond it do not exist
+      ov = *reinterpret_cast<const uint4*>(o);
+      dv = *reinterpret_cast<const uint4*>(d_o);
+    }
     const __half2* oh = reinterpret_cast<const __half2*>(&ov);
     const __half2* dh = reinterpret_cast<const __half2*>(&dv);
 #pragma unroll
@@ -780,7 +784,7 @@ __global__ void __launch_bounds__(256) fal_bwd_prep_kernel(const BwdPrepParams p
 // Post-pass: dQ = fp16(scale * accumulator)  (csrc/flash_attn_legacy.cpp:184 of the reference).
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) fal_bwd_post_kernel(const BwdPostParams p) {
-  const int chunks = p.head_dim / 8;
+  const int chunks = p.head_dim_real / 8;  // only the columns the tensors have
   const int64_t total = static_cast<int64_t>(p.batch) * p.heads_q * p.rows * chunks;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (idx >= total) return;
@@ -858,7 +862,7 @@ cudaError_t launch_bwd(int head_dim, bool causal, const CUtensorMap& tq, const C
 }
 
 cudaError_t launch_bwd_post(const BwdPostParams& p, cudaStream_t stream) {
-  const int64_t total = static_cast<int64_t>(p.batch) * p.heads_q * p.rows * (p.head_dim / 8);
+  const int64_t total = static_cast<int64_t>(p.batch) * p.heads_q * p.rows * (p.head_dim_real / 8);
   const int64_t blocks = (total + 255) / 256;
   fal_bwd_post_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
   return cudaGetLastError();

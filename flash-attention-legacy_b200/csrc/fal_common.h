@@ -32,6 +32,8 @@ struct FwdParams {
   int heads_kv;
   int seqlen_q;   // batched mode only
   int seqlen_k;   // batched mode only
+  int head_dim;   // the tensors' head_dim: 32 and 96 run on the 64 / 128 kernels (TMA fills the missing
+                  // columns with zeros), output columns beyond it are not written
   int cta_rows;   // query rows per CTA: 256 (two tiles) or 128 (one tile, both softmax warpgroups on it)
   int num_qblk;   // batched: ceil(seqlen_q / cta_rows); packed: bound on all sequences' blocks
   int causal_shift;  // causal kernels, batched: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
@@ -66,6 +68,7 @@ struct BwdParams {
   int heads_kv;
   int seqlen_q;
   int seqlen_k;
+  int head_dim;   // the tensors' head_dim (32 / 96 run on the 64 / 128 kernels); dK, dV columns beyond it are not written
   int num_kvblk;  // batched: ceil(seqlen_k / 128); packed: bound over all sequences
   int causal_shift;        // causal, batched: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
   int shift_per_sequence;  // causal, packed: the shift of a sequence is its seqlen_k - seqlen_q

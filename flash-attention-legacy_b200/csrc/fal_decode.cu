@@ -147,11 +147,12 @@ fal_decode_splitk_kernel(const DecodeParams p) {
     const int new_local = len_old - start;
     const int store_split = new_local >= 0 ? new_local / p.split_len : 0;
     if (split == store_split) {
-      for (int c = threadIdx.x; c < 2 * kChunks; c += kDecThreads) {
-        const bool is_v = c >= kChunks;
-        const int cc = is_v ? c - kChunks : c;
+      const int real_chunks = p.head_dim_real / 8;  // head_dim 32 / 96 run on the 64 / 128 kernels
+      for (int c = threadIdx.x; c < 2 * real_chunks; c += kDecThreads) {
+        const bool is_v = c >= real_chunks;
+        const int cc = is_v ? c - real_chunks : c;
         const __half* src = static_cast<const __half*>(is_v ? p.v_new : p.k_new) +
-                            (static_cast<int64_t>(b) * p.heads_kv + kv_head) * D + cc * 8;
+                            (static_cast<int64_t>(b) * p.heads_kv + kv_head) * p.head_dim_real + cc * 8;
         const RowStrides& st = is_v ? p.v_strides : p.k_strides;
         __half* dst = static_cast<__half*>(is_v ? p.v_cache : p.k_cache) + b * st.batch + kv_head * st.head +
                       static_cast<int64_t>(len_old) * st.row + cc * 8;
@@ -173,14 +174,16 @@ fal_decode_splitk_kernel(const DecodeParams p) {
   // ---- query fragments (A operand: row = head, col = head_dim) ---------------
   uint32_t qa[kKSteps][4];
   {
-    const __half* qb = static_cast<const __half*>(p.q) + (static_cast<int64_t>(b) * p.heads_q + hq0) * D;
+    // (columns beyond the tensors' head_dim -- 32 and 96 run on the 64 / 128 kernels -- read as zero)
+    const int dr = p.head_dim_real;
+    const __half* qb = static_cast<const __half*>(p.q) + (static_cast<int64_t>(b) * p.heads_q + hq0) * dr;
 #pragma unroll
     for (int ks = 0; ks < kKSteps; ++ks) {
       const int col = ks * 16 + 2 * t;
-      qa[ks][0] = (g < rows_valid) ? *reinterpret_cast<const uint32_t*>(qb + g * D + col) : 0u;
-      qa[ks][1] = (g + 8 < rows_valid) ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + col) : 0u;
-      qa[ks][2] = (g < rows_valid) ? *reinterpret_cast<const uint32_t*>(qb + g * D + col + 8) : 0u;
-      qa[ks][3] = (g + 8 < rows_valid) ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + col + 8) : 0u;
+      qa[ks][0] = (g < rows_valid && col < dr) ? *reinterpret_cast<const uint32_t*>(qb + g * dr + col) : 0u;
+      qa[ks][1] = (g + 8 < rows_valid && col < dr) ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * dr + col) : 0u;
+      qa[ks][2] = (g < rows_valid && col + 8 < dr) ? *reinterpret_cast<const uint32_t*>(qb + g * dr + col + 8) : 0u;
+      qa[ks][3] = (g + 8 < rows_valid && col + 8 < dr) ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * dr + col + 8) : 0u;
     }
   }
 
@@ -189,6 +192,7 @@ fal_decode_splitk_kernel(const DecodeParams p) {
   const __half* vbase = static_cast<const __half*>(p.v_cache) + b * p.v_strides.batch +
                         kv_head * p.v_strides.head + static_cast<int64_t>(start) * p.v_strides.row;
   const uint32_t wbase = smem_u32(dec_smem) + warp * L::kWarpBytes;
+  const int real_chunks = p.head_dim_real / 8;
 
   // Issues the loads of this warp's i-th slice (keys pos0 + (i*4 + warp)*16 ...).
   auto issue_slice = [&](int i) {
@@ -202,11 +206,12 @@ fal_decode_splitk_kernel(const DecodeParams p) {
         const int row = idx / kChunks;
         const int ch = idx % kChunks;
         const int key = key0 + row;
-        const bool ok = key < pos_end;
-        const int64_t krow = static_cast<int64_t>(ok ? key : pos0);
+        const bool ok = key < pos_end && ch < real_chunks;  // chunks past the tensors' head_dim fill with zeros
+        const int64_t krow = static_cast<int64_t>(key < pos_end ? key : pos0);
+        const int src_ch = ch < real_chunks ? ch : 0;
         const uint32_t soff = row * L::kRowBytes + ((ch ^ (row & 7)) << 4);
-        cp_async_16_zfill(sb + soff, kbase + krow * p.k_strides.row + ch * 8, ok);
-        cp_async_16_zfill(sb + L::kSliceBytes + soff, vbase + krow * p.v_strides.row + ch * 8, ok);
+        cp_async_16_zfill(sb + soff, kbase + krow * p.k_strides.row + src_ch * 8, ok);
+        cp_async_16_zfill(sb + L::kSliceBytes + soff, vbase + krow * p.v_strides.row + src_ch * 8, ok);
       }
     }
     cp_async_commit();  // always commit so that group counting stays uniform
@@ -372,10 +377,10 @@ __global__ void fal_decode_combine_kernel(const DecodeParams p) {
   float lsum = 0.f;
   for (int i = 0; i < n; ++i) lsum += fast_exp2(ml[2 * i] - muse) * ml[2 * i + 1];
   const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+  for (int c = threadIdx.x; c < p.head_dim_real; c += blockDim.x) {
     float o = 0.f;
     for (int i = 0; i < n; ++i) o += fast_exp2(ml[2 * i] - muse) * po[static_cast<int64_t>(i) * D + c];
-    static_cast<__half*>(p.o)[static_cast<int64_t>(bh) * D + c] = __float2half_rn(o * inv);
+    static_cast<__half*>(p.o)[static_cast<int64_t>(bh) * p.head_dim_real + c] = __float2half_rn(o * inv);
   }
   if (p.lse != nullptr && threadIdx.x == 0) {
     p.lse[bh] = (lsum > 0.f) ? (mmax + log2f(lsum)) * 0.6931471805599453f : kNegInfD;

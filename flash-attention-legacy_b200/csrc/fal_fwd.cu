@@ -585,6 +585,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (row_ok) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
+            if (ch * (D / 2) + c * 32 + v * 8 >= p.head_dim) continue;  // head_dim 32 / 96: no such column
             uint4 out;
             out.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
             out.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
@@ -771,6 +772,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (row_ok) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
+          if (c * 32 + v * 8 >= p.head_dim) continue;  // head_dim 32 / 96: no such column
           uint4 out;
           out.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
           out.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);

@@ -57,7 +57,8 @@ struct BwdPrepParams {
   int heads_q;
   int rows;        // batched: seqlen_q; packed: total_q
   int padded_rows; // rows of delta / dq_accum per (batch, head)
-  int head_dim;
+  int head_dim;      // kernel head_dim (64, 128, 256): row length of dq_accum
+  int head_dim_real; // the tensors' head_dim (32 -> 64 and 96 -> 128 kernels read the rest as zeros)
 };
 cudaError_t launch_bwd_prep(const BwdPrepParams& p, cudaStream_t stream);
 
@@ -77,7 +78,8 @@ struct BwdPostParams {
   int batch;
   int heads_q;
   int rows;
-  int head_dim;
+  int head_dim;      // kernel head_dim: row length of dq_accum
+  int head_dim_real; // the tensors' head_dim: columns of dq that exist
   float scale;
 };
 cudaError_t launch_bwd_post(const BwdPostParams& p, cudaStream_t stream);
@@ -133,7 +135,8 @@ struct DecodeParams {
   int heads_q;
   int heads_kv;
   int capacity;         // cache positions per batch entry
-  int head_dim;
+  int head_dim;         // kernel head_dim (64, 128, 256): row length of the partial results
+  int head_dim_real;    // the tensors' head_dim (32 and 96 run on the 64 / 128 kernels)
   int split_len;        // positions per split (multiple of the key tile)
   int splits;           // ceil(capacity / split_len)
   float scale;

@@ -14,7 +14,6 @@ from typing import Optional
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 from torch.autograd import Function
 
 try:
@@ -26,22 +25,10 @@ except ImportError as e:  # same failure mode as the reference: no extension, no
         f"Original error: {e}"
     )
 
+# Head dims of the reference (csrc/flash_attn_legacy.cpp:56).  64, 128 and 256 have kernels of their
+# own; 32 and 96 run on the 64 / 128 kernels inside the library, which reads the missing columns as
+# zeros through its TMA descriptors and never writes them -- no padded copies on this side.
 SUPPORTED_HEAD_DIMS = (32, 64, 96, 128, 256)
-_NATIVE_HEAD_DIMS = (64, 128, 256)   # what the kernels run at (forward, backward and decode)
-
-
-def _native_head_dim(d: int) -> int:
-    """Head dim the kernels run at: 32 -> 64 and 96 -> 128 by zero padding (exact: padded
-    columns add 0 to every score and produce output columns that are sliced away)."""
-    if d in _NATIVE_HEAD_DIMS:
-        return d
-    if d == 32:
-        return 64
-    if d == 96:
-        return 128
-    raise NotImplementedError(f"head_dim={d} is not built (32, 64, 96, 128 and 256 are)")
-
-
 
 
 def _kernel_ready(t: torch.Tensor) -> torch.Tensor:
@@ -73,7 +60,7 @@ class FlashAttentionFunc(Function):
         assert k.dtype == torch.float16 and v.dtype == torch.float16
         assert q.is_cuda and q.dim() == 4
         d = q.shape[-1]
-        assert d in _NATIVE_HEAD_DIMS, f"native head_dim must be 64, 128 or 256, got {d}"
+        assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
         h_q, h_kv = q.shape[1], k.shape[1]
         assert h_q % h_kv == 0, f"H_q ({h_q}) must be divisible by H_kv ({h_kv})"
 
@@ -98,10 +85,6 @@ class FlashAttentionFunc(Function):
         return dq, dk, dv, None, None, None
 
 
-def _pad_last(x, d_to):
-    return x if x.shape[-1] == d_to else F.pad(x, (0, d_to - x.shape[-1]))
-
-
 def flash_attention(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -123,11 +106,6 @@ def flash_attention(
     assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(d)
-    dn = _native_head_dim(d)
-    if dn != d:
-        out = FlashAttentionFunc.apply(_pad_last(q, dn), _pad_last(k, dn), _pad_last(v, dn),
-                                       softmax_scale, is_causal, out_layout)
-        return out[..., :d]
     return FlashAttentionFunc.apply(q, k, v, softmax_scale, is_causal, out_layout)
 
 
@@ -171,12 +149,12 @@ def flash_attention_chunk(
     aligned to the bottom-right corner).  This is the step between prefill and single-token
     decode -- prefill in chunks, or a few new tokens after a cached prefix -- which the reference
     sends to its eager fallback with its usual top-left mask (integrations.py:63, :77-98).
-    Not in the reference's API.  Differentiable; head dims 64, 128, 256.
+    Not in the reference's API.  Differentiable.
     """
     assert q.dtype == torch.float16 and k.dtype == torch.float16 and v.dtype == torch.float16
     assert q.is_cuda and q.dim() == 4
     d = q.shape[-1]
-    assert d in _NATIVE_HEAD_DIMS, f"head_dim must be 64, 128 or 256 here, got {d}"
+    assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
     assert q.shape[1] % k.shape[1] == 0, "H_q must be divisible by H_kv"
     assert k.shape[2] >= q.shape[2], "the key sequence must be at least as long as the query chunk"
     assert out_layout in ("bhnd", "bnhd"), f"out_layout must be 'bhnd' or 'bnhd', got {out_layout}"
@@ -198,7 +176,7 @@ class FlashAttnVarlenFunc(Function):
         assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
         assert q.is_cuda and q.dim() == 3
         d = q.shape[-1]
-        assert d in _NATIVE_HEAD_DIMS, f"native head_dim must be 64, 128 or 256, got {d}"
+        assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
 
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         cu_seqlens_q = cu_seqlens_q.contiguous().to(torch.int32)
@@ -257,12 +235,6 @@ def flash_attn_varlen_func(
     assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(d)
-    dn = _native_head_dim(d)
-    if dn != d:
-        out = FlashAttnVarlenFunc.apply(_pad_last(q, dn), _pad_last(k, dn), _pad_last(v, dn),
-                                        cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                                        softmax_scale, causal, causal_bottom_right)
-        return out[..., :d]
     return FlashAttnVarlenFunc.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                      softmax_scale, causal, causal_bottom_right)
 
@@ -290,7 +262,7 @@ def flash_attn_with_kvcache(
     assert q.dim() == 4 and q.shape[1] == 1, "q must be [B, 1, H_q, d]"
     assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
     b, _, hq, d = q.shape
-    assert d in _NATIVE_HEAD_DIMS, f"decode supports head_dim 64, 128 and 256, got {d}"
+    assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
     seq_axis = 1 if cache_layout == "bshd" else 2
     if cache_seqlens is None:
         cache_seqlens = torch.full((b,), k_cache.shape[seq_axis], dtype=torch.int32, device=q.device)

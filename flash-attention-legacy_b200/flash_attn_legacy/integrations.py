@@ -28,7 +28,7 @@ import torch
 import torch.nn as nn
 
 _KERNEL_HEAD_DIMS = (32, 64, 96, 128, 256)
-_DECODE_HEAD_DIMS = (64, 128, 256)
+_DECODE_HEAD_DIMS = _KERNEL_HEAD_DIMS  # decode and chunked prefill cover the same head dims
 
 
 def _resolve_causal(module, attention_mask, q_len, kwargs):

@@ -58,6 +58,10 @@ def test_workspace_sizes(lib):
     expect = 4 * 32 * rows * 128 * 4 + 4 * 32 * rows * 4
     assert lib.fal_bwd_workspace_bytes(4, 32, 4096, 128) == expect
     assert lib.fal_bwd_workspace_bytes(0, 32, 4096, 128) == 0
+    # head dims 32 and 96 run on the 64 / 128 kernels: their scratch is that of the kernel they run on
+    assert lib.fal_bwd_workspace_bytes(4, 32, 4096, 96) == expect
+    assert lib.fal_bwd_workspace_bytes(1, 2, 100, 32) == lib.fal_bwd_workspace_bytes(1, 2, 100, 64)
+    assert lib.fal_decode_workspace_bytes(2, 8, 5000, 96) == lib.fal_decode_workspace_bytes(2, 8, 5000, 128)
     # 32 splits of 1024 positions, (d + 2) floats per (batch, head, split)
     assert lib.fal_decode_workspace_bytes(64, 32, 32768, 128) == 64 * 32 * 32 * 130 * 4
     assert lib.fal_decode_workspace_bytes(1, 8, 1000, 64) == 1 * 8 * 1 * 66 * 4

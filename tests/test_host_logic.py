@@ -28,11 +28,15 @@ def test_binding_exposes_the_reference_extension_functions():
         assert callable(getattr(ext, name))
 
 
-def test_native_head_dim_mapping():
-    from flash_attn_legacy.flash_attn import _native_head_dim
-    assert [_native_head_dim(d) for d in (32, 64, 96, 128, 256)] == [64, 64, 128, 128, 256]
-    with pytest.raises(NotImplementedError):
-        _native_head_dim(80)
+def test_head_dims_of_the_reference_are_accepted_without_padding():
+    """32 and 96 go to the library as they are (it runs them on its 64 / 128 kernels); the operator
+    no longer makes padded copies, and refuses what the reference refuses."""
+    from flash_attn_legacy import flash_attn as mod
+    assert mod.SUPPORTED_HEAD_DIMS == (32, 64, 96, 128, 256)
+    assert not hasattr(mod, "_pad_last")
+    with pytest.raises(AssertionError):
+        mod.flash_attention(torch.zeros(1, 1, 4, 80, dtype=torch.float16), torch.zeros(1, 1, 4, 80, dtype=torch.float16),
+                            torch.zeros(1, 1, 4, 80, dtype=torch.float16))
 
 
 def test_strided_views_pass_through_and_broadcast_views_are_copied():

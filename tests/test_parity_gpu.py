@@ -731,6 +731,67 @@ def test_varlen_with_end_aligned_masks_forward_and_backward(ext, d, h, hkv):
     assert ext.device_status() == 0
 
 
+@pytest.mark.parametrize("d", [32, 96])
+def test_head_dims_32_and_96_run_without_padded_copies(ext, fal, d):
+    """32 and 96 run on the 64 / 128 kernels: the TMA descriptors carry the real width (the missing
+    columns arrive as zeros) and no output column beyond it is written.  Batched forward + backward
+    (both forward variants), packed, chunk, decode with append -- straight through the binding, into
+    output tensors with guard columns that must stay untouched."""
+    gen = torch.Generator().manual_seed(1000 + d)
+    scale = 1.0 / math.sqrt(d)
+    # batched, strided [B,N,H,d] inputs, both forward variants
+    b, hq, hkv, n = 2, 4, 2, 333
+    qm, km, vm, dom = rand_half(gen, b, n, hq, d), rand_half(gen, b, n, hkv, d), rand_half(gen, b, n, hkv, d), rand_half(gen, b, n, hq, d)
+    q, k, v, do = (t.cuda().transpose(1, 2) for t in (qm, km, vm, dom))
+    qf, kf, vf, dof = (t.transpose(1, 2) for t in (qm, km, vm, dom))
+    o_ref, lse_ref = orc.attention_fwd(qf, kf, vf, scale, True)
+    ref = orc.attention_bwd(qf, kf, vf, dof, scale, True)
+    for variant in (1, 2):
+        ext.set_forward_variant(variant)
+        try:
+            wide = torch.full((b, hq, n, d + 8), 7.0, dtype=torch.float16, device="cuda")   # guard columns
+            o, lse = ext.forward(q, k, v, scale, True, out=wide[..., :d])
+        finally:
+            ext.set_forward_variant(0)
+        check_fwd(o, lse, o_ref, lse_ref)
+        assert (wide[..., d:] == 7.0).all()
+    gw = [torch.full((b, h, n, d + 8), 7.0, dtype=torch.float16, device="cuda") for h in (hq, hkv, hkv)]
+    grads = ext.backward(do, q, k, v, o, lse, scale, True, out=[t[..., :d] for t in gw])
+    check_grads(grads, ref)
+    assert all((t[..., d:] == 7.0).all() for t in gw)
+    # packed, through the autograd operator
+    lens = [70, 300, 9]
+    qp, kp, vp, dop, cu = packed_inputs(gen, lens, 4, 2, d)
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (qp, kp, vp))
+    out = fal.flash_attn_varlen_func(qc, kc, vc, cu.cuda(), cu.cuda(), 300, 300, causal=True)
+    out.backward(dop.cuda())
+    o_ref, _ = orc.varlen_fwd(qp, kp, vp, cu, cu, scale, True)
+    assert orc.rel_max_err(out.detach(), o_ref) <= orc.TOL_O
+    check_grads((qc.grad, kc.grad, vc.grad), orc.varlen_bwd(qp, kp, vp, dop, cu, cu, scale, True))
+    # a chunk behind a prefix
+    qx, kx, vx = rand_half(gen, 1, 4, 100, d), rand_half(gen, 1, 2, 420, d), rand_half(gen, 1, 2, 420, d)
+    oc = fal.flash_attention_chunk(qx.cuda(), kx.cuda(), vx.cuda())
+    assert orc.rel_max_err(oc, orc.attention_fwd(qx, kx, vx, scale, True, causal_shift=320)[0]) <= orc.TOL_O
+    # decode with an append, both cache layouts
+    B, S = 3, 1500
+    kc_, vc_, qd = rand_half(gen, B, S, hkv, d), rand_half(gen, B, S, hkv, d), rand_half(gen, B, hq, d)
+    kn, vn = rand_half(gen, B, hkv, d), rand_half(gen, B, hkv, d)
+    lens_t = torch.tensor([0, 1023, 1499], dtype=torch.int32)
+    for layout in ("bshd", "bhsd"):
+        kcc, vcc = kc_.cuda(), vc_.cuda()
+        if layout == "bhsd":
+            kcc, vcc = kcc.transpose(1, 2).contiguous(), vcc.transpose(1, 2).contiguous()
+        od, lsed = ext.decode(qd.cuda(), kcc, vcc, lens_t.cuda(), scale, kn.cuda(), vn.cuda(), cache_layout=layout,
+                              return_lse=True)
+        kr, vr = kc_.clone(), vc_.clone()
+        for i in range(B):
+            kr[i, lens_t[i]], vr[i, lens_t[i]] = kn[i], vn[i]
+        got_k = kcc if layout == "bshd" else kcc.transpose(1, 2)
+        assert torch.equal(got_k.cpu(), kr)
+        check_fwd(od, lsed, *orc.decode_fwd(qd, kr, vr, lens_t + 1, scale))
+    assert ext.device_status() == 0
+
+
 def test_chunked_prefill_equals_one_prefill(fal):
     """Prefill in three chunks through flash_attention_chunk == one causal flash_attention call."""
     gen = torch.Generator().manual_seed(99)
