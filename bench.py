@@ -775,6 +775,8 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=0,
                     help="decode workload on one rank: run this many of the 64 batch entries (what one of "
                          "64/N ranks holds), to see a shard's step without the other GPUs")
+    ap.add_argument("--e2e-kv-heads-per-chunk", type=int, default=4, choices=[1, 2, 4, 8],
+                    help="end-to-end leg: KV heads (with their query heads) of one batch entry per pipeline chunk")
     ap.add_argument("--kernel-source-hash", action="store_true",
                     help="print the hash an ncu capture record of the backward kernel must carry, and exit")
     ap.add_argument("--decode-profile", action="store_true",
@@ -875,38 +877,47 @@ def main():
     h_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v)]
     dq_, dk_, dv_ = q, k, v  # device staging buffers reused as H2D destinations
 
-    # One batch element per chunk, three streams: the copy-in of chunk b+1 and the copy-out of chunk
-    # b-1 run beside the kernels of chunk b (the PCIe link is full duplex).  Every chunk goes
-    # through the public autograd operator.
+    # Eight chunks -- one batch entry x four KV heads (with their sixteen query heads) each --, three
+    # streams: the copy-in of chunk c+1 and the copy-out of chunk c-1 run beside the kernels of chunk c
+    # (the PCIe link is full duplex).  The copy-in stream sets the pace (336 MB per step); smaller chunks
+    # shorten what cannot overlap -- the first chunk's copy-in, the last chunk's kernels and copy-out --
+    # until the host's launch path becomes the limit (measured per step: 4 chunks 7.47 ms, 8 chunks
+    # 6.70 ms, 16 chunks 7.42 ms, 32 chunks 14.5 ms).  Every chunk goes through the public autograd
+    # operator on strided views: no staging copy.
     main_stream = torch.cuda.current_stream()
     s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-    nchunk = q.shape[0]
-    computed = [None] * nchunk  # event: the kernels that read chunk b's staging buffers are done
+    kv_per_chunk = args.e2e_kv_heads_per_chunk
+    group = Hq // Hkv
+    chunks = [(b, kh, kh + kv_per_chunk) for b in range(B) for kh in range(0, Hkv, kv_per_chunk)]
+    nchunk = len(chunks)
+    computed = [None] * nchunk  # event: the kernels that read chunk c's staging buffers are done
 
     def e2e_step():
-        for b in range(nchunk):
-            sl = slice(b, b + 1)
+        for c, (b, k0, k1) in enumerate(chunks):
+            bs, ks, qs = slice(b, b + 1), slice(k0, k1), slice(k0 * group, k1 * group)
             with torch.cuda.stream(s_in):
-                if computed[b] is not None:
-                    s_in.wait_event(computed[b])
-                dq_[sl].copy_(hq[sl], non_blocking=True)
-                dk_[sl].copy_(hk[sl], non_blocking=True)
-                dv_[sl].copy_(hv[sl], non_blocking=True)
-                do[sl].copy_(hdo[sl], non_blocking=True)
+                if computed[c] is not None:
+                    s_in.wait_event(computed[c])
+                dq_[bs, qs].copy_(hq[bs, qs], non_blocking=True)
+                dk_[bs, ks].copy_(hk[bs, ks], non_blocking=True)
+                dv_[bs, ks].copy_(hv[bs, ks], non_blocking=True)
+                do[bs, qs].copy_(hdo[bs, qs], non_blocking=True)
                 loaded = torch.cuda.Event()
                 loaded.record(s_in)
             with torch.cuda.stream(s_cmp):
                 s_cmp.wait_event(loaded)
-                qa, ka, va = (t[sl].detach().requires_grad_(True) for t in (dq_, dk_, dv_))
+                qa = dq_[bs, qs].detach().requires_grad_(True)
+                ka = dk_[bs, ks].detach().requires_grad_(True)
+                va = dv_[bs, ks].detach().requires_grad_(True)
                 out = fal.flash_attention(qa, ka, va, softmax_scale=scale, is_causal=causal)
-                out.backward(do[sl])
-                computed[b] = torch.cuda.Event()
-                computed[b].record(s_cmp)
+                out.backward(do[bs, qs])
+                computed[c] = torch.cuda.Event()
+                computed[c].record(s_cmp)
             with torch.cuda.stream(s_out):
-                s_out.wait_event(computed[b])
-                for dst, g in zip(h_out, (qa.grad, ka.grad, va.grad)):
+                s_out.wait_event(computed[c])
+                for dst, g, sl in zip(h_out, (qa.grad, ka.grad, va.grad), (qs, ks, ks)):
                     g.record_stream(s_out)
-                    dst[sl].copy_(g, non_blocking=True)
+                    dst[bs, sl].copy_(g, non_blocking=True)
 
     def e2e_join():
         for st in (s_in, s_cmp, s_out):
@@ -1013,7 +1024,8 @@ def main():
             "per_gpu_tflops": value / world,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "pipeline": f"{nchunk} batch chunks; copy-in, kernels and copy-out on three streams"},
+                    "pipeline": f"{nchunk} chunks of one batch entry x {kv_per_chunk} KV heads; copy-in, kernels and "
+                                "copy-out on three streams"},
             "gpu_launches": 4 * args.steps,
             "launches_per_step": {"fal_fwd_kernel": 1, "fal_bwd_prep_kernel": 1, "fal_bwd_kernel": 1,
                                   "fal_bwd_post_kernel": 1},
