@@ -61,7 +61,7 @@ def measured_peaks():
     return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
-KERNEL_SOURCES = ("fal_bwd.cu", "sm100_ptx.cuh", "fal_common.h", "fal_launch.h")
+KERNEL_SOURCES = ("fal_bwd.cu", "sm100_ptx.cuh", "fal_common.h")
 
 
 def kernel_source_hash():
@@ -185,11 +185,12 @@ def dist_setup(n_gpus):
     return 0, 1, 0, None
 
 
-def cpu_baseline_sample(num_slices, threads=None):
-    """Times the oracle's forward + backward on `num_slices` (batch, kv-head-group) slices.
+def cpu_baseline_sample(num_slices, min_seconds=0.0):
+    """Times the oracle's forward + backward on (batch, kv-head-group) slices of the workload: at least
+    `num_slices` of them, and as many more as it takes to fill `min_seconds` (32 at most -- the step).
 
     One slice = 1 batch entry x 4 query heads x 1 KV head x N=4096 x d=128 (1/32 of a step).
-    Returns (tflops, seconds, threads).
+    Returns (tflops, seconds, threads, slices).
     """
     sys.path.insert(0, ROOT)
     from oracle import attention_oracle as orc
@@ -204,11 +205,13 @@ def cpu_baseline_sample(num_slices, threads=None):
     fwd, bwd = step_flops()
     slice_flops = (fwd + bwd) / (w["B"] * w["Hkv"])
     t0 = time.perf_counter()
-    for _ in range(num_slices):
+    done = 0
+    while done < num_slices or (time.perf_counter() - t0 < min_seconds and done < w["B"] * w["Hkv"]):
         orc.attention_fwd(q, k, v, scale, w["causal"])
         orc.attention_bwd(q, k, v, do, scale, w["causal"])
+        done += 1
     dt = time.perf_counter() - t0
-    return slice_flops * num_slices / dt / 1e12, dt, torch.get_num_threads()
+    return slice_flops * done / dt / 1e12, dt, torch.get_num_threads(), done
 
 
 def run_reference(args):
@@ -223,7 +226,7 @@ def run_reference(args):
         cpu_baseline_sample(1)
     t_total, tf_list = 0.0, []
     for _ in range(args.steps):
-        tf, dt, threads = cpu_baseline_sample(slices_per_step)
+        tf, dt, threads, _ = cpu_baseline_sample(slices_per_step)
         tf_list.append(tf)
         t_total += dt
     value = sum(tf_list) / len(tf_list)
@@ -261,7 +264,7 @@ def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False, check
     # kernel in a process loads its module (about 15 ms once -- inside a 256-step timed loop that was
     # 60 us per step on an 8-entry batch).  The appended rows are overwritten by the timed steps.
     lens = lens0.clone()
-    for i in range(8):
+    for i in range(min(8, steps)):
         ext.decode(q[i], kc, vc, lens, scale, kn[i], vn[i], out=out)
         lens += 1
     torch.cuda.synchronize()
@@ -1004,9 +1007,9 @@ def main():
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_extras:
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
-        tf, dt, threads = cpu_baseline_sample(6)
+        tf, dt, threads, n_sl = cpu_baseline_sample(6, min_seconds=10.0)
         cpu_baseline = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
-                        "sample": f"6 of 32 (batch, kv-head-group) slices of the same workload, {dt:.1f} s, "
+                        "sample": f"{n_sl} of 32 (batch, kv-head-group) slices of the same workload, {dt:.1f} s, "
                                   f"fp32 oracle forward + backward, os.cpu_count()={os.cpu_count()}"}
         try:
             extra["decode"] = run_decode_extra(ext, peaks)

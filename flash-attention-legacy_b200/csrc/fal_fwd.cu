@@ -52,23 +52,10 @@ constexpr float kNegInf = -INFINITY;
 // Skip the O rescale while the running maximum grows by less than 2^8.
 constexpr float kRescaleThreshold = 8.0f;
 
-// Of every 8 consecutive score columns, this many take the FMA-pipe exp2 instead of the
-// special-function unit (16 ex2/clk/SM would otherwise cap the kernel at d=128).
-#ifndef FAL_EXP_EMU_PER8
-#define FAL_EXP_EMU_PER8 0
-#endif
-template <int K>
-__device__ __forceinline__ float tile_exp2(int i, float x) {
-  // i is a multiple of 4 under full unrolling, so the choice folds at compile time.
-  return (((i + K) & 7) < FAL_EXP_EMU_PER8) ? exp2_fma(x) : fast_exp2(x);
-}
-
-// Packed softmax arithmetic: scale-and-subtract, the row sums and (for a share of the pairs) the
-// exponential itself run as two-float instructions.  FAL_FWD_EMU_PAIRS of every 4 pairs take the
-// polynomial path instead of the special-function unit (0 = none).
-#ifndef FAL_FWD_PACKED
-#define FAL_FWD_PACKED 1
-#endif
+// The softmax arithmetic -- scale-and-subtract, the row sums and (for a share of the pairs) the
+// exponential itself -- runs as two-float instructions.  FAL_FWD_EMU_PAIRS of every 4 pairs take the
+// polynomial path on the FMA pipe instead of the special-function unit (0 = none: measured slower
+// with 1, the kernel is bound by dependency latency, not by the special-function unit).
 #ifndef FAL_FWD_EMU_PAIRS
 #define FAL_FWD_EMU_PAIRS 0
 #endif
@@ -683,7 +670,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
       // P = exp2(s * c2 - m * c2) from the registers, four independent row-sum chains,
       // fp16 P back into TMEM over the first half of S.
-#if FAL_FWD_PACKED
       const uint64_t c2p = pack_f32x2(c2, c2);
       const uint64_t moffp = pack_f32x2(-moff, -moff);
       uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
@@ -716,32 +702,6 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       float sum0, sum1, sum2, sum3;
       unpack_f32x2(sum_a, sum0, sum1);
       unpack_f32x2(sum_b, sum2, sum3);
-#else
-      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float p0 = tile_exp2<0>(i, fmaf(__uint_as_float(sr[c][i + 0]), c2, -moff));
-          const float p1 = tile_exp2<1>(i, fmaf(__uint_as_float(sr[c][i + 1]), c2, -moff));
-          const float p2 = tile_exp2<2>(i, fmaf(__uint_as_float(sr[c][i + 2]), c2, -moff));
-          const float p3 = tile_exp2<3>(i, fmaf(__uint_as_float(sr[c][i + 3]), c2, -moff));
-          sum0 += p0;
-          sum1 += p1;
-          sum2 += p2;
-          sum3 += p3;
-          pk[(i >> 1) + 0] = pack_half2(p0, p1);
-          pk[(i >> 1) + 1] = pack_half2(p2, p3);
-        }
-        tmem_st_32x32b_x16(tS + c * 16, pk);
-        if (c == 1) {  // the first 64 keys of P are in TMEM: the PV MMA may start on them
-          tmem_wait_st();
-          tc_fence_before_sync();
-          mbar_arrive(bar(iPHalf + wg));
-        }
-      }
-#endif
       const float sum_lo = sum0 + sum1, sum_hi = sum2 + sum3;
       const float sum01 = sum_lo + sum_hi;
       l += sum01;

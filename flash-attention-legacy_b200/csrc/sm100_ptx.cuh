@@ -113,73 +113,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 }
 
 // ---------------------------------------------------------------------------
-// Two-CTA clusters ("CTA pairs"): rank, cluster barrier, the peer's shared memory.
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-
-// All threads of all CTAs of the cluster (every thread must execute it).
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-
-// Arrive on an mbarrier anywhere in the cluster (address from cluster_map_shared).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
-}
-
-// Same without release semantics: for arrivals that publish no ordinary memory (TMEM contents
-// are ordered by tcgen05.wait / tcgen05.fence instead).  A cluster-scope release costs the
-// arriving thread several hundred cycles.
-__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar_cluster_addr) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
-}
-
-// try_wait that also acquires what other CTAs of the cluster released before arriving.
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-
-// mbar_wait for a barrier that CTAs of the whole cluster arrive on (same abort protocol).
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                                  int barrier_id) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t spins = 0;
-  while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++spins & 255u) == 0u) {
-      if (*ctx.abort_smem) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        *ctx.abort_smem = 1;
-        if (ctx.status) atomicCAS(ctx.status, 0, kDevWaitTimeout + barrier_id);
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-// ---------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor) loads: plain single-CTA loads only.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
@@ -197,24 +130,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const CUtensorMap
       : "memory");
 }
 
-// Bulk fp32 add-reduction of a contiguous shared-memory block into global memory.
-__device__ __forceinline__ void bulk_reduce_add_f32(float* dst_global, uint32_t src_smem,
-                                                    uint32_t bytes) {
-  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
-               ::"l"(dst_global), "r"(src_smem), "r"(bytes)
-               : "memory");
-}
-
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
-// Waits until the bulk groups issued by this thread have finished READING shared memory.
-__device__ __forceinline__ void bulk_wait_group_read0() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
-
-// Same, but lets the N most recent groups stay in flight.
+// Waits until all but the N most recent bulk groups issued by this thread have finished READING
+// shared memory.
 template <int N>
 __device__ __forceinline__ void bulk_wait_group_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
@@ -244,20 +165,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
                : "memory");
 }
 
-// CTA-pair forms: executed by one warp of EACH CTA of the pair; both get the same address.
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
-}
-
 __device__ __forceinline__ void tc_fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -281,14 +188,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                : "memory");
 }
 
-// CTA-pair form: arrives (once the pair MMAs issued so far by this thread are done) on the
-// barrier at the given cluster address, i.e. in one chosen CTA of the pair.
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar_cluster_addr)
-               : "memory");
-}
-
 // 32 lanes x 32 consecutive 32-bit columns; thread i of the warp gets lane (base_lane + i).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -300,17 +199,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
@@ -350,18 +238,12 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int a_mn_maj
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// Shared-memory operand descriptor, 128-byte swizzle, tile base 1024-byte
-// aligned.  addr/lbo/sbo in bytes.  Bits: [0,14) addr>>4, [16,30) LBO>>4,
-// [32,46) SBO>>4, [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) |
-         (static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16) |
-         (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// The same descriptor split into its 32-bit halves, so that an issuing thread can keep the low
-// word of a tile's base descriptor in a register and step through a tile with one 32-bit add
-// per MMA (the address field holds addr >> 4 and shared-memory addresses never carry out of it).
+// Shared-memory operand descriptor, 128-byte swizzle, tile base 1024-byte aligned.  addr / LBO /
+// SBO in bytes.  Bits: [0,14) addr>>4, [16,30) LBO>>4, [32,46) SBO>>4, [46,48) version = 1,
+// [61,64) layout = 2 (SWIZZLE_128B).  It is built from its 32-bit halves, so that an issuing thread
+// can keep the low word of a tile's base descriptor in a register and step through a tile with one
+// 32-bit add per MMA (the address field holds addr >> 4 and shared-memory addresses never carry out
+// of it).
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo) {
   return ((addr & 0x3FFFFu) >> 4) | (((lbo >> 4) & 0x3FFFu) << 16);
 }
@@ -395,33 +277,6 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ".reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-      "}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// CTA-pair MMAs (issued by one thread of the pair's leader CTA, rank 0): M = 256, rows 0..127
-// from the leader's A and accumulator, rows 128..255 from the peer's; each CTA supplies its own
-// A and HALF of B (N/2 rows of a K-major B, N/2 columns of an MN-major B) at the same
-// shared-memory / TMEM addresses.
-__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
       "}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
