@@ -99,8 +99,11 @@ template <int D, bool ONE_TILE>
 struct FwdSmem {
   // One 128-row query tile per CTA: always at head_dim 256 (its O accumulator alone takes 256 of the
   // 512 TMEM columns; single K and V buffers, a 128 x 256 tile is 64 KB), and at head_dim 64 / 128
-  // when two-tile CTAs would leave SMs without work.  Both softmax warpgroups then share the one
-  // tile, 64 score columns each.
+  // when two-tile CTAs would leave SMs without work.  At 64 / 128 both softmax warpgroups then share
+  // the one tile, 64 score columns each (kSplitCols); at 256, where the single K / V buffer and not the
+  // softmax sets the pace, one warpgroup keeps whole rows and the other idles (measured 3 - 6 % faster
+  // there than the shared tile).
+  static constexpr bool kSplitCols = ONE_TILE && D != 256;
   static_assert(ONE_TILE || D != 256, "head_dim 256 runs one query tile per CTA");
   static constexpr int kQTiles = ONE_TILE ? 1 : 2;
   static constexpr int kCtaRows = kQTiles * kTileM;
@@ -119,7 +122,7 @@ struct FwdSmem {
   // split-column softmax: row maxima (two buffers) and row sums the two column halves of a row exchange
   static constexpr int kXchOff = kMiscOff + 16;
   static constexpr int kXchTileBytes = 3 * 2 * kTileM * 4;
-  static constexpr int kXchBytes = ONE_TILE ? kXchTileBytes : 0;
+  static constexpr int kXchBytes = kSplitCols ? kXchTileBytes : 0;
   static constexpr int kBytes = kXchOff + kXchBytes;
   static constexpr int kAllocBytes = kBytes + 1024;  // room to align the base to 1024
 };
@@ -402,7 +405,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else {
     // ===================== softmax + output =================================
     setmaxnreg_inc<kRegsSoftmax>();
-    if constexpr (ONE_TILE) {
+    if constexpr (L::kSplitCols) {
       // Two warps per TMEM lane quarter of the tile: one for score columns [0, 64) (column half 0), one
       // for [64, 128), on the same 32 rows.  They exchange the row maxima of every step through
       // shared memory (two buffers, one 64-thread named barrier per quarter), so both hold
@@ -716,7 +719,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_after_sync();
     }
     const float inv = (l > 0.f) ? 1.f / l : 0.f;
-    const bool row_ok = q_local < wk.seqlen_q;
+    const bool row_ok = wg < L::kQTiles && q_local < wk.seqlen_q;  // an unused second tile owns no rows
     __half* o_row = static_cast<__half*>(p.o) + wk.o_base +
                     static_cast<int64_t>(q_local) * p.o_strides.row;
 #pragma unroll
