@@ -158,14 +158,22 @@ int sm_count() {
 }
 
 // Forward kernel variant.  Two 128-row tiles per CTA let one tile's softmax run under the other's
-// MMAs; when that grid would leave SMs without a CTA, one tile per CTA (both softmax warpgroups on
-// it, half the score columns each) doubles the number of CTAs and shortens each tile's softmax.
+// MMAs and fetch every K / V tile once for 256 query rows; a CTA of one tile (the softmax warpgroups
+// take alternate key tiles of it) takes about 0.6 of the time of a two-tile CTA, measured on grids of
+// many waves.  One tile per CTA is chosen where its larger number of shorter waves finishes first:
+// grids that leave SMs without a two-tile CTA, or that end in a mostly empty wave.
 std::atomic<int> g_fwd_variant{FAL_FWD_AUTO};  // fal_set_fwd_variant
 
 int forward_cta_rows(int head_dim, int64_t blocks_of_256_rows, int64_t units) {
   const int forced = g_fwd_variant.load(std::memory_order_relaxed);
-  const bool one_tile = forced == FAL_FWD_ONE_TILE ||
-                        (forced == FAL_FWD_AUTO && blocks_of_256_rows * units < sm_count());
+  bool one_tile = forced == FAL_FWD_ONE_TILE;
+  if (forced == FAL_FWD_AUTO) {
+    const int64_t sms = sm_count() > 0 ? sm_count() : 148;
+    const int64_t ctas2 = blocks_of_256_rows * units;
+    const int64_t waves2 = (ctas2 + sms - 1) / sms;
+    const int64_t waves1 = (2 * ctas2 + sms - 1) / sms;
+    one_tile = 6 * waves1 < 10 * waves2;
+  }
   return fal::fwd_cta_rows(head_dim, one_tile);
 }
 

@@ -11,21 +11,32 @@
 // chunk of new tokens behind a cached prefix, which the reference computes
 // eagerly (flash_attn_legacy/integrations.py:77-98).
 //
-// One CTA owns 256 query rows of one (batch, head): two 128-row tiles, each
-// with its own softmax warpgroup, S/P tile and O accumulator in TMEM.  The
-// single MMA-issuing thread interleaves the two tiles so that one tile's
-// softmax overlaps the other's tensor-core work:
+// Two CTA shapes, both 384 threads:
 //
-//   warps 0-3   softmax + output for rows   0..127  (TMEM lanes by warp % 4)
-//   warps 4-7   softmax + output for rows 128..255
+//   warps 0-3   softmax warpgroup 0 (TMEM lanes by warp % 4)
+//   warps 4-7   softmax warpgroup 1
 //   warp  8     TMA producer (one elected lane)
 //   warp  9     tcgen05.mma issuer (one elected lane), TMEM owner
 //   warps 10-11 idle (they complete the third warpgroup so that registers can be
 //               moved from it to the softmax warpgroups with setmaxnreg)
 //
+// Two tiles (256 query rows of one (batch, head) per CTA): each softmax warpgroup owns a 128-row
+// tile with its own S/P block and O accumulator in TMEM; the MMA-issuing thread interleaves the
+// two tiles so that one tile's softmax overlaps the other's tensor-core work.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
-// P (fp16) overwrites the first 64 columns of its S tile and feeds the PV MMA
-// straight from TMEM.
+//
+// One tile (128 query rows per CTA; head_dim 256, and the smaller grids of 64 / 128): the two S
+// blocks are two buffers of the one tile, key tiles alternate between them and between the
+// warpgroups (warpgroup j % 2 takes key tile j), and there is one O accumulator.  The scores of
+// key tile j + 2 are computed as soon as P V of tile j is issued, so a warpgroup finds its next
+// scores waiting; the warpgroups share the running row maximum through shared memory (only that
+// short part of a step is serial) and keep private row sums that are added in the epilogue.
+// TMEM columns: S even [0,128) S odd [128,256) P even [256,320) P odd [320,384) O [384,384+D):
+// P has columns of its own here, so a score buffer is free again as soon as its warpgroup has read it.
+// (head_dim 256 has no columns left for this: one warpgroup takes every key tile, as in a two-tile CTA.)
+//
+// P (fp16) feeds the PV MMA straight from TMEM; in the two-tile CTA it overwrites the first 64
+// columns of its S block.
 #define FAL_WAIT_SLOW_PATH_INLINE  // this kernel uses setmaxnreg, which rules out calls
 #include "fal_common.h"
 #include "fal_launch.h"
@@ -36,14 +47,17 @@ namespace fal {
 namespace {
 
 // Kernel variants (ONE_TILE):
-//   false  two query tiles per CTA, one softmax warpgroup per tile (a thread owns a 128-column row)
-//   true   one query tile per CTA, both softmax warpgroups on it (a thread owns 64 columns of a row)
-// Three warpgroups either way: softmax 0, softmax 1, {TMA producer, MMA issuer, 2 idle warps}.
-// (Two tiles with two softmax warpgroups EACH -- 640 threads, 104 registers per softmax thread -- was
-// built and measured on B4 Hq32 Hkv8 N4096 d128 causal: 583 against 515 us.  ncu: tensor pipe 45.7 %
-// against 54.3 %, long-scoreboard stalls per issue 4.9 against 2.5, MIO throttle 1.0 against 0.1: the
-// register cut spills inside the exponential loop and five warps per scheduler crowd the one
-// MMA-issuing thread.  It is not part of the library.)
+//   false  two query tiles per CTA, one softmax warpgroup per tile
+//   true   one query tile per CTA, the softmax warpgroups take alternate key tiles of it
+// A thread owns one 128-column score row either way.
+// Built, measured on B4 Hq32 Hkv8 N4096 d128 causal and not kept:
+//  - two tiles with two softmax warpgroups EACH (640 threads, 104 registers per softmax thread): 583
+//    against 515 us; ncu: tensor pipe 45.7 % against 54.3 %, long-scoreboard stalls per issue 4.9
+//    against 2.5: the register cut spills inside the exponential loop and five warps per scheduler
+//    crowd the one MMA-issuing thread;
+//  - one tile with both warpgroups on the SAME key tile, 64 score columns per thread and the row
+//    maxima exchanged every step: 600 us even with two score buffers; the two warps of a scheduler
+//    then run in lockstep (both load, both exponentiate) instead of filling each other's gaps.
 constexpr int kFwdThreads = 384;
 constexpr int kSmWarps = 8;  // softmax warps; then producer, issuer, 2 idle
 constexpr int kTileM = 128;   // query rows per softmax warpgroup
@@ -99,13 +113,12 @@ template <int D, bool ONE_TILE>
 struct FwdSmem {
   // One 128-row query tile per CTA: always at head_dim 256 (its O accumulator alone takes 256 of the
   // 512 TMEM columns; single K and V buffers, a 128 x 256 tile is 64 KB), and at head_dim 64 / 128
-  // when two-tile CTAs would leave SMs without work.  At 64 / 128 both softmax warpgroups then share
-  // the one tile, 64 score columns each (kSplitCols); at 256, where the single K / V buffer and not the
-  // softmax sets the pace, one warpgroup keeps whole rows and the other idles (measured 3 - 6 % faster
-  // there than the shared tile).
-  static constexpr bool kSplitCols = ONE_TILE && D != 256;
+  // when two-tile CTAs would leave SMs without work.
   static_assert(ONE_TILE || D != 256, "head_dim 256 runs one query tile per CTA");
   static constexpr int kQTiles = ONE_TILE ? 1 : 2;
+  // One tile at head_dim 64 / 128: the softmax warpgroups take alternate key tiles (kAlt).  At 256 there
+  // is no TMEM left for that (P needs columns of its own), one warpgroup takes every key tile.
+  static constexpr bool kAlt = ONE_TILE && D != 256;
   static constexpr int kCtaRows = kQTiles * kTileM;
   static constexpr int kStages = (D == 256) ? 1 : (D == 128) ? 2 : 4;
   static constexpr int kBoxes = D / 64;                 // 64-element (128-byte) column boxes
@@ -116,13 +129,12 @@ struct FwdSmem {
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kBarOff = kVOff + kStages * kTileBytes;
   // barriers: q_full[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_ready[2] p_ready[2] o_done[2]
-  //           p_half[2]
-  static constexpr int kNumBars = 2 + 4 * kStages + 8;
+  //           p_half[2] s_free[2]
+  static constexpr int kNumBars = 2 + 4 * kStages + 10;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
-  // split-column softmax: row maxima (two buffers) and row sums the two column halves of a row exchange
+  // one tile: the running row maximum the warpgroups hand to each other, and their two row sums
   static constexpr int kXchOff = kMiscOff + 16;
-  static constexpr int kXchTileBytes = 3 * 2 * kTileM * 4;
-  static constexpr int kXchBytes = kSplitCols ? kXchTileBytes : 0;
+  static constexpr int kXchBytes = kAlt ? 3 * kTileM * 4 : 0;
   static constexpr int kBytes = kXchOff + kXchBytes;
   static constexpr int kAllocBytes = kBytes + 1024;  // room to align the base to 1024
 };
@@ -226,7 +238,8 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t bar0 = sbase + L::kBarOff;
   auto bar = [&](int i) { return bar0 + 8u * i; };
   const int iQFull = 0, iKFull = 2, iKEmpty = 2 + NS, iVFull = 2 + 2 * NS, iVEmpty = 2 + 3 * NS,
-            iSReady = 2 + 4 * NS, iPReady = iSReady + 2, iODone = iSReady + 4, iPHalf = iSReady + 6;
+            iSReady = 2 + 4 * NS, iPReady = iSReady + 2, iODone = iSReady + 4, iPHalf = iSReady + 6,
+            iSFree = iSReady + 8;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kMiscOff + 4);
   const WaitCtx wctx{abort_flag, p.status};
@@ -290,6 +303,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(bar(iPReady + w), kTileM);
       mbar_init(bar(iPHalf + w), kTileM);
       mbar_init(bar(iODone + w), 1);
+      mbar_init(bar(iSFree + w), kTileM);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tm_q);
@@ -299,6 +313,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (ntile[w] > 0) load_q(w);
     if (n_max > 0) {
       load_k(0);
+      if (NS > 1 && n_max > 1) load_k(1);
       load_v(0);
     }
   }
@@ -315,16 +330,25 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   // keep a whole 128-wide score row in registers, the producer / issuer warpgroup needs few.
   if (warp >= kSmWarps) {
     setmaxnreg_dec<kRegsOther>();
-    if (warp == kSmWarps) {
-    // ===================== TMA producer =====================================
+    if (warp == kSmWarps || warp == kSmWarps + 2) {
+    // ===================== TMA producers ====================================
+    // K tiles from warp 8, V tiles from warp 10: each ring refills as soon as its own stage is free
+    // (the first tiles went out during setup).
     if (lane == 0) {
-      for (int j = 1; j < n_max; ++j) {  // tile 0 went out during setup
-        const int s = j % NS;
-        const int use = j / NS;
-        if (use > 0) mbar_wait(bar(iKEmpty + s), (use - 1) & 1, wctx, kBarKEmpty + s);
-        load_k(j);
-        if (use > 0) mbar_wait(bar(iVEmpty + s), (use - 1) & 1, wctx, kBarVEmpty + s);
-        load_v(j);
+      if (warp == kSmWarps) {
+        for (int j = (NS > 1) ? 2 : 1; j < n_max; ++j) {
+          const int s = j % NS;
+          const int use = j / NS;
+          if (use > 0) mbar_wait(bar(iKEmpty + s), (use - 1) & 1, wctx, kBarKEmpty + s);
+          load_k(j);
+        }
+      } else {
+        for (int j = 1; j < n_max; ++j) {
+          const int s = j % NS;
+          const int use = j / NS;
+          if (use > 0) mbar_wait(bar(iVEmpty + s), (use - 1) & 1, wctx, kBarVEmpty + s);
+          load_v(j);
+        }
       }
     }
     __syncwarp();
@@ -339,36 +363,84 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                 smem_desc_lo(sbase + L::kQOff + L::kTileBytes, 16)};
       // S[w] = Q[w] K_j^T : both operands K-major (head_dim contiguous), 16 head-dim
       // elements (32 bytes inside the 128-byte swizzle row) per instruction.
-      auto issue_qk = [&](int w, int j) {
+      // sb = score buffer (TMEM columns [128 sb, +128)), qt = query tile in shared memory.
+      auto issue_qk = [&](int sb, int qt, int j) {
         const uint32_t k_lo = smem_desc_lo(sbase + L::kKOff + (j % NS) * L::kTileBytes, 16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * L::kBoxBytes + (ks & 3) * 32) >> 4;
-          umma_ss(tmem_base + w * kTileN, smem_desc_join(q_lo[w] + off, kHi),
+          umma_ss(tmem_base + sb * kTileN, smem_desc_join(q_lo[qt] + off, kHi),
                   smem_desc_join(k_lo + off, kHi), idesc_qk, ks > 0 ? 1u : 0u);
         }
       };
       // O[w] += P[w] V_j : A = P from TMEM (8 columns of packed fp16 per 16 keys), B = V
       // MN-major (head_dim contiguous): 16 keys = 2048 bytes per step, 64-column halves
       // kBoxBytes apart (LBO), 8-key groups 1024 bytes apart (SBO).
-      auto issue_pv = [&](int w, int j, int half) {
+      // sb = buffer that holds P, ot = output accumulator.
+      auto issue_pv = [&](int sb, int ot, int j, int half) {
         const uint32_t v_lo = smem_desc_lo(sbase + L::kVOff + (j % NS) * L::kTileBytes, L::kBoxBytes);
+        const uint32_t t_o = L::kAlt ? tmem_base + 384 : tmem_base + 256 + ot * D;
+        const uint32_t t_p = L::kAlt ? tmem_base + 256 + sb * 64 : tmem_base + sb * kTileN;
 #pragma unroll
         for (int kk = 0; kk < kTileN / 32; ++kk) {
           const int ks = half * (kTileN / 32) + kk;
-          umma_ts(tmem_base + 256 + w * D, tmem_base + w * kTileN + ks * 8,
+          umma_ts(t_o, t_p + ks * 8,
                   smem_desc_join(v_lo + ((ks * 2048) >> 4), kHi), idesc_pv,
                   (j > 0 || ks > 0) ? 1u : 0u);
         }
       };
 
+      if constexpr (L::kAlt) {
+        // One query tile, two score buffers (barrier index = buffer, parity = (j / 2) % 2).  The scores
+        // of key tile j + 2 are issued as soon as the warpgroup of tile j has read its scores out of
+        // the buffer (s_free), so it finds the next ones waiting; the order below follows the order
+        // the events come in when the two warpgroups run half a step apart.
+        const int nt = ntile[0];
+        auto next_scores = [&](int j) {  // scores of key tile j + 2 into the buffer of tile j
+          if (j >= 0 && j + 2 < nt) {
+            const int sb = j & 1;
+            const int s2 = (j + 2) % NS;
+            mbar_wait(bar(iSFree + sb), (j >> 1) & 1, wctx, kBarSReady + sb);
+            mbar_wait(bar(iKFull + s2), ((j + 2) / NS) & 1, wctx, kBarKFull + s2);
+            tc_fence_after_sync();
+            issue_qk(sb, 0, j + 2);
+            tc_commit(bar(iSReady + sb));
+            tc_commit(bar(iKEmpty + s2));
+          }
+        };
+        if (nt > 0) {
+          mbar_wait(bar(iQFull), 0, wctx, kBarQFull);
+          for (int j = 0; j < min(nt, 2); ++j) {
+            mbar_wait(bar(iKFull + j % NS), (j / NS) & 1, wctx, kBarKFull + j % NS);
+            tc_fence_after_sync();
+            issue_qk(j, 0, j);
+            tc_commit(bar(iSReady + j));
+            tc_commit(bar(iKEmpty + j % NS));
+          }
+          next_scores(0);
+        }
+        for (int j = 0; j < nt; ++j) {
+          const int sb = j & 1;
+          const int s = j % NS;
+          mbar_wait(bar(iPHalf + sb), (j >> 1) & 1, wctx, kBarPReady + sb);
+          mbar_wait(bar(iVFull + s), (j / NS) & 1, wctx, kBarVFull + s);
+          tc_fence_after_sync();
+          issue_pv(sb, 0, j, 0);
+          next_scores(j + 1);
+          mbar_wait(bar(iPReady + sb), (j >> 1) & 1, wctx, kBarPReady + sb);
+          tc_fence_after_sync();
+          issue_pv(sb, 0, j, 1);
+          tc_commit(bar(iODone + sb));
+          tc_commit(bar(iVEmpty + s));
+        }
+      } else {
       if (n_max > 0) {
         mbar_wait(bar(iKFull + 0), 0, wctx, kBarKFull);
         for (int w = 0; w < 2; ++w) {
           if (ntile[w] == 0) continue;
           mbar_wait(bar(iQFull + w), 0, wctx, kBarQFull + w);
           tc_fence_after_sync();
-          issue_qk(w, 0);
+          issue_qk(w, w, 0);
           tc_commit(bar(iSReady + w));
         }
         tc_commit(bar(iKEmpty + 0));
@@ -383,21 +455,22 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mbar_wait(bar(iPHalf + w), j & 1, wctx, kBarPReady + w);
           mbar_wait(bar(iVFull + s), use & 1, wctx, kBarVFull + s);
           tc_fence_after_sync();
-          issue_pv(w, j, 0);
+          issue_pv(w, w, j, 0);
           mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w);
           tc_fence_after_sync();
-          issue_pv(w, j, 1);
+          issue_pv(w, w, j, 1);
           tc_commit(bar(iODone + w));
           if (w == 1 || j >= ntile[1]) tc_commit(bar(iVEmpty + s));
           if (j + 1 < ntile[w]) {
             const int s1 = (j + 1) % NS;
             mbar_wait(bar(iKFull + s1), ((j + 1) / NS) & 1, wctx, kBarKFull + s1);
             tc_fence_after_sync();
-            issue_qk(w, j + 1);
+            issue_qk(w, w, j + 1);
             tc_commit(bar(iSReady + w));
             if (w == 1 || j + 1 >= ntile[1]) tc_commit(bar(iKEmpty + s1));
           }
         }
+      }
       }
     }
     __syncwarp();
@@ -405,207 +478,42 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else {
     // ===================== softmax + output =================================
     setmaxnreg_inc<kRegsSoftmax>();
-    if constexpr (L::kSplitCols) {
-      // Two warps per TMEM lane quarter of the tile: one for score columns [0, 64) (column half 0), one
-      // for [64, 128), on the same 32 rows.  They exchange the row maxima of every step through
-      // shared memory (two buffers, one 64-thread named barrier per quarter), so both hold
-      // the same reference maximum and take the same rescale decision; the row sums are added once,
-      // in the epilogue.  The first 64 keys of P are column half 0's work (p_half), the rest half 1's
-      // (p_ready).  A thread keeps 32 scores in registers at a time; the other 32 are read again from
-      // tensor memory under the first 32 exponentials.
-      const int ch = (warp >> 2) & 1;
-      const int quarter = warp & 3;
-      const int row = quarter * 32 + lane;
-      const int q_tile0 = wk.qblk * kCtaRows;
-      const int q_local = q_tile0 + row;
-      const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-      const uint32_t tS = tmem_base + lane_addr;
-      const uint32_t tO = tmem_base + lane_addr + 256;
-      const int nt = ntile[0];
-      const float c2 = p.scale_log2;
-      float* xch = reinterpret_cast<float*>(sgen + L::kXchOff);  // [3][2 halves][128 rows]
-      const int pair_bar = 1 + quarter;
-      auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
-      const int iS = iSReady, iPH = iPHalf, iPR = iPReady, iOD = iODone;
-
-      float m_ref = kNegInf;
-      float l = 0.f;
-      for (int j = 0; j < nt; ++j) {
-        mbar_wait(bar(iS), j & 1, wctx, kBarSReady);
-        tc_fence_after_sync();
-        const int kv0 = j * kTileN;
-        int limit = wk.seqlen_k - kv0;  // columns c < limit of the tile are visible
-        if (CAUSAL) limit = min(limit, q_local + cshift - kv0 + 1);
-        limit -= ch * 64;  // in this thread's own 64 columns
-        const bool tile_mask =
-            (kv0 + kTileN > wk.seqlen_k) || (CAUSAL && (kv0 + kTileN - 1 > q_tile0 + cshift));
-
-        // Row maximum over this thread's 64 columns; chunk 1 stays in registers, chunk 0 is read again below.
-        uint32_t s1[32];
-        float mx;
-        {
-          uint32_t s0[32];
-          tmem_ld_32x32b_x32(tS + ch * 64, s0);
-          tmem_ld_32x32b_x32(tS + ch * 64 + 32, s1);
-          tmem_wait_ld();
-          if (tile_mask) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (i >= limit) s0[i] = __float_as_uint(kNegInf);
-              if (32 + i >= limit) s1[i] = __float_as_uint(kNegInf);
-            }
-          }
-          float part[4];
-#pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf) {
-            const int b0 = hlf * 16;
-            float a = fmax3(__uint_as_float(s0[b0]), __uint_as_float(s0[b0 + 1]), __uint_as_float(s0[b0 + 2]));
-            float b = fmax3(__uint_as_float(s1[b0]), __uint_as_float(s1[b0 + 1]), __uint_as_float(s1[b0 + 2]));
-#pragma unroll
-            for (int i = 3; i + 1 < 16; i += 2) {
-              a = fmax3(a, __uint_as_float(s0[b0 + i]), __uint_as_float(s0[b0 + i + 1]));
-              b = fmax3(b, __uint_as_float(s1[b0 + i]), __uint_as_float(s1[b0 + i + 1]));
-            }
-            part[hlf] = fmaxf(a, __uint_as_float(s0[b0 + 15]));
-            part[2 + hlf] = fmaxf(b, __uint_as_float(s1[b0 + 15]));
-          }
-          mx = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
-        }
-        float* xm = xch + (j & 1) * 2 * kTileM;
-        xm[ch * kTileM + row] = mx;
-        pair_sync();
-        mx = fmaxf(mx, xm[(ch ^ 1) * kTileM + row]);
-        const float m_new = fmaxf(m_ref, mx);
-
-        if (j == 0) {
-          m_ref = m_new;
-        } else {
-          const bool need = (m_new - m_ref) * c2 > kRescaleThreshold;
-          if (__any_sync(0xffffffffu, need)) {
-            // PV of the previous step must have landed before O is touched; each half rescales
-            // its own D/2 output columns.
-            mbar_wait(bar(iOD), (j - 1) & 1, wctx, kBarODone);
-            tc_fence_after_sync();
-            const float alpha = (m_new == kNegInf) ? 1.f : fast_exp2((m_ref - m_new) * c2);
-#pragma unroll
-            for (int c = 0; c < D / 64; ++c) {
-              uint32_t r[32];
-              tmem_ld_32x32b_x32(tO + ch * (D / 2) + c * 32, r);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st_32x32b_x32(tO + ch * (D / 2) + c * 32, r);
-            }
-            l *= alpha;
-            m_ref = m_new;
-          }
-        }
-        const float moff = (m_ref == kNegInf) ? 0.f : m_ref * c2;
-
-        const uint64_t c2p = pack_f32x2(c2, c2);
-        const uint64_t moffp = pack_f32x2(-moff, -moff);
-        uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-        // 32 scores -> exp2 -> packed fp16 P (16 registers)
-        auto exp_chunk = [&](const uint32_t (&sc)[32], uint32_t (&pk)[16]) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const uint64_t x01 = ffma2(pack_f32x2(__uint_as_float(sc[i + 0]), __uint_as_float(sc[i + 1])), c2p, moffp);
-            const uint64_t x23 = ffma2(pack_f32x2(__uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3])), c2p, moffp);
-            const uint64_t p01 = tile_exp2_pair<0>(i, x01);
-            const uint64_t p23 = tile_exp2_pair<1>(i, x23);
-            sum_a = fadd2(sum_a, p01);
-            sum_b = fadd2(sum_b, p23);
-            float p0, p1, p2, p3;
-            unpack_f32x2(p01, p0, p1);
-            unpack_f32x2(p23, p2, p3);
-            pk[(i >> 1) + 0] = pack_half2(p0, p1);
-            pk[(i >> 1) + 1] = pack_half2(p2, p3);
-          }
-        };
-        {
-          // Packed P of keys [64 ch + 32 c, +32) goes to TMEM columns [32 ch + 16 c, +16) of the tile's
-          // S block.  For column half 0 those columns hold its own chunk-0 scores, so chunk 0 is read
-          // back into registers (under the exponentials of chunk 1) before any P is stored.
-          uint32_t s0[32];
-          tmem_ld_32x32b_x32(tS + ch * 64, s0);
-          uint32_t pk[16];
-          exp_chunk(s1, pk);
-          tmem_wait_ld();
-          tmem_st_32x32b_x16(tS + (2 * ch + 1) * 16, pk);
-          if (tile_mask) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i >= limit) s0[i] = __float_as_uint(kNegInf);
-          }
-          exp_chunk(s0, pk);
-          tmem_st_32x32b_x16(tS + (2 * ch) * 16, pk);
-        }
-        float sum0, sum1, sum2, sum3;
-        unpack_f32x2(sum_a, sum0, sum1);
-        unpack_f32x2(sum_b, sum2, sum3);
-        l += (sum0 + sum1) + (sum2 + sum3);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(bar(ch == 0 ? iPH : iPR));
-      }
-
-      // ---- epilogue: O / l -> fp16, LSE (each half its own D/2 columns) ----------
-      if (nt > 0) {
-        mbar_wait(bar(iOD), (nt - 1) & 1, wctx, kBarODone);
-        tc_fence_after_sync();
-      }
-      float* xl = xch + 2 * 2 * kTileM;
-      xl[ch * kTileM + row] = l;
-      pair_sync();
-      l += xl[(ch ^ 1) * kTileM + row];
-      const float inv = (l > 0.f) ? 1.f / l : 0.f;
-      const bool row_ok = q_local < wk.seqlen_q;
-      __half* o_row = static_cast<__half*>(p.o) + wk.o_base + static_cast<int64_t>(q_local) * p.o_strides.row +
-                      ch * (D / 2);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t r[32];
-        if (nt > 0) {
-          tmem_ld_32x32b_x32(tO + ch * (D / 2) + c * 32, r);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (ch * (D / 2) + c * 32 + v * 8 >= p.head_dim) continue;  // head_dim 32 / 96: no such column
-            uint4 out;
-            out.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
-            out.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
-            out.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
-            out.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(o_row + c * 32 + v * 8) = out;
-          }
-        }
-      }
-      if (row_ok && ch == 0) {
-        const float lse = (nt > 0 && m_ref != kNegInf) ? m_ref * p.scale + logf(fmaxf(l, 1e-20f)) : kNegInf;
-        p.lse[wk.lse_base + static_cast<int64_t>(q_local) * p.lse_strides.row] = lse;
-      }
-    } else {
+    {
+    // kAlt (one query tile): warpgroup wg takes key tiles wg, wg + 2, ... of the one tile, from score
+    // buffer wg.  Otherwise warpgroup wg owns query tile wg and takes every key tile of it.
+    constexpr bool kAlt = L::kAlt;
     const int wg = warp >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    const int q_tile0 = wk.qblk * kCtaRows + wg * kTileM;  // first row of this tile (local)
+    const int q_tile0 = wk.qblk * kCtaRows + (kAlt ? 0 : wg * kTileM);  // first row of this tile (local)
     const int q_local = q_tile0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tS = tmem_base + lane_addr + wg * kTileN;
-    const uint32_t tO = tmem_base + lane_addr + 256 + wg * D;
-    const int nt = ntile[wg];
+    const uint32_t tO = tmem_base + lane_addr + (kAlt ? 384 : 256 + wg * D);
+    const uint32_t tP = kAlt ? tmem_base + lane_addr + 256 + wg * 64 : tS;  // packed fp16 P
+    const int nt = kAlt ? ntile[0] : ntile[wg];
     const float c2 = p.scale_log2;
+    // kAlt: the reference maximum of a row travels between the two threads that own the row (same
+    // quarter, same lane, other warpgroup) through xm[row]; named barrier 1 + 2 quarter + w says
+    // "warpgroup w has published" (the publisher arrives, the reader syncs; the two strictly alternate).
+    float* xm = reinterpret_cast<float*>(sgen + L::kXchOff);
+    float* xl = xm + kTileM;  // [2][kTileM] row sums, added in the epilogue
+    auto hand_over = [&](float m) {
+      xm[row] = m;
+      __threadfence_block();
+      asm volatile("bar.arrive %0, 64;" ::"r"(1 + 2 * quarter + wg) : "memory");
+    };
+    auto take_over = [&]() -> float {
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + 2 * quarter + (wg ^ 1)) : "memory");
+      return xm[row];
+    };
 
     float m_ref = kNegInf;
     float l = 0.f;
 
-    for (int j = 0; j < nt; ++j) {
-      mbar_wait(bar(iSReady + wg), j & 1, wctx, kBarSReady + wg);
+    for (int j = kAlt ? wg : 0; j < nt; j += kAlt ? 2 : 1) {
+      const int par = kAlt ? (j >> 1) & 1 : j & 1;
+      mbar_wait(bar(iSReady + wg), par, wctx, kBarSReady + wg);
       tc_fence_after_sync();
       const int kv0 = j * kTileN;
       int limit = wk.seqlen_k - kv0;  // columns c < limit are visible
@@ -618,6 +526,10 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tS + c * 32, sr[c]);
       tmem_wait_ld();
+      if (kAlt) {  // the scores are in registers: the buffer may take those of key tile j + 2
+        tc_fence_before_sync();
+        mbar_arrive(bar(iSFree + wg));
+      }
       if (tile_mask) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -645,6 +557,14 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mx = fmaxf(fmax3(part[0], part[1], part[2]), fmax3(part[3], part[4], part[5]));
         mx = fmax3(mx, part[6], part[7]);
       }
+      if (kAlt && j > 0) {
+        // The other warpgroup's reference after key tile j - 1: bring the private row sum onto it.
+        const float m_other = take_over();
+        if (m_other != m_ref) {
+          l = (m_ref == kNegInf) ? 0.f : l * fast_exp2((m_ref - m_other) * c2);
+          m_ref = m_other;
+        }
+      }
       const float m_new = fmaxf(m_ref, mx);
 
       if (j == 0) {
@@ -653,7 +573,8 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const bool need = (m_new - m_ref) * c2 > kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
           // PV of the previous step must have landed before O is touched.
-          mbar_wait(bar(iODone + wg), (j - 1) & 1, wctx, kBarODone + wg);
+          if (kAlt) mbar_wait(bar(iODone + (wg ^ 1)), ((j - 1) >> 1) & 1, wctx, kBarODone + (wg ^ 1));
+          else mbar_wait(bar(iODone + wg), (j - 1) & 1, wctx, kBarODone + wg);
           tc_fence_after_sync();
           const float alpha = (m_new == kNegInf) ? 1.f : fast_exp2((m_ref - m_new) * c2);
 #pragma unroll
@@ -667,6 +588,14 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
           l *= alpha;
           m_ref = m_new;
+        }
+      }
+      if (kAlt) {
+        hand_over(m_ref);
+        // P of key tile j - 2 sits where this step's P goes: its P V must have read it.
+        if (j >= 2) {
+          mbar_wait(bar(iODone + wg), ((j - 2) >> 1) & 1, wctx, kBarODone + wg);
+          tc_fence_after_sync();
         }
       }
       const float moff = (m_ref == kNegInf) ? 0.f : m_ref * c2;
@@ -695,7 +624,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           pk[(i >> 1) + 0] = pack_half2(p0, p1);
           pk[(i >> 1) + 1] = pack_half2(p2, p3);
         }
-        tmem_st_32x32b_x16(tS + c * 16, pk);
+        tmem_st_32x32b_x16(tP + c * 16, pk);
         if (c == 1) {  // the first 64 keys of P are in TMEM: the PV MMA may start on them
           tmem_wait_st();
           tc_fence_before_sync();
@@ -715,15 +644,37 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     // ---- epilogue: O / l -> fp16, LSE -----------------------------------------
     if (nt > 0) {
-      mbar_wait(bar(iODone + wg), (nt - 1) & 1, wctx, kBarODone + wg);
+      if (kAlt) mbar_wait(bar(iODone + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1, wctx, kBarODone + ((nt - 1) & 1));
+      else mbar_wait(bar(iODone + wg), (nt - 1) & 1, wctx, kBarODone + wg);
       tc_fence_after_sync();
     }
+    int col0 = 0;           // first output column this thread writes
+    int ncol = D;           // and how many
+    bool row_ok = wg < L::kQTiles && q_local < wk.seqlen_q;  // an unused second tile owns no rows
+    if (kAlt) {
+      // The warpgroup that did not take the last key tile picks up the final reference (the last
+      // hand-over has no other reader); then the two row sums are added, and each warpgroup
+      // writes one half of the output columns.
+      if (nt > 0 && ((nt - 1) & 1) != wg) {
+        const float m_other = take_over();
+        if (m_other != m_ref) {
+          l = (m_ref == kNegInf) ? 0.f : l * fast_exp2((m_ref - m_other) * c2);
+          m_ref = m_other;
+        }
+      }
+      xl[wg * kTileM + row] = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(9 + quarter) : "memory");
+      l += xl[(wg ^ 1) * kTileM + row];
+      col0 = wg * (D / 2);
+      ncol = D / 2;
+      row_ok = q_local < wk.seqlen_q;
+    }
     const float inv = (l > 0.f) ? 1.f / l : 0.f;
-    const bool row_ok = wg < L::kQTiles && q_local < wk.seqlen_q;  // an unused second tile owns no rows
     __half* o_row = static_cast<__half*>(p.o) + wk.o_base +
                     static_cast<int64_t>(q_local) * p.o_strides.row;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
+      if (c * 32 < col0 || c * 32 >= col0 + ncol) continue;
       uint32_t r[32];
       if (nt > 0) {
         tmem_ld_32x32b_x32(tO + c * 32, r);
@@ -745,12 +696,11 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
     }
-    if (row_ok) {
+    if (row_ok && (!kAlt || wg == 0)) {
       const float lse = (nt > 0 && m_ref != kNegInf) ? m_ref * p.scale + logf(fmaxf(l, 1e-20f))
                                                       : kNegInf;
       p.lse[wk.lse_base + static_cast<int64_t>(q_local) * p.lse_strides.row] = lse;
     }
-  
     }
   }
 

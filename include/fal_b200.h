@@ -93,11 +93,11 @@ FAL_API int fal_fwd(const void* q, const void* k, const void* v, void* o, float*
  * Forward kernel variants.  A thread block takes one or two 128-row query tiles:
  *   FAL_FWD_TWO_TILES        two tiles, one softmax warpgroup each (a thread owns a whole score row),
  *                            one tile's softmax running under the other tile's MMAs;
- *   FAL_FWD_ONE_TILE         one tile with both softmax warpgroups on it (a thread owns 64 columns
- *                            of a row): twice as many blocks, for problems whose two-tile grid would
- *                            not give every SM a block.
- * FAL_FWD_AUTO (default) chooses per call (one tile when the two-tile grid has fewer blocks than the
- * device has SMs; head_dim 256 always runs one tile).  fal_set_fwd_variant forces a variant for
+ *   FAL_FWD_ONE_TILE         one tile, the softmax warpgroups taking alternate key tiles of it from
+ *                            two score buffers: twice as many, shorter blocks, for problems whose
+ *                            two-tile grid would leave SMs without a block or end in a thin wave.
+ * FAL_FWD_AUTO (default) chooses per call (one tile when its waves, at 0.6 of a two-tile wave each,
+ * finish first; head_dim 256 always runs one tile).  fal_set_fwd_variant forces a variant for
  * every later call in the process: a tuning and test control -- the results agree within rounding.
  * The reference picks tile sizes from a compile-time table per architecture instead
  * (csrc/include/flash_attn_common.h:157-292).

@@ -224,12 +224,13 @@ def test_rectangular_forward_top_left_causal(ext):
 @pytest.mark.parametrize("tiles", [1, 2])
 @pytest.mark.parametrize("d", [64, 128])
 def test_every_forward_kernel_variant(ext, tiles, d):
-    """Both forward variants -- one 128-row tile per thread block with both softmax warpgroups on it
-    (1), two tiles with one warpgroup each (2) -- on the same problems; by default the library picks
-    by grid size, so small problems would otherwise only ever see the first."""
+    """Both forward variants -- one 128-row tile per thread block whose key tiles alternate between the
+    two softmax warpgroups (1), two tiles with one warpgroup each (2) -- on the same problems; by
+    default the library picks by grid size, so small problems would otherwise only ever see the first."""
     ext.set_forward_variant(tiles)
     try:
-        for n, hq, hkv, causal in ((1, 4, 2, True), (100, 4, 2, True), (257, 4, 4, False), (777, 8, 2, True),
+        for n, hq, hkv, causal in ((1, 4, 2, True), (100, 4, 2, True), (200, 2, 2, False), (257, 4, 4, False),
+                                   (777, 8, 2, True),
                                    (1500, 4, 1, True), (2048, 2, 2, False)):
             g = torch.Generator().manual_seed(n + d + tiles)
             q, k, v = rand_half(g, 2, hq, n, d), rand_half(g, 2, hkv, n, d), rand_half(g, 2, hkv, n, d)
@@ -243,6 +244,13 @@ def test_every_forward_kernel_variant(ext, tiles, d):
         q, k, v = rand_half(g, 1, 2, 600, d) * 6, rand_half(g, 1, 2, 600, d) * 6, rand_half(g, 1, 2, 600, d)
         o, lse = ext.forward(q.cuda(), k.cuda(), v.cuda(), 1 / math.sqrt(d), True)
         check_fwd(o, lse, *orc.attention_fwd(q, k, v, 1 / math.sqrt(d), True))
+        # scores that keep growing along the keys: the maximum moves at most steps, so (variant 1) both
+        # warpgroups rescale O and bring their private row sums onto the other's reference
+        ramp = (1 + 7 * torch.arange(1500) / 1500).view(1, 1, 1500, 1)
+        q, k, v = rand_half(g, 1, 2, 1500, d), (rand_half(g, 1, 2, 1500, d) * ramp).half(), rand_half(g, 1, 2, 1500, d)
+        for causal in (False, True):
+            o, lse = ext.forward(q.cuda(), k.cuda(), v.cuda(), 1 / math.sqrt(d), causal)
+            check_fwd(o, lse, *orc.attention_fwd(q, k, v, 1 / math.sqrt(d), causal))
         # packed sequences and the end-aligned mask
         lens = [300, 17, 1025, 256]
         qp, kp, vp, _, cu = packed_inputs(g, lens, 4, 2, d)
