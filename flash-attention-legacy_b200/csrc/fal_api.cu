@@ -272,19 +272,26 @@ int fal_last_cuda_error(void) { return g_last_cuda_error; }
 
 const char* fal_version(void) { return "0.1.0"; }
 
-int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
-            int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
-            const fal_strides* q_strides, const fal_strides* k_strides,
-            const fal_strides* v_strides, const fal_strides* o_strides, float softmax_scale,
-            int is_causal, int* status, void* stream) {
+namespace {
+
+// The batched forward; `seqused_k` (device, one int per batch entry, or null) limits every entry to
+// its own number of keys, seqlen_k then being the capacity the tensors are laid out for.
+int fwd_batched(const void* q, const void* k, const void* v, void* o, float* lse,
+                const int32_t* seqused_k, int batch, int heads_q, int heads_kv, int seqlen_q,
+                int seqlen_k, int head_dim, const fal_strides* q_strides,
+                const fal_strides* k_strides, const fal_strides* v_strides,
+                const fal_strides* o_strides, float softmax_scale, int is_causal, int* status,
+                void* stream) {
   if (!q || !k || !v || !o || !lse || !q_strides || !k_strides || !v_strides || !o_strides)
     return FAL_ERR_INVALID_ARGUMENT;
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || seqlen_q <= 0 || seqlen_k < 0)
     return FAL_ERR_INVALID_ARGUMENT;
   if (heads_q % heads_kv != 0 || !(softmax_scale > 0.f)) return FAL_ERR_INVALID_ARGUMENT;
-  // The bottom-right-aligned mask is defined here for a query block that ends where the keys end.
+  // The bottom-right-aligned mask is defined here for a query block that ends where the keys end
+  // (with a length per entry, an entry shorter than the block leaves its first queries without keys).
   if (is_causal < 0 || is_causal > FAL_CAUSAL_BOTTOM_RIGHT) return FAL_ERR_INVALID_ARGUMENT;
-  if (is_causal == FAL_CAUSAL_BOTTOM_RIGHT && seqlen_k < seqlen_q) return FAL_ERR_INVALID_ARGUMENT;
+  if (is_causal == FAL_CAUSAL_BOTTOM_RIGHT && seqused_k == nullptr && seqlen_k < seqlen_q)
+    return FAL_ERR_INVALID_ARGUMENT;
   if (!head_dim_ok(head_dim)) return FAL_ERR_UNSUPPORTED_HEAD_DIM;
   if ((reinterpret_cast<uintptr_t>(o) & 15u) != 0 || o_strides->row % 8 != 0 ||
       o_strides->head % 8 != 0 || o_strides->batch % 8 != 0)
@@ -314,7 +321,9 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   p.head_dim = head_dim;
   p.seqlen_q = seqlen_q;
   p.seqlen_k = seqlen_k;
-  p.causal_shift = is_causal == FAL_CAUSAL_BOTTOM_RIGHT ? seqlen_k - seqlen_q : 0;
+  p.seqused_k = seqused_k;
+  if (seqused_k == nullptr) p.causal_shift = is_causal == FAL_CAUSAL_BOTTOM_RIGHT ? seqlen_k - seqlen_q : 0;
+  else p.shift_per_sequence = is_causal == FAL_CAUSAL_BOTTOM_RIGHT ? 1 : 0;
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
@@ -329,6 +338,29 @@ int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   cudaError_t e = fal::launch_fwd(kdim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
+}
+
+}  // namespace
+
+int fal_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
+            int heads_q, int heads_kv, int seqlen_q, int seqlen_k, int head_dim,
+            const fal_strides* q_strides, const fal_strides* k_strides,
+            const fal_strides* v_strides, const fal_strides* o_strides, float softmax_scale,
+            int is_causal, int* status, void* stream) {
+  return fwd_batched(q, k, v, o, lse, nullptr, batch, heads_q, heads_kv, seqlen_q, seqlen_k, head_dim,
+                     q_strides, k_strides, v_strides, o_strides, softmax_scale, is_causal, status, stream);
+}
+
+int fal_fwd_kvcache(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
+                    const int32_t* cache_seqlens, int batch, int heads_q, int heads_kv, int seqlen_q,
+                    int cache_capacity, int head_dim, const fal_strides* q_strides,
+                    const fal_strides* k_strides, const fal_strides* v_strides,
+                    const fal_strides* o_strides, float softmax_scale, int is_causal, int* status,
+                    void* stream) {
+  if (!cache_seqlens) return FAL_ERR_INVALID_ARGUMENT;
+  return fwd_batched(q, k_cache, v_cache, o, lse, cache_seqlens, batch, heads_q, heads_kv, seqlen_q,
+                     cache_capacity, head_dim, q_strides, k_strides, v_strides, o_strides,
+                     softmax_scale, is_causal, status, stream);
 }
 
 int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* lse,

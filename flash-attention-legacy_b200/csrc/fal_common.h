@@ -38,6 +38,8 @@ struct FwdParams {
   int num_qblk;   // batched: ceil(seqlen_q / cta_rows); packed: bound on all sequences' blocks
   int causal_shift;  // causal kernels, batched: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
   int shift_per_sequence;  // causal kernels, packed: the shift of a sequence is its seqlen_k - seqlen_q
+  const int32_t* seqused_k;  // batched mode, optional: keys in use per batch entry (a cache filled to different
+                             // lengths); seqlen_k is then the capacity, and shift_per_sequence applies per entry
   float scale;       // softmax scale
   float scale_log2;  // softmax scale * log2(e)
   int* status;       // device status word, may be nullptr

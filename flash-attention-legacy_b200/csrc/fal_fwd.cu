@@ -129,8 +129,8 @@ struct FwdSmem {
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kBarOff = kVOff + kStages * kTileBytes;
   // barriers: q_full[2] k_full[S] k_empty[S] v_full[S] v_empty[S] s_ready[2] p_ready[2] o_done[2]
-  //           p_half[2] s_free[2]
-  static constexpr int kNumBars = 2 + 4 * kStages + 10;
+  //           p_half[2] s_free[2] v_fixed
+  static constexpr int kNumBars = 2 + 4 * kStages + 11;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
   // one tile: the running row maximum the warpgroups hand to each other, and their two row sums
   static constexpr int kXchOff = kMiscOff + 16;
@@ -166,7 +166,7 @@ __device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, int cta_rows
     w.q_row0 = 0;
     w.k_row0 = 0;
     w.seqlen_q = p.seqlen_q;
-    w.seqlen_k = p.seqlen_k;
+    w.seqlen_k = p.seqused_k != nullptr ? max(min(__ldg(p.seqused_k + w.batch), p.seqlen_k), 0) : p.seqlen_k;
     w.o_base = w.batch * p.o_strides.batch + w.head * p.o_strides.head;
     w.lse_base = w.batch * p.lse_strides.batch + w.head * p.lse_strides.head;
   } else {
@@ -239,7 +239,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto bar = [&](int i) { return bar0 + 8u * i; };
   const int iQFull = 0, iKFull = 2, iKEmpty = 2 + NS, iVFull = 2 + 2 * NS, iVEmpty = 2 + 3 * NS,
             iSReady = 2 + 4 * NS, iPReady = iSReady + 2, iODone = iSReady + 4, iPHalf = iSReady + 6,
-            iSFree = iSReady + 8;
+            iSFree = iSReady + 8, iVFixed = iSReady + 10;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kMiscOff + 4);
   const WaitCtx wctx{abort_flag, p.status};
@@ -247,8 +247,11 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // SHIFTED: keys the causal diagonal is moved by (batched: one value; packed: per sequence).
-  const int cshift = SHIFTED ? (p.cu_q != nullptr ? wk.seqlen_k - wk.seqlen_q : p.causal_shift) : 0;
+  // SHIFTED: keys the causal diagonal is moved by (batched: one value; packed, or a cache with its
+  // own length per entry: each sequence's seqlen_k - seqlen_q).
+  const int cshift = SHIFTED ? ((p.cu_q != nullptr || p.seqused_k != nullptr) ? wk.seqlen_k - wk.seqlen_q
+                                                                              : p.causal_shift)
+                             : 0;
   // Number of key tiles each 128-row query tile visits.
   const int nk_tiles = (wk.seqlen_k + kTileN - 1) / kTileN;
   int ntile[2];
@@ -263,6 +266,11 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     ntile[w] = n;
   }
   const int n_max = max(ntile[0], ntile[1]);
+  // A cache entry shorter than its capacity: the rows behind its last key are memory the caller
+  // never wrote.  Masked score columns take care of such K rows, but P = 0 times a V row that
+  // happens to hold a NaN or an infinity would still poison O, so the V warp clears those rows of
+  // the last tile in shared memory before the P V that reads them (v_fixed).
+  const bool v_fix = p.seqused_k != nullptr && n_max == nk_tiles && (wk.seqlen_k % kTileN) != 0;
 
   // ---- one-time setup -------------------------------------------------------
   // The producer lane initialises the barriers and sends the first loads (Q, K_0, V_0) on their way
@@ -305,6 +313,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(bar(iODone + w), 1);
       mbar_init(bar(iSFree + w), kTileM);
     }
+    mbar_init(bar(iVFixed), 1);
     fence_mbar_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
@@ -334,21 +343,40 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // ===================== TMA producers ====================================
     // K tiles from warp 8, V tiles from warp 10: each ring refills as soon as its own stage is free
     // (the first tiles went out during setup).
-    if (lane == 0) {
-      if (warp == kSmWarps) {
+    if (warp == kSmWarps) {
+      if (lane == 0) {
         for (int j = (NS > 1) ? 2 : 1; j < n_max; ++j) {
           const int s = j % NS;
           const int use = j / NS;
           if (use > 0) mbar_wait(bar(iKEmpty + s), (use - 1) & 1, wctx, kBarKEmpty + s);
           load_k(j);
         }
-      } else {
+      }
+    } else {
+      if (lane == 0) {
         for (int j = 1; j < n_max; ++j) {
           const int s = j % NS;
           const int use = j / NS;
           if (use > 0) mbar_wait(bar(iVEmpty + s), (use - 1) & 1, wctx, kBarVEmpty + s);
           load_v(j);
         }
+      }
+      __syncwarp();
+      if (v_fix) {
+        // Rows [valid, 128) of the last V tile, every 64-column box: whole 128-byte rows, so the
+        // swizzle inside a row does not matter.
+        const int j = n_max - 1;
+        const int s = j % NS;
+        mbar_wait(bar(iVFull + s), (j / NS) & 1, wctx, kBarVFull + s);
+        const int valid = wk.seqlen_k - j * kTileN;
+        const int chunks = (kTileM - valid) * 8;  // 16-byte pieces per box
+        for (int bx = 0; bx < L::kBoxes; ++bx) {
+          uint4* base = reinterpret_cast<uint4*>(sgen + L::kVOff + s * L::kTileBytes + bx * L::kBoxBytes + valid * 128);
+          for (int i = lane; i < chunks; i += 32) base[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(iVFixed));
       }
     }
     __syncwarp();
@@ -424,6 +452,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           const int s = j % NS;
           mbar_wait(bar(iPHalf + sb), (j >> 1) & 1, wctx, kBarPReady + sb);
           mbar_wait(bar(iVFull + s), (j / NS) & 1, wctx, kBarVFull + s);
+          if (v_fix && j == nt - 1) mbar_wait(bar(iVFixed), 0, wctx, kBarVFull + s);
           tc_fence_after_sync();
           issue_pv(sb, 0, j, 0);
           next_scores(j + 1);
@@ -454,6 +483,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           // still exponentiating the second half.
           mbar_wait(bar(iPHalf + w), j & 1, wctx, kBarPReady + w);
           mbar_wait(bar(iVFull + s), use & 1, wctx, kBarVFull + s);
+          if (v_fix && j == n_max - 1) mbar_wait(bar(iVFixed), 0, wctx, kBarVFull + s);
           tc_fence_after_sync();
           issue_pv(w, w, j, 0);
           mbar_wait(bar(iPReady + w), j & 1, wctx, kBarPReady + w);

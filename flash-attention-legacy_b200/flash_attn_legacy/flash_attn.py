@@ -250,32 +250,61 @@ def flash_attn_with_kvcache(
     cache_layout: str = "bshd",
     cache_starts: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """One decode step: q [B,1,Hq,d] attends to the first cache_seqlens[b] cache positions
-    (from position cache_starts[b] on, if given: the positions before it are left padding).
+    """Attention of new query tokens against key/value caches filled to a length per entry.
 
-    Caches are [B,S,Hkv,d] (`cache_layout="bshd"`) or [B,Hkv,S,d] ("bhsd", HuggingFace).
-    If k, v ([B,1,Hkv,d]) are given they are written into the caches at position
-    cache_seqlens[b] first and attended to as well; `cache_seqlens` itself is not
-    modified.  No causal mask (q_len == 1), as in the reference hook's decode branch
-    (integrations.py:77-98), which this replaces with a split-K kernel.  Inference only.
+    q [B,Lq,Hq,d].  Caches are [B,S,Hkv,d] (`cache_layout="bshd"`) or [B,Hkv,S,d] ("bhsd",
+    HuggingFace); entry b holds cache_seqlens[b] positions (from position cache_starts[b] on, if
+    given: the positions before it are left padding -- decode only).  If k, v ([B,Lq,Hkv,d]) are
+    given they are written into the caches at positions cache_seqlens[b] ... + Lq - 1 first and
+    attended to as well; `cache_seqlens` itself is not modified.  Inference only.
+
+    Lq == 1 is a decode step: no causal mask, as in the reference hook's decode branch
+    (integrations.py:77-98), on the split-K kernel.  Lq > 1 is a chunk of a longer prompt: the
+    chunk's tokens see the entry's cached positions and, causally, each other (the mask is aligned
+    to the end of every entry's keys); it runs on the forward kernel with a key length per entry.
+    The reference computes both cases eagerly over the whole cache.
     """
-    assert q.dim() == 4 and q.shape[1] == 1, "q must be [B, 1, H_q, d]"
+    assert q.dim() == 4, "q must be [B, L_q, H_q, d]"
     assert q.dtype == torch.float16, f"Q must be float16, got {q.dtype}"
-    b, _, hq, d = q.shape
+    b, lq, hq, d = q.shape
     assert d in SUPPORTED_HEAD_DIMS, f"head_dim must be 32, 64, 96, 128, or 256, got {d}"
     seq_axis = 1 if cache_layout == "bshd" else 2
     if cache_seqlens is None:
         cache_seqlens = torch.full((b,), k_cache.shape[seq_axis], dtype=torch.int32, device=q.device)
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(d)
-    k_new = k.reshape(b, -1, d).contiguous() if k is not None else None
-    v_new = v.reshape(b, -1, d).contiguous() if v is not None else None
-    out = flash_attn_legacy_cuda.decode(
-        q.reshape(b, hq, d).contiguous(), k_cache, v_cache, cache_seqlens.to(torch.int32),
-        softmax_scale, k_new, v_new, cache_layout=cache_layout,
-        cache_starts=cache_starts.to(torch.int32).contiguous() if cache_starts is not None else None,
-    )
-    return out.view(b, 1, hq, d)
+    if lq == 1:
+        k_new = k.reshape(b, -1, d).contiguous() if k is not None else None
+        v_new = v.reshape(b, -1, d).contiguous() if v is not None else None
+        out = flash_attn_legacy_cuda.decode(
+            q.reshape(b, hq, d).contiguous(), k_cache, v_cache, cache_seqlens.to(torch.int32),
+            softmax_scale, k_new, v_new, cache_layout=cache_layout,
+            cache_starts=cache_starts.to(torch.int32).contiguous() if cache_starts is not None else None,
+        )
+        return out.view(b, 1, hq, d)
+
+    assert cache_starts is None, "left-padded caches are supported for single-token steps only"
+    lens = cache_seqlens.to(torch.int32)
+    if k is not None:
+        assert v is not None and k.shape == v.shape and k.shape[:2] == (b, lq), "k, v must be [B, L_q, H_kv, d]"
+        # rows lens[b] ... lens[b] + Lq - 1 of every entry (an entry without room for the chunk is an error
+        # the indexing reports)
+        pos = lens.long()[:, None] + torch.arange(lq, device=q.device)[None, :]
+        rows = torch.arange(b, device=q.device)[:, None]
+        if cache_layout == "bshd":
+            k_cache[rows, pos] = k
+            v_cache[rows, pos] = v
+        else:
+            k_cache.transpose(1, 2)[rows, pos] = k
+            v_cache.transpose(1, 2)[rows, pos] = v
+        lens = lens + lq
+    kc = k_cache.transpose(1, 2) if cache_layout == "bshd" else k_cache
+    vc = v_cache.transpose(1, 2) if cache_layout == "bshd" else v_cache
+    # O is written as [B,Lq,Hq,d] memory through its [B,Hq,Lq,d] view: no transpose afterwards
+    out = torch.empty((b, lq, hq, d), dtype=torch.float16, device=q.device)
+    flash_attn_legacy_cuda.forward_kvcache(q.transpose(1, 2), kc, vc, lens.contiguous(), softmax_scale, True,
+                                           out=out.transpose(1, 2))
+    return out
 
 
 class FlashAttention(nn.Module):

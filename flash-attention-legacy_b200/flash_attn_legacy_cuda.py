@@ -47,6 +47,9 @@ _lib.fal_version.argtypes = []
 _lib.fal_fwd.restype = _i
 _lib.fal_fwd.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _sp, _sp, _sp, _sp, _f, _i,
                          _vp, _vp]
+_lib.fal_fwd_kvcache.restype = _i
+_lib.fal_fwd_kvcache.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _sp, _sp, _sp, _sp, _f, _i,
+                                 _vp, _vp]
 _lib.fal_fwd_varlen.restype = _i
 _lib.fal_fwd_varlen.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
                                 _sp, _sp, _sp, _sp, _f, _i, _vp, _vp]
@@ -264,6 +267,41 @@ def forward_rect(Q, K, V, softmax_scale, is_causal=False, bottom_right=False, ou
                         _bhn_strides(Q), _bhn_strides(K), _bhn_strides(V), _bhn_strides(O),
                         float(softmax_scale), (2 if bottom_right else 1) if is_causal else 0,
                         _status_word(Q.device).data_ptr(), _stream(Q)))
+    return [O, L]
+
+
+def forward_kvcache(Q, K_cache, V_cache, cache_seqlens, softmax_scale, is_causal=True, out=None):
+    """A chunk of query tokens against caches filled to a different length per entry.
+
+    Q [B,Hq,Nq,d]; caches [B,Hkv,S,d] (any strides with a contiguous head_dim, so a [B,S,Hkv,d] cache
+    is passed as its transpose(1, 2) view); cache_seqlens int32 [B] on the device: entry b attends to
+    its first cache_seqlens[b] rows.  With `is_causal` the mask is aligned to the end of each entry's
+    keys (query i sees keys <= cache_seqlens[b] - Nq + i): the chunk's own keys are expected to be
+    in the cache already.  Returns [O [B,Hq,Nq,d], L [B,Hq,Nq]].  No device-to-host copy of the
+    lengths.  The reference has no such entry point (its hook computes every step with a cache
+    eagerly, flash_attn_legacy/integrations.py:77-98).
+    """
+    _require_cuda_half("Q", Q, 4)
+    _require_cuda_half("K_cache", K_cache, 4)
+    _require_cuda_half("V_cache", V_cache, 4)
+    _same_device(Q, K_cache, V_cache, cache_seqlens)
+    B, Hq, Nq, d = Q.shape
+    Hkv, S = K_cache.shape[1], K_cache.shape[2]
+    if K_cache.shape[0] != B or tuple(V_cache.shape) != tuple(K_cache.shape) or K_cache.shape[3] != d:
+        raise RuntimeError("caches must be [B, H_kv, S, d] with Q's batch and head_dim")
+    if cache_seqlens.dtype != torch.int32 or tuple(cache_seqlens.shape) != (B,) or not cache_seqlens.is_contiguous():
+        raise RuntimeError("cache_seqlens must be contiguous int32 [B]")
+    if out is not None:
+        _require_cuda_half("out", out, 4)
+        if tuple(out.shape) != (B, Hq, Nq, d):
+            raise RuntimeError("out must be [B, H_q, N_q, d]")
+    O = out if out is not None else torch.empty((B, Hq, Nq, d), dtype=torch.float16, device=Q.device)
+    L = torch.empty((B, Hq, Nq), dtype=torch.float32, device=Q.device)
+    _check(_lib.fal_fwd_kvcache(Q.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), O.data_ptr(), L.data_ptr(),
+                                cache_seqlens.data_ptr(), B, Hq, Hkv, Nq, S, d,
+                                _bhn_strides(Q), _bhn_strides(K_cache), _bhn_strides(V_cache), _bhn_strides(O),
+                                float(softmax_scale), 2 if is_causal else 0,
+                                _status_word(Q.device).data_ptr(), _stream(Q)))
     return [O, L]
 
 

@@ -110,6 +110,24 @@ enum fal_fwd_variant {
 FAL_API int fal_set_fwd_variant(int variant);
 
 /*
+ * Forward of a chunk of query tokens against a key/value cache whose entries are filled to
+ * different lengths: entry b attends to the first cache_seqlens[b] rows of its cache (device int32
+ * [B]; clamped to [0, cache_capacity]).  Otherwise fal_fwd: q [B,Hq,Nq,d], caches [B,Hkv,capacity,d]
+ * by strides (so [B,capacity,Hkv,d] memory works as well), o, lse as there.  is_causal = 2 aligns
+ * the mask to the end of every entry's keys -- query i of the chunk sees keys <= cache_seqlens[b] -
+ * Nq + i, the case of a chunk of new tokens already appended to the cache; a query left without
+ * any key gets o = 0, lse = -inf.  The rows of a cache behind an entry's length are never used,
+ * whatever they hold.  The reference has no counterpart: its hook sends every step with a cache to
+ * eager attention over the whole, equally long cache (flash_attn_legacy/integrations.py:77-98).
+ */
+FAL_API int fal_fwd_kvcache(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
+                            const int32_t* cache_seqlens, int batch, int heads_q, int heads_kv,
+                            int seqlen_q, int cache_capacity, int head_dim,
+                            const fal_strides* q_strides, const fal_strides* k_strides,
+                            const fal_strides* v_strides, const fal_strides* o_strides,
+                            float softmax_scale, int is_causal, int* status, void* stream);
+
+/*
  * Packed (variable-length) forward.  Stands in for flash_attn_forward_varlen
  * (csrc/flash_attn_legacy.cpp:193-290; bound as `forward_varlen` at :299-304).
  *   q [total_q,Hq,d], k/v [total_k,Hkv,d], o [total_q,Hq,d]; lse [total_q,Hq] contiguous.

@@ -151,6 +151,26 @@ def decode_fwd(q, k_cache, v_cache, cache_seqlens, scale, cache_starts=None):
     return o, lse
 
 
+def kvcache_chunk_fwd(q, k_cache, v_cache, cache_seqlens, scale, causal=True):
+    """q [B,Hq,Lq,d]; caches [B,Hkv,S,d]; entry b attends to its first cache_seqlens[b] cache rows, the
+    causal mask aligned to the end of them (query i sees keys <= cache_seqlens[b] - Lq + i): the eager
+    arithmetic of the reference hook's cache branch (integrations.py:80-98), per entry, with the mask
+    where a chunk behind a cached prefix needs it.  Rows of the caches behind an entry's length are
+    not read.  -> (O fp32 [B,Hq,Lq,d], LSE fp32 [B,Hq,Lq]).
+    """
+    bsz, hq, lq, d = q.shape
+    o = torch.zeros(bsz, hq, lq, d, dtype=torch.float32)
+    lse = torch.full((bsz, hq, lq), float("-inf"), dtype=torch.float32)
+    for b in range(bsz):
+        n = int(cache_seqlens[b])
+        if n == 0:
+            continue
+        ob, lb = attention_fwd(q[b:b + 1], k_cache[b:b + 1, :, :n], v_cache[b:b + 1, :, :n], scale, causal,
+                               causal_shift=n - lq)
+        o[b], lse[b] = ob[0], lb[0]
+    return o, lse
+
+
 def attention_fwd_rows(q, k, v, scale, causal, row_start, row_end):
     """attention_fwd restricted to query rows [row_start, row_end) -- same arithmetic, bounded memory.
 

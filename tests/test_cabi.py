@@ -24,7 +24,7 @@ def declared_functions():
 
 def test_header_declares_the_expected_entry_points():
     names = declared_functions()
-    for must in ("fal_fwd", "fal_fwd_varlen", "fal_bwd", "fal_bwd_varlen", "fal_decode", "fal_decode_ranged",
+    for must in ("fal_fwd", "fal_fwd_kvcache", "fal_fwd_varlen", "fal_bwd", "fal_bwd_varlen", "fal_decode", "fal_decode_ranged",
                  "fal_bwd_workspace_bytes", "fal_decode_workspace_bytes", "fal_strerror", "fal_set_fwd_variant"):
         assert must in names
 

@@ -179,3 +179,26 @@ def test_decode_empty_and_full_cache():
     assert torch.all(o[0] == 0) and torch.all(torch.isinf(lse[0]))
     ref, _ = orc.attention_fwd(q[1].view(1, 2, 1, 16), kc[1].permute(1, 0, 2)[None], vc[1].permute(1, 0, 2)[None], 0.25)
     assert torch.allclose(o[1], ref.view(2, 16), atol=1e-6)
+
+
+def test_chunk_against_ragged_caches_is_the_square_problem_per_entry():
+    """kvcache_chunk_fwd: for every entry, the chunk's rows equal the last Lq rows of the square causal
+    problem over that entry's own positions, whatever the caches hold behind its length."""
+    g = torch.Generator().manual_seed(5)
+    bsz, hq, hkv, lq, cap, d = 3, 4, 2, 7, 40, 16
+    lens = torch.tensor([40, 19, 7], dtype=torch.int32)
+    kc = torch.randn(bsz, hkv, cap, d, generator=g)
+    vc = torch.randn(bsz, hkv, cap, d, generator=g)
+    q = torch.randn(bsz, hq, lq, d, generator=g)
+    for b in range(bsz):               # poison what lies behind the lengths
+        kc[b, :, int(lens[b]):] = float("nan")
+        vc[b, :, int(lens[b]):] = float("inf")
+    o, lse = orc.kvcache_chunk_fwd(q, kc, vc, lens, 0.25)
+    assert torch.isfinite(o).all() and torch.isfinite(lse).all()
+    for b in range(bsz):
+        n = int(lens[b])
+        qfull = torch.zeros(1, hq, n, d)
+        qfull[:, :, n - lq:] = q[b]
+        o_sq, lse_sq = orc.attention_fwd(qfull, kc[b:b + 1, :, :n], vc[b:b + 1, :, :n], 0.25, True)
+        assert torch.allclose(o[b], o_sq[0, :, n - lq:], atol=1e-6)
+        assert torch.allclose(lse[b], lse_sq[0, :, n - lq:], atol=1e-6)

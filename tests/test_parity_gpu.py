@@ -825,6 +825,49 @@ def test_chunked_prefill_equals_one_prefill(fal):
     check_grads((qg.grad, kg.grad, vg.grad), ref)
 
 
+@pytest.mark.parametrize("layout", ["bshd", "bhsd"])
+@pytest.mark.parametrize("d", [64, 128])
+def test_chunk_against_caches_of_different_lengths(ext, fal, layout, d):
+    """A chunk of new tokens per entry against caches filled to different lengths (fal_fwd_kvcache):
+    through the binding with the chunk already in the caches, and through flash_attn_with_kvcache, which
+    appends it first.  What lies behind an entry's length is NaN / infinity here and must not matter."""
+    gen = torch.Generator().manual_seed(41 + d)
+    B, Hq, Hkv, S = 5, 8, 2, 1000
+    scale = 1 / math.sqrt(d)
+    for lq, lens in ((37, [1000, 37, 128, 513, 64]), (256, [256, 999, 300, 640, 257]), (130, [130, 131, 1000, 258, 500])):
+        lens_t = torch.tensor(lens, dtype=torch.int32)
+        kc, vc = rand_half(gen, B, Hkv, S, d), rand_half(gen, B, Hkv, S, d)
+        for b in range(B):
+            kc[b, :, lens[b]:] = float("nan")
+            vc[b, :, lens[b]:] = float("inf")
+        q = rand_half(gen, B, Hq, lq, d)
+        o_ref, lse_ref = orc.kvcache_chunk_fwd(q, kc, vc, lens_t, scale)
+        kc_dev = kc.cuda() if layout == "bhsd" else kc.transpose(1, 2).contiguous().cuda()   # [B,S,Hkv,d] memory
+        vc_dev = vc.cuda() if layout == "bhsd" else vc.transpose(1, 2).contiguous().cuda()
+        kv_view = (lambda t: t) if layout == "bhsd" else (lambda t: t.transpose(1, 2))
+        o, lse = ext.forward_kvcache(q.cuda(), kv_view(kc_dev), kv_view(vc_dev), lens_t.cuda(), scale)
+        check_fwd(o, lse, o_ref, lse_ref)
+        # the operator: the caches hold everything but the chunk, which it appends
+        old = lens_t - lq
+        k_new = torch.stack([kc[b, :, old[b]:lens[b]] for b in range(B)]).transpose(1, 2).contiguous()   # [B,lq,Hkv,d]
+        v_new = torch.stack([vc[b, :, old[b]:lens[b]] for b in range(B)]).transpose(1, 2).contiguous()
+        for b in range(B):
+            kc_dev_b = kv_view(kc_dev)[b]
+            kc_dev_b[:, int(old[b]):int(lens[b])] = float("nan")        # not there yet
+        out = fal.flash_attn_with_kvcache(q.transpose(1, 2).contiguous().cuda(), kc_dev, vc_dev, k_new.cuda(), v_new.cuda(),
+                                          cache_seqlens=old.cuda(), cache_layout=layout)
+        assert tuple(out.shape) == (B, lq, Hq, d)
+        assert orc.rel_max_err(out.transpose(1, 2), o_ref) <= orc.TOL_O
+        for b in range(B):     # and the chunk is in the caches now
+            assert torch.equal(kv_view(kc_dev)[b, :, int(old[b]):lens[b]].cpu(), kc[b, :, int(old[b]):lens[b]])
+    # an entry shorter than the chunk: its first queries see no key
+    lens_t = torch.tensor([10, 200, 0, 64, 65], dtype=torch.int32)
+    kc, vc, q = rand_half(gen, B, Hkv, S, d), rand_half(gen, B, Hkv, S, d), rand_half(gen, B, Hq, 64, d)
+    o, lse = ext.forward_kvcache(q.cuda(), kc.cuda(), vc.cuda(), lens_t.cuda(), scale)
+    check_fwd(o, lse, *orc.kvcache_chunk_fwd(q, kc, vc, lens_t, scale))
+    assert ext.device_status() == 0
+
+
 def test_broadcast_views_are_copied_not_misread(ext, fal):
     """K/V expanded over the heads (stride 0) and the expanded gradient of a reduction: the operator
     copies them, the binding refuses them (tests/test_flash_attn.py:177-193 of the reference)."""
