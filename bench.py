@@ -373,8 +373,9 @@ def run_varlen(args, rank, world, local, dist, ext):
 def run_shapes(args, ext):
     """Kernel timing on stated shapes, one JSON line each (one GPU).  A shape is
     `pass:B,Hq,Hkv,Nq,Nk,d[:noncausal]` with pass = fwd, bwd (backward incl. its pre- and post-pass; Nq = Nk)
-    or chunk (forward of the last Nq positions against Nk keys, causal mask aligned to the end of the keys).
-    FLOPs: 4*B*Hq*d per visible (query, key) pair forward, 2.5x that backward."""
+    chunk (forward of the last Nq positions against Nk keys, causal mask aligned to the end of the keys)
+    or kvchunk (chunk against caches of capacity Nk filled to a different length per entry, seeded lengths
+    between Nq and Nk).  FLOPs: 4*Hq*d per visible (query, key) pair forward, 2.5x that backward."""
     for spec in args.shape:
         parts = spec.split(":")
         kind = parts[0]
@@ -390,6 +391,12 @@ def run_shapes(args, ext):
             pairs = Nq * (Nk - Nq) + Nq * (Nq + 1) / 2.0
             fn = lambda: ext.forward_rect(q, k, v, scale, True, bottom_right=True)
             mult = 1.0
+        elif kind == "kvchunk":
+            lens = torch.randint(Nq, Nk + 1, (B,), generator=torch.Generator().manual_seed(7), dtype=torch.int32)
+            pairs = float(sum(Nq * (int(n) - Nq) + Nq * (Nq + 1) / 2.0 for n in lens)) / B  # per batch entry
+            lens_dev = lens.cuda()
+            fn = lambda: ext.forward_kvcache(q, k, v, lens_dev, scale, True)
+            mult = 1.0
         else:
             if Nq != Nk:
                 raise SystemExit("fwd / bwd shapes need Nq == Nk")
@@ -402,7 +409,7 @@ def run_shapes(args, ext):
                 fn = lambda: ext.backward(do, q, k, v, o, lse, scale, causal)
                 mult = 2.5
             else:
-                raise SystemExit(f"unknown pass {kind!r}: fwd, bwd or chunk")
+                raise SystemExit(f"unknown pass {kind!r}: fwd, bwd, chunk or kvchunk")
         for _ in range(args.warmup):
             fn()
         torch.cuda.synchronize()
@@ -769,7 +776,7 @@ def main():
     ap.add_argument("--ring-layout", default="zigzag", choices=["zigzag", "contiguous"],
                     help="long_context with more than one rank: how the sequence rows are dealt to the ranks")
     ap.add_argument("--shape", action="append", default=[],
-                    help="--workload shape: pass:B,Hq,Hkv,Nq,Nk,d[:noncausal] with pass = fwd | bwd | chunk; repeatable")
+                    help="--workload shape: pass:B,Hq,Hkv,Nq,Nk,d[:noncausal] with pass = fwd | bwd | chunk | kvchunk; repeatable")
     ap.add_argument("--fwd-variant", type=int, default=0, choices=[0, 1, 2],
                     help="--workload shape: forward kernel variant (0 = the library's own choice, 1 = one query tile "
                          "per thread block, 2 = two tiles)")
