@@ -264,6 +264,37 @@ def test_every_forward_kernel_variant(ext, tiles, d):
         ext.set_forward_variant(0)
 
 
+def test_seeded_sweep_of_small_shapes(ext):
+    """Sixty seeded random problems -- lengths 1..700 with unequal query / key lengths, every head_dim,
+    GQA ratios 1 / 2 / 4 / 8, no mask / the reference's mask / the end-aligned mask, both forward kernel
+    variants as the library picks them -- forward and backward against the oracle."""
+    rnd = torch.Generator().manual_seed(2024)
+    pick = lambda choices: choices[int(torch.randint(len(choices), (1,), generator=rnd))]
+    for case in range(60):
+        d = pick([32, 64, 96, 128, 256])
+        hkv = pick([1, 2, 3])
+        hq = hkv * pick([1, 2, 4, 8])
+        b = pick([1, 2, 3])
+        nk = int(torch.randint(1, 701, (1,), generator=rnd))
+        mode = pick([0, 1, 2])          # 0 no mask, 1 top-left causal, 2 end-aligned causal
+        nq = nk if mode == 1 or pick([True, False]) else int(torch.randint(1, nk + 1, (1,), generator=rnd))
+        scale = pick([1 / math.sqrt(d), 0.05, 0.3])
+        q, k, v, do = (rand_half(rnd, b, hq, nq, d), rand_half(rnd, b, hkv, nk, d), rand_half(rnd, b, hkv, nk, d),
+                       rand_half(rnd, b, hq, nq, d))
+        shift = nk - nq if mode == 2 else 0
+        where = f"case {case}: b{b} hq{hq} hkv{hkv} nq{nq} nk{nk} d{d} mode{mode}"
+        o, lse = ext.forward_rect(q.cuda(), k.cuda(), v.cuda(), scale, mode != 0, bottom_right=mode == 2)
+        o_ref, lse_ref = orc.attention_fwd(q, k, v, scale, mode != 0, causal_shift=shift)
+        assert orc.rel_max_err(o, o_ref) <= orc.TOL_O, where
+        assert orc.abs_max_err(lse, lse_ref) <= orc.TOL_LSE, where
+        if nq == nk or mode == 2:       # the batched backward takes equal lengths or the end-aligned mask
+            got = ext.backward(do.cuda(), q.cuda(), k.cuda(), v.cuda(), o, lse, scale, mode != 0, bottom_right=mode == 2)
+            ref = orc.attention_bwd(q, k, v, do, scale, mode != 0, causal_shift=shift)
+            for g, r, name in zip(got, ref, ("dq", "dk", "dv")):
+                assert orc.rel_max_err(g, r) <= orc.TOL_GRAD, f"{where} {name}"
+    assert ext.device_status() == 0
+
+
 # ---------------------------------------------------------------------------------------------
 # Packed sequences
 # ---------------------------------------------------------------------------------------------
