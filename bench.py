@@ -243,18 +243,21 @@ def run_reference(args):
     }))
 
 
-def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False, check=False):
+def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False, check=False, lens_init=None):
     """Secondary metric: KV-cache split-K decode with appends, B=64 Hq=32 Hkv=8 d=128, cache 32768.
 
     graph=True captures one step (split-K with append, combine, the length increment) in a CUDA graph
     and replays it `steps` times: a small per-GPU batch is otherwise bound by the host's launch path,
     not by the kernels.  Every replay appends the same new token (at a new position) and uses the same
-    query; the kernels and the bytes they move are those of the eager loop."""
-    B, Hq, Hkv, S, d = batch, 32, 8, 32768, 128
+    query; the kernels and the bytes they move are those of the eager loop.
+    lens_init: the entries' starting lengths (a rank's share of a batch dealt by length); else seeded."""
+    B, Hq, Hkv, S, d = (batch if lens_init is None else len(lens_init)), 32, 8, 32768, 128
     g = torch.Generator(device="cuda").manual_seed(seed)
     kc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
     vc = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
     lens0 = torch.randint(1024, S - steps + 1, (B,), device="cuda", generator=g).to(torch.int32)
+    if lens_init is not None:
+        lens0 = torch.as_tensor(lens_init, dtype=torch.int32).cuda()
     q = torch.randn(steps, B, Hq, d, device="cuda", dtype=torch.float16, generator=g)
     kn = torch.randn(steps, B, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
     vn = torch.randn(steps, B, Hkv, d, device="cuda", dtype=torch.float16, generator=g)
@@ -310,6 +313,20 @@ def run_decode_extra(ext, peaks, steps=256, batch=64, seed=3, graph=False, check
     del kc, vc
     torch.cuda.empty_cache()
     return res
+
+
+def decode_lengths_dealt(world, steps=256, batch=64, capacity=32768, seed=3):
+    """The decode workload's starting lengths (seeded, the same on every rank) and their deal to the ranks:
+    sorted by length and handed out back and forth, so every rank gets batch / world entries and nearly the
+    same number of cached tokens (the ranks' step times are compared by their maximum).
+    -> (all lengths, [the lengths of rank 0, of rank 1, ...])."""
+    lens = torch.randint(1024, capacity - steps + 1, (batch,), generator=torch.Generator().manual_seed(seed)).tolist()
+    order = sorted(range(batch), key=lambda i: -lens[i])
+    shares = [[] for _ in range(world)]
+    for pos, i in enumerate(order):
+        rnd, slot = divmod(pos, world)
+        shares[slot if rnd % 2 == 0 else world - 1 - slot].append(lens[i])
+    return lens, shares
 
 
 def _max_over_ranks(dist, dev, x):
@@ -448,7 +465,8 @@ def run_decode(args, rank, world, local, dist, ext):
     if dist is not None:
         dist.barrier()
     shard = args.decode_batch if (world == 1 and args.decode_batch > 0) else 64 // world
-    res = run_decode_extra(ext, peaks, steps=256, batch=shard, seed=3 + rank, graph=args.decode_graph)
+    share = decode_lengths_dealt(world)[1][rank] if world > 1 else None
+    res = run_decode_extra(ext, peaks, steps=256, batch=shard, seed=3 + rank, graph=args.decode_graph, lens_init=share)
     ms = _max_over_ranks(dist, dev, res["ms_per_step"])
     total_bytes = res["kv_bytes_per_step"]
     if dist is not None:
@@ -463,7 +481,7 @@ def run_decode(args, rank, world, local, dist, ext):
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "dtype": "f16",
             "data": "synthetic",
             "config": {"workload": "decode_B64_Hq32_Hkv8_d128_cache32768_256steps_with_append",
-                       "parallelism": f"{shard} of 64 batch entries per rank, no collective",
+                       "parallelism": f"{shard} of 64 batch entries per rank, dealt by cached length, no collective",
                        "launch_path": res["launch_path"]},
             "frac_of_hbm_peak_per_gpu": gbs / world / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
             "device_status": status}))
@@ -651,10 +669,11 @@ def leg_varlen_split(args, rank, world, dev, dist, ext):
 def leg_decode_split(args, rank, world, dev, dist, ext, peaks):
     """The decode workload (batch 64, cache 32768, 256 steps with appends): the batch entries dealt to the
     ranks.  The one-GPU time (all 64 entries) is taken on every rank in the same run."""
-    full = run_decode_extra(ext, peaks, steps=256, batch=64, seed=300 + rank)
+    all_lens, shares = decode_lengths_dealt(world)
+    full = run_decode_extra(ext, peaks, steps=256, seed=300 + rank, lens_init=all_lens)
     full_ms = _max_over_ranks(dist, dev, full["ms_per_step"])
     shard_n = 64 // world
-    part = run_decode_extra(ext, peaks, steps=256, batch=shard_n, seed=300 + rank, check=(rank == 0))
+    part = run_decode_extra(ext, peaks, steps=256, seed=300 + rank, check=(rank == 0), lens_init=shares[rank])
     ms = _max_over_ranks(dist, dev, part["ms_per_step"])
     total_bytes = part["kv_bytes_per_step"]
     if dist is not None:
@@ -662,7 +681,8 @@ def leg_decode_split(args, rank, world, dev, dist, ext, peaks):
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         total_bytes = t.item()
     res = {"workload": "decode_B64_Hq32_Hkv8_d128_cache32768_256steps_with_append",
-           "parallelism": f"{shard_n} of 64 batch entries per rank, no collective", "launch_path": "eager, two launches per step",
+           "parallelism": f"{shard_n} of 64 batch entries per rank, dealt by cached length (the same 64 lengths as the "
+                          "one-GPU run), no collective", "launch_path": "eager, two launches per step",
            "ms_per_step": ms, "value": total_bytes / ms / 1e6, "unit": "GB/s",
            "frac_of_hbm_peak_per_gpu": total_bytes / ms / 1e6 / world / peaks["hbm_gbs"],
            "one_gpu_ms_per_step": full_ms, "efficiency_vs_one_gpu": full_ms / (world * ms)}

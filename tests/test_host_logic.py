@@ -196,3 +196,20 @@ def test_padding_mask_reaches_the_hook_and_is_honoured_on_cpu(fal):
     real = mask.bool()
     assert torch.allclose(a[real], b[real], atol=1e-4, rtol=1e-4)
     assert not torch.allclose(a[1, 5:], unmasked[1, 5:], atol=1e-4)  # the mask does change row 1
+
+
+def test_bench_deals_decode_entries_by_cached_length():
+    """bench.py's sharded decode leg: every rank gets 64 / world entries of the same 64 seeded lengths and
+    nearly the same number of cached tokens (the ranks are compared by their slowest)."""
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for world in (2, 4, 8):
+        lens, shares = bench.decode_lengths_dealt(world)
+        assert len(lens) == 64 and sorted(x for s in shares for x in s) == sorted(lens)
+        assert all(len(s) == 64 // world for s in shares)
+        totals = [sum(s) for s in shares]
+        assert max(totals) <= 1.05 * min(totals)
+        assert bench.decode_lengths_dealt(world)[0] == lens      # seeded: the same on every rank
