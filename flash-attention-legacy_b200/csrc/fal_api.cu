@@ -504,6 +504,12 @@ int run_bwd(const BwdCall& c) {
     return rc;
   if ((rc = make_tensor_map(&tk, c.k, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_k, 128))) return rc;
   if ((rc = make_tensor_map(&tv, c.v, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_v, 128))) return rc;
+  // dK and dV leave their CTA as whole tiles through TMA stores when their layout can be described
+  // to the TMA unit (else, and for the fp32 partials of a ring step, row by row from registers).
+  CUtensorMap tdk = tk, tdv = tv;
+  const bool store_by_tma = !partial &&
+                            make_tensor_map(&tdk, c.dk, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_dk, 128) == FAL_OK &&
+                            make_tensor_map(&tdv, c.dv, c.head_dim, c.rows_k, c.heads_kv, c.batch, c.s_dv, 128) == FAL_OK;
 
   fal::BwdPrepParams pp{};
   pp.o = c.o;
@@ -530,6 +536,7 @@ int run_bwd(const BwdCall& c) {
   p.dv = c.dv;
   p.dk_f32 = c.dk_f32;
   p.dv_f32 = c.dv_f32;
+  p.store_by_tma = store_by_tma ? 1 : 0;
   p.dk_strides = c.s_dk;
   p.dv_strides = c.s_dv;
   p.dq_accum = dq_accum;
@@ -558,7 +565,7 @@ int run_bwd(const BwdCall& c) {
   const int64_t grid = static_cast<int64_t>(p.num_kvblk) * c.batch * c.heads_kv;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_BWD, c.stream);
-  e = fal::launch_bwd(kdim, c.causal != 0, tq, tk, tv, tdo, tdq, p, static_cast<int>(grid),
+  e = fal::launch_bwd(kdim, c.causal != 0, tq, tk, tv, tdo, tdq, tdk, tdv, p, static_cast<int>(grid),
                       c.stream);
   g_timer.end(FAL_KERNEL_BWD, rec, c.stream);
   if (e != cudaSuccess) return cuda_fail(e);

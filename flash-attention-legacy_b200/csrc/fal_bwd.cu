@@ -199,6 +199,16 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, uint32
       : "memory");
 }
 
+// One swizzled shared-memory box into a 4-D tensor (TMA store; rows and columns past the tensor's
+// extent are dropped).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -207,7 +217,8 @@ template <int D, bool CAUSAL, bool SPLIT>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-               const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
+               const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
+               const __grid_constant__ CUtensorMap tm_dv, const BwdParams p) {
   using L = BwdSmem<D>;
   constexpr int NS = SPLIT ? 1 : L::kQStages;
   // SPLIT: head_dim is 2 * D; CTAs 2n and 2n+1 share key tile n and own columns [0, D) and [D, 2D).
@@ -640,6 +651,14 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     float* out_row32 = p.dk_f32 != nullptr ? (is_dk ? p.dk_f32 : p.dv_f32) + out_off : nullptr;
     const float mul = is_dk ? p.scale : 1.f;
     const uint32_t t_acc = tmem_base + lane_addr + (is_dk ? kColDk : kColDv);
+    // Whole tiles leave through shared memory (the K buffer for dK, the V buffer for dV: every MMA that
+    // read them has completed) and TMA stores: a thread owns a key row, and 32 threads storing 16
+    // bytes each into 32 different rows of global memory is what takes microseconds here otherwise.
+    // A packed sequence's last, partial tile keeps the row-by-row path (the rows behind it belong to
+    // the next sequence, which a tile store would overwrite), and so do the fp32 partials.
+    const bool by_tma = p.store_by_tma != 0 && out_row32 == nullptr &&
+                        (p.cu_k == nullptr || wk.seqlen_k - kv0 >= kKvTile);
+    uint8_t* stage_row = sgen + (is_dk ? L::kKOff : L::kVOff) + kv_row * 128;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
       uint32_t r[32];
@@ -650,7 +669,18 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = 0u;
       }
-      if (kv_ok && out_row32 != nullptr) {
+      if (by_tma) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 out;
+          out.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
+          out.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
+          out.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
+          out.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
+          // box c / 2, 16-byte chunk (c % 2) * 4 + v of the row, 128-byte XOR swizzle
+          *reinterpret_cast<uint4*>(stage_row + (c >> 1) * L::kBoxBytes + ((((c & 1) * 4 + v) ^ (kv_row & 7)) << 4)) = out;
+        }
+      } else if (kv_ok && out_row32 != nullptr) {
         // unrounded partial for a caller that sums the key shard's gradient over several calls
 #pragma unroll
         for (int v = 0; v < 8; ++v)
@@ -668,6 +698,18 @@ fal_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           out.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
           *reinterpret_cast<uint4*>(out_row + c * 32 + v * 8) = out;
         }
+      }
+    }
+    if (by_tma) {  // uniform over the CTA
+      fence_proxy_async_smem();
+      named_barrier_sync(2 + half, 128);
+      if (quarter == 0 && lane == 0) {
+        const uint32_t src = sbase + (is_dk ? L::kKOff : L::kVOff);
+        for (int bx = 0; bx < L::kBoxes; ++bx)
+          tma_store_4d(is_dk ? &tm_dk : &tm_dv, src + bx * L::kBoxBytes, col_own + bx * 64, wk.k_row0 + kv0,
+                       wk.kv_head, wk.batch);
+        bulk_commit_group();
+        bulk_wait_group_read<0>();  // the boxes must have been read before the CTA's shared memory goes away
       }
     }
   } else if (warp < 14) {
@@ -810,8 +852,8 @@ __global__ void __launch_bounds__(256) fal_bwd_post_kernel(const BwdPostParams p
 
 template <int D, bool CAUSAL, bool SPLIT = false>
 cudaError_t launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const CUtensorMap& tdo, const CUtensorMap& tdq, const BwdParams& p, int grid,
-                         cudaStream_t stream) {
+                         const CUtensorMap& tdo, const CUtensorMap& tdq, const CUtensorMap& tdk,
+                         const CUtensorMap& tdv, const BwdParams& p, int grid, cudaStream_t stream) {
   auto kern = fal_bwd_kernel<D, CAUSAL, SPLIT>;
   static DeviceOnce configured;
   cudaError_t e = configured.run([&] {
@@ -820,7 +862,7 @@ cudaError_t launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   });
   if (e != cudaSuccess) return e;
   if (SPLIT && grid > 0x3fffffff) return cudaErrorInvalidValue;
-  kern<<<SPLIT ? 2 * grid : grid, kBwdThreads, BwdSmem<D>::kAllocBytes, stream>>>(tq, tk, tv, tdo, tdq, p);
+  kern<<<SPLIT ? 2 * grid : grid, kBwdThreads, BwdSmem<D>::kAllocBytes, stream>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
   return cudaGetLastError();
 }
 
@@ -845,18 +887,19 @@ cudaError_t launch_bwd_prep(const BwdPrepParams& p, cudaStream_t stream) {
 
 cudaError_t launch_bwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq,
-                       const BwdParams& p, int grid, cudaStream_t stream) {
+                       const CUtensorMap& tdk, const CUtensorMap& tdv, const BwdParams& p, int grid,
+                       cudaStream_t stream) {
   if (head_dim == 128) {
-    return causal ? launch_bwd_t<128, true>(tq, tk, tv, tdo, tdq, p, grid, stream)
-                  : launch_bwd_t<128, false>(tq, tk, tv, tdo, tdq, p, grid, stream);
+    return causal ? launch_bwd_t<128, true>(tq, tk, tv, tdo, tdq, tdk, tdv, p, grid, stream)
+                  : launch_bwd_t<128, false>(tq, tk, tv, tdo, tdq, tdk, tdv, p, grid, stream);
   }
   if (head_dim == 64) {
-    return causal ? launch_bwd_t<64, true>(tq, tk, tv, tdo, tdq, p, grid, stream)
-                  : launch_bwd_t<64, false>(tq, tk, tv, tdo, tdq, p, grid, stream);
+    return causal ? launch_bwd_t<64, true>(tq, tk, tv, tdo, tdq, tdk, tdv, p, grid, stream)
+                  : launch_bwd_t<64, false>(tq, tk, tv, tdo, tdq, tdk, tdv, p, grid, stream);
   }
   if (head_dim == 256) {  // two CTAs per key tile, 128 output columns each
-    return causal ? launch_bwd_t<128, true, true>(tq, tk, tv, tdo, tdq, p, grid, stream)
-                  : launch_bwd_t<128, false, true>(tq, tk, tv, tdo, tdq, p, grid, stream);
+    return causal ? launch_bwd_t<128, true, true>(tq, tk, tv, tdo, tdq, tdk, tdv, p, grid, stream)
+                  : launch_bwd_t<128, false, true>(tq, tk, tv, tdo, tdq, tdk, tdv, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

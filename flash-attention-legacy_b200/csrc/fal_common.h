@@ -51,6 +51,7 @@ struct BwdParams {
   void* dv;  // fp16
   float* dk_f32;  // when set, dK and dV leave as unrounded fp32 here instead (same strides, in floats)
   float* dv_f32;
+  int store_by_tma;  // dK / dV tiles leave through shared memory and TMA stores (the tensor maps are valid)
   RowStrides dk_strides;
   RowStrides dv_strides;
   float* dq_accum;  // fp32 [batch, heads_q, padded_q_rows, head_dim] (packed: [heads_q, padded_total, head_dim])

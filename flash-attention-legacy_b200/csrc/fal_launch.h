@@ -66,7 +66,8 @@ cudaError_t launch_bwd_prep(const BwdPrepParams& p, cudaStream_t stream);
 // tdq: fp32 tensor map of the dQ accumulator (head_dim, padded rows, heads, batch), 32 x 128 boxes.
 cudaError_t launch_bwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq,
-                       const BwdParams& p, int grid, cudaStream_t stream);
+                       const CUtensorMap& tdk, const CUtensorMap& tdv, const BwdParams& p, int grid,
+                       cudaStream_t stream);
 
 // Backward post-pass: dQ = fp16(scale * dq_accum).
 struct BwdPostParams {
