@@ -307,7 +307,13 @@ int fwd_batched(const void* q, const void* k, const void* v, void* o, float* lse
   if ((rc = make_tensor_map(&tv, v, head_dim, seqlen_k, heads_kv, batch, to_rs(v_strides), 128)))
     return rc;
 
+  // O leaves its CTA as whole tiles through TMA stores when its layout can be described to the TMA
+  // unit (else row by row from registers).
+  CUtensorMap to = tq;
+  const bool o_by_tma = make_tensor_map(&to, o, head_dim, seqlen_q, heads_q, batch, to_rs(o_strides), 128) == FAL_OK;
+
   fal::FwdParams p{};
+  p.store_by_tma = o_by_tma ? 1 : 0;
   p.o = o;
   p.lse = lse;
   p.o_strides = to_rs(o_strides);
@@ -335,7 +341,7 @@ int fwd_batched(const void* q, const void* k, const void* v, void* o, float* lse
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * batch * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
-  cudaError_t e = fal::launch_fwd(kdim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  cudaError_t e = fal::launch_fwd(kdim, is_causal != 0, tq, tk, tv, to, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }
@@ -393,7 +399,13 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   if ((rc = make_tensor_map(&tk, k, head_dim, total_k, heads_kv, 1, ks, 128))) return rc;
   if ((rc = make_tensor_map(&tv, v, head_dim, total_k, heads_kv, 1, vs, 128))) return rc;
 
+  fal::RowStrides os = to_rs(o_strides);
+  os.batch = 0;
+  CUtensorMap to = tq;
+  const bool o_by_tma = make_tensor_map(&to, o, head_dim, total_q, heads_q, 1, os, 128) == FAL_OK;
+
   fal::FwdParams p{};
+  p.store_by_tma = o_by_tma ? 1 : 0;
   p.o = o;
   p.lse = lse;
   p.o_strides = to_rs(o_strides);
@@ -421,7 +433,7 @@ int fal_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* 
   const int64_t grid = static_cast<int64_t>(p.num_qblk) * heads_q;
   if (grid > 0x7fffffff) return FAL_ERR_INVALID_ARGUMENT;
   const int rec = g_timer.begin(FAL_KERNEL_FWD, st);
-  cudaError_t e = fal::launch_fwd(kdim, is_causal != 0, tq, tk, tv, p, static_cast<int>(grid), st);
+  cudaError_t e = fal::launch_fwd(kdim, is_causal != 0, tq, tk, tv, to, p, static_cast<int>(grid), st);
   g_timer.end(FAL_KERNEL_FWD, rec, st);
   return e == cudaSuccess ? FAL_OK : cuda_fail(e);
 }

@@ -38,6 +38,7 @@ struct FwdParams {
   int num_qblk;   // batched: ceil(seqlen_q / cta_rows); packed: bound on all sequences' blocks
   int causal_shift;  // causal kernels, batched: query row i sees keys <= i + causal_shift (0: top-left aligned mask)
   int shift_per_sequence;  // causal kernels, packed: the shift of a sequence is its seqlen_k - seqlen_q
+  int store_by_tma;  // O tiles leave through shared memory and TMA stores (the output's tensor map is valid)
   const int32_t* seqused_k;  // batched mode, optional: keys in use per batch entry (a cache filled to different
                              // lengths); seqlen_k is then the capacity, and shift_per_sequence applies per entry
   float scale;       // softmax scale

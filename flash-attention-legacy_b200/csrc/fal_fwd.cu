@@ -218,12 +218,23 @@ __device__ __forceinline__ bool fwd_decode_work(const FwdParams& p, int cta_rows
   return true;
 }
 
+// One swizzled shared-memory box into a 4-D tensor (TMA store; rows and columns past the tensor's
+// extent are dropped).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 // SHIFTED (causal only): the mask's diagonal is moved by seqlen_k - seqlen_q keys (bottom-right
 // alignment); the kernels of the reference's own top-left mask are compiled without it.
 template <int D, bool CAUSAL, bool SHIFTED, bool ONE_TILE>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+               const FwdParams p) {
   using L = FwdSmem<D, ONE_TILE>;
   constexpr int NS = L::kStages;
 
@@ -702,6 +713,16 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const float inv = (l > 0.f) ? 1.f / l : 0.f;
     __half* o_row = static_cast<__half*>(p.o) + wk.o_base +
                     static_cast<int64_t>(q_local) * p.o_strides.row;
+    // A whole tile leaves through shared memory (the tile's Q buffer: its last Q K^T has completed)
+    // and TMA stores: a thread owns a row, and 32 threads storing 16 bytes each into 32 different
+    // rows of global memory is slow.  A packed sequence's last, partial tile keeps the row-by-row
+    // path (the rows behind it belong to the next sequence, which a tile store would overwrite).
+    const bool tile_used = (kAlt || wg < L::kQTiles) && q_tile0 < wk.seqlen_q;
+    // (Not at head_dim 256: measured 5 - 10 % slower there -- the CTA then waits for the TMA unit to read
+    // 64 KB of staging before it can exit, where plain stores drain behind its back.)
+    const bool by_tma = D != 256 && p.store_by_tma != 0 && tile_used &&
+                        (p.cu_q == nullptr || q_tile0 + kTileM <= wk.seqlen_q);
+    uint8_t* stage_row = sgen + L::kQOff + (kAlt ? 0 : wg * L::kTileBytes) + row * 128;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
       if (c * 32 < col0 || c * 32 >= col0 + ncol) continue;
@@ -713,7 +734,18 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = 0u;
       }
-      if (row_ok) {
+      if (by_tma) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 out;
+          out.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
+          out.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
+          out.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
+          out.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
+          // box c / 2, 16-byte chunk (c % 2) * 4 + v of the row, 128-byte XOR swizzle
+          *reinterpret_cast<uint4*>(stage_row + (c >> 1) * L::kBoxBytes + ((((c & 1) * 4 + v) ^ (row & 7)) << 4)) = out;
+        }
+      } else if (row_ok) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           if (c * 32 + v * 8 >= p.head_dim) continue;  // head_dim 32 / 96: no such column
@@ -731,6 +763,18 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                                       : kNegInf;
       p.lse[wk.lse_base + static_cast<int64_t>(q_local) * p.lse_strides.row] = lse;
     }
+    if (by_tma) {  // the same for every thread that wrote into the tile's staging buffer
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (kAlt) asm volatile("bar.sync 15, 256;" ::: "memory");
+      else asm volatile("bar.sync %0, 128;" ::"r"(13 + wg) : "memory");
+      if (quarter == 0 && lane == 0 && (!kAlt || wg == 0)) {
+        const uint32_t src = sbase + L::kQOff + (kAlt ? 0 : wg * L::kTileBytes);
+        for (int bx = 0; bx < L::kBoxes; ++bx)
+          tma_store_4d(&tm_o, src + bx * L::kBoxBytes, bx * 64, wk.q_row0 + q_tile0, wk.head, wk.batch);
+        bulk_commit_group();
+        bulk_wait_group_read<0>();  // the boxes must have been read before the CTA's shared memory goes away
+      }
+    }
     }
   }
 
@@ -745,7 +789,7 @@ fal_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
 template <int D, bool CAUSAL, bool SHIFTED, bool ONE_TILE>
 cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const FwdParams& p, int grid, cudaStream_t stream) {
+                         const CUtensorMap& to, const FwdParams& p, int grid, cudaStream_t stream) {
   auto kern = fal_fwd_kernel<D, CAUSAL, SHIFTED, ONE_TILE>;
   static DeviceOnce configured;  // one per template instance
   cudaError_t e = configured.run([&] {
@@ -753,17 +797,17 @@ cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
                                 FwdSmem<D, ONE_TILE>::kAllocBytes);
   });
   if (e != cudaSuccess) return e;
-  kern<<<grid, kFwdThreads, FwdSmem<D, ONE_TILE>::kAllocBytes, stream>>>(tq, tk, tv, p);
+  kern<<<grid, kFwdThreads, FwdSmem<D, ONE_TILE>::kAllocBytes, stream>>>(tq, tk, tv, to, p);
   return cudaGetLastError();
 }
 
 template <int D, bool ONE_TILE>
 cudaError_t launch_fwd_d(bool causal, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const FwdParams& p, int grid, cudaStream_t stream) {
+                         const CUtensorMap& to, const FwdParams& p, int grid, cudaStream_t stream) {
   if (causal && (p.causal_shift != 0 || p.shift_per_sequence != 0))
-    return launch_fwd_t<D, true, true, ONE_TILE>(tq, tk, tv, p, grid, stream);
-  return causal ? launch_fwd_t<D, true, false, ONE_TILE>(tq, tk, tv, p, grid, stream)
-                : launch_fwd_t<D, false, false, ONE_TILE>(tq, tk, tv, p, grid, stream);
+    return launch_fwd_t<D, true, true, ONE_TILE>(tq, tk, tv, to, p, grid, stream);
+  return causal ? launch_fwd_t<D, true, false, ONE_TILE>(tq, tk, tv, to, p, grid, stream)
+                : launch_fwd_t<D, false, false, ONE_TILE>(tq, tk, tv, to, p, grid, stream);
 }
 
 }  // namespace
@@ -771,16 +815,17 @@ cudaError_t launch_fwd_d(bool causal, const CUtensorMap& tq, const CUtensorMap& 
 int fwd_cta_rows(int head_dim, bool one_tile) { return (head_dim == 256 || one_tile) ? 128 : 256; }
 
 cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream) {
+                       const CUtensorMap& tv, const CUtensorMap& to, const FwdParams& p, int grid,
+                       cudaStream_t stream) {
   const bool one_tile = p.cta_rows == 128;
-  if (head_dim == 256) return one_tile ? launch_fwd_d<256, true>(causal, tq, tk, tv, p, grid, stream) : cudaErrorInvalidValue;
+  if (head_dim == 256) return one_tile ? launch_fwd_d<256, true>(causal, tq, tk, tv, to, p, grid, stream) : cudaErrorInvalidValue;
   if (head_dim == 128) {
-    return one_tile ? launch_fwd_d<128, true>(causal, tq, tk, tv, p, grid, stream)
-                    : launch_fwd_d<128, false>(causal, tq, tk, tv, p, grid, stream);
+    return one_tile ? launch_fwd_d<128, true>(causal, tq, tk, tv, to, p, grid, stream)
+                    : launch_fwd_d<128, false>(causal, tq, tk, tv, to, p, grid, stream);
   }
   if (head_dim == 64) {
-    return one_tile ? launch_fwd_d<64, true>(causal, tq, tk, tv, p, grid, stream)
-                    : launch_fwd_d<64, false>(causal, tq, tk, tv, p, grid, stream);
+    return one_tile ? launch_fwd_d<64, true>(causal, tq, tk, tv, to, p, grid, stream)
+                    : launch_fwd_d<64, false>(causal, tq, tk, tv, to, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

@@ -39,7 +39,8 @@ class DeviceOnce {
 // a CTA takes: 256 (two query tiles) unless head_dim is 256 or the one-tile variant is asked for.
 int fwd_cta_rows(int head_dim, bool one_tile);
 cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const FwdParams& p, int grid, cudaStream_t stream);
+                       const CUtensorMap& tv, const CUtensorMap& to, const FwdParams& p, int grid,
+                       cudaStream_t stream);
 
 // Backward pre-pass: delta = rowsum(dO * O) and zero of the fp32 dQ accumulator.
 struct BwdPrepParams {
